@@ -1,0 +1,583 @@
+// Runtime half of libappy_sm100: context set-up, cached device allocator,
+// pinned-host registration, device mirrors of host ranges, NVRTC compile with
+// an in-memory and on-disk cubin cache, kernel launch, timing, and the host-side
+// integer work for multi-GPU partitioning.  Declarations and the reference
+// interfaces they replace are in include/appy_sm100.h.
+#include <cuda_runtime.h>
+#include <nvrtc.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <map>
+#include <mutex>
+#include <sstream>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/appy_sm100.h"
+
+namespace {
+
+thread_local std::string g_err;
+thread_local std::string g_log;
+std::mutex g_mu;
+std::atomic<int64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  char buf[2048];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+#define CK(call)                                                                          \
+  do {                                                                                    \
+    cudaError_t e_ = (call);                                                              \
+    if (e_ != cudaSuccess)                                                                \
+      return fail(APPY_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_),  \
+                  __FILE__, __LINE__);                                                    \
+  } while (0)
+
+const size_t kWorkspaceBytes = 256 + 8 * 4 * 65536;  // ticket + 4 variables x 65536 CTAs
+
+struct DeviceState {
+  bool ready = false;
+  cudaStream_t streams[2] = {nullptr, nullptr};
+  std::unordered_map<cudaStream_t, void*> workspaces;
+  std::multimap<size_t, void*> free_blocks;          // cached allocator: size -> block
+  std::unordered_map<void*, size_t> live_blocks;     // block -> rounded size
+  std::unordered_map<const void*, std::pair<void*, size_t>> mirrors;  // host -> (dev, bytes)
+  std::unordered_map<const void*, size_t> pinned;    // host ranges registered by us
+};
+DeviceState g_dev[16];
+
+int cur_device(int* dev) {
+  CK(cudaGetDevice(dev));
+  if (*dev < 0 || *dev >= 16) return fail(APPY_ERR_STATE, "device index %d out of range", *dev);
+  return APPY_OK;
+}
+
+size_t round_block(size_t bytes) {
+  if (bytes < 512) return 512;
+  if (bytes <= (1u << 20)) {  // next power of two
+    size_t r = 512;
+    while (r < bytes) r <<= 1;
+    return r;
+  }
+  const size_t q = 2u << 20;  // 2 MiB granules above 1 MiB
+  return (bytes + q - 1) / q * q;
+}
+
+struct Kernel {
+  cudaLibrary_t lib = nullptr;
+  cudaKernel_t kern = nullptr;
+  std::string name;
+};
+std::unordered_map<std::string, Kernel*> g_kernels;  // key: hash + name
+
+uint64_t fnv1a(const std::string& s, uint64_t h = 1469598103934665603ull) {
+  for (unsigned char c : s) {
+    h ^= c;
+    h *= 1099511628211ull;
+  }
+  return h;
+}
+
+int load_cubin(const std::vector<char>& image, const char* name, Kernel** out) {
+  Kernel* k = new Kernel;
+  k->name = name;
+  cudaError_t e = cudaLibraryLoadData(&k->lib, image.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+  if (e != cudaSuccess) {
+    delete k;
+    return fail(APPY_ERR_CUDA, "cudaLibraryLoadData failed: %s", cudaGetErrorString(e));
+  }
+  e = cudaLibraryGetKernel(&k->kern, k->lib, name);
+  if (e != cudaSuccess) {
+    cudaLibraryUnload(k->lib);
+    delete k;
+    return fail(APPY_ERR_CUDA, "kernel `%s` not found in compiled image: %s", name,
+                cudaGetErrorString(e));
+  }
+  *out = k;
+  return APPY_OK;
+}
+
+int nvrtc_build(const char* src, const char* kernel_name, const std::vector<std::string>& opts,
+                std::vector<char>& image) {
+  nvrtcProgram prog;
+  nvrtcResult r = nvrtcCreateProgram(&prog, src, (std::string(kernel_name) + ".cu").c_str(), 0,
+                                     nullptr, nullptr);
+  if (r != NVRTC_SUCCESS)
+    return fail(APPY_ERR_NVRTC, "nvrtcCreateProgram: %s", nvrtcGetErrorString(r));
+  std::vector<const char*> copts;
+  for (auto& o : opts) copts.push_back(o.c_str());
+  r = nvrtcCompileProgram(prog, (int)copts.size(), copts.data());
+  size_t logsz = 0;
+  nvrtcGetProgramLogSize(prog, &logsz);
+  if (logsz > 1) {
+    g_log.resize(logsz);
+    nvrtcGetProgramLog(prog, &g_log[0]);
+  }
+  if (r != NVRTC_SUCCESS) {
+    nvrtcDestroyProgram(&prog);
+    return fail(APPY_ERR_NVRTC, "NVRTC compilation of `%s` failed: %s\n%s", kernel_name,
+                nvrtcGetErrorString(r), g_log.c_str());
+  }
+  size_t sz = 0;
+  r = nvrtcGetCUBINSize(prog, &sz);
+  if (r != NVRTC_SUCCESS || sz == 0) {
+    nvrtcDestroyProgram(&prog);
+    return fail(APPY_ERR_NVRTC, "nvrtcGetCUBINSize: %s", nvrtcGetErrorString(r));
+  }
+  image.resize(sz);
+  nvrtcGetCUBIN(prog, image.data());
+  nvrtcDestroyProgram(&prog);
+  return APPY_OK;
+}
+
+std::vector<std::string> nvrtc_options(const char* options) {
+  std::vector<std::string> opts = {"--gpu-architecture=sm_100a", "--std=c++17", "-default-device"};
+  if (options) {
+    std::stringstream ss(options);
+    std::string line;
+    while (std::getline(ss, line, '\n'))
+      if (!line.empty()) opts.push_back(line);
+  }
+  return opts;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* appy_last_error(void) { return g_err.c_str(); }
+const char* appy_compile_log(void) { return g_log.c_str(); }
+int64_t appy_launch_count(void) { return g_launches.load(); }
+void appy_reset_launch_count(void) { g_launches.store(0); }
+}
+
+// used by the prebuilt kernels' host wrappers
+void appy_note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+int appy_fail_cuda(cudaError_t e, const char* what) {
+  return fail(APPY_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+}
+int appy_fail_arg(const char* what) { return fail(APPY_ERR_ARG, "%s", what); }
+
+extern "C" {
+
+int appy_device_count(int* count) {
+  if (!count) return fail(APPY_ERR_ARG, "count is NULL");
+  cudaError_t e = cudaGetDeviceCount(count);
+  if (e != cudaSuccess) {
+    *count = 0;
+    return fail(APPY_ERR_CUDA, "cudaGetDeviceCount failed: %s", cudaGetErrorString(e));
+  }
+  return APPY_OK;
+}
+
+int appy_device_info(int device, int* sm_count, int* l2_bytes, int* cc, size_t* total_mem) {
+  cudaDeviceProp p;
+  CK(cudaGetDeviceProperties(&p, device));
+  if (sm_count) *sm_count = p.multiProcessorCount;
+  if (l2_bytes) *l2_bytes = p.l2CacheSize;
+  if (cc) *cc = p.major * 10 + p.minor;
+  if (total_mem) *total_mem = p.totalGlobalMem;
+  return APPY_OK;
+}
+
+int appy_init(int device) {
+  if (device < 0 || device >= 16) return fail(APPY_ERR_ARG, "device index %d out of range", device);
+  CK(cudaSetDevice(device));
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState& d = g_dev[device];
+  if (d.ready) return APPY_OK;
+  for (int i = 0; i < 2; ++i) CK(cudaStreamCreateWithFlags(&d.streams[i], cudaStreamNonBlocking));
+  d.ready = true;
+  return APPY_OK;
+}
+
+int appy_shutdown(void) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  for (int dev = 0; dev < 16; ++dev) {
+    DeviceState& d = g_dev[dev];
+    if (!d.ready) continue;
+    if (cudaSetDevice(dev) != cudaSuccess) continue;
+    cudaDeviceSynchronize();
+    for (auto& kv : d.pinned) cudaHostUnregister(const_cast<void*>(kv.first));
+    d.pinned.clear();
+    for (auto& kv : d.mirrors) d.free_blocks.emplace(d.live_blocks[kv.second.first], kv.second.first);
+    d.mirrors.clear();
+    for (auto& kv : d.workspaces) cudaFree(kv.second);
+    d.workspaces.clear();
+    for (auto& kv : d.live_blocks) cudaFree(kv.first);
+    d.live_blocks.clear();
+    d.free_blocks.clear();
+    for (int i = 0; i < 2; ++i)
+      if (d.streams[i]) cudaStreamDestroy(d.streams[i]);
+    d.streams[0] = d.streams[1] = nullptr;
+    d.ready = false;
+  }
+  return APPY_OK;
+}
+
+int appy_get_stream(int which, void** stream) {
+  int dev;
+  if (int rc = cur_device(&dev)) return rc;
+  if (!g_dev[dev].ready) return fail(APPY_ERR_STATE, "appy_init(%d) has not been called", dev);
+  if (which < 0 || which > 1 || !stream) return fail(APPY_ERR_ARG, "bad stream selector");
+  *stream = g_dev[dev].streams[which];
+  return APPY_OK;
+}
+
+int appy_sync(void* stream) {
+  CK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  return APPY_OK;
+}
+
+// ---------------------------------------------------------------- memory
+
+int appy_malloc(void** dptr, size_t bytes) {
+  if (!dptr) return fail(APPY_ERR_ARG, "dptr is NULL");
+  int dev;
+  if (int rc = cur_device(&dev)) return rc;
+  const size_t want = round_block(bytes ? bytes : 1);
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState& d = g_dev[dev];
+  auto it = d.free_blocks.lower_bound(want);
+  if (it != d.free_blocks.end() && it->first <= 2 * want) {
+    *dptr = it->second;
+    d.free_blocks.erase(it);
+    return APPY_OK;
+  }
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, want);
+  if (e == cudaErrorMemoryAllocation) {  // give cached blocks back and retry once
+    cudaGetLastError();
+    for (auto& kv : d.free_blocks) {
+      cudaFree(kv.second);
+      d.live_blocks.erase(kv.second);
+    }
+    d.free_blocks.clear();
+    e = cudaMalloc(&p, want);
+  }
+  if (e != cudaSuccess)
+    return fail(APPY_ERR_CUDA, "cudaMalloc(%zu) failed: %s", want, cudaGetErrorString(e));
+  d.live_blocks[p] = want;
+  *dptr = p;
+  return APPY_OK;
+}
+
+int appy_free(void* dptr) {
+  if (!dptr) return APPY_OK;
+  int dev;
+  if (int rc = cur_device(&dev)) return rc;
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState& d = g_dev[dev];
+  auto it = d.live_blocks.find(dptr);
+  if (it == d.live_blocks.end()) return fail(APPY_ERR_ARG, "appy_free: unknown block %p", dptr);
+  d.free_blocks.emplace(it->second, dptr);
+  return APPY_OK;
+}
+
+int appy_trim(void) {
+  int dev;
+  if (int rc = cur_device(&dev)) return rc;
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState& d = g_dev[dev];
+  CK(cudaDeviceSynchronize());
+  for (auto& kv : d.free_blocks) {
+    cudaFree(kv.second);
+    d.live_blocks.erase(kv.second);
+  }
+  d.free_blocks.clear();
+  return APPY_OK;
+}
+
+int appy_memset(void* dptr, int value, size_t bytes, void* stream) {
+  CK(cudaMemsetAsync(dptr, value, bytes, static_cast<cudaStream_t>(stream)));
+  return APPY_OK;
+}
+
+int appy_register_host(void* hptr, size_t bytes) {
+  if (!hptr || !bytes) return fail(APPY_ERR_ARG, "appy_register_host: empty range");
+  int dev;
+  if (int rc = cur_device(&dev)) return rc;
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState& d = g_dev[dev];
+  auto it = d.pinned.find(hptr);
+  if (it != d.pinned.end()) {
+    if (it->second >= bytes) return APPY_OK;
+    cudaHostUnregister(hptr);
+    d.pinned.erase(it);
+  }
+  cudaError_t e = cudaHostRegister(hptr, bytes, cudaHostRegisterPortable);
+  if (e == cudaErrorHostMemoryAlreadyRegistered) {  // pinned by someone else (e.g. torch): fine
+    cudaGetLastError();
+    return APPY_OK;
+  }
+  if (e != cudaSuccess)
+    return fail(APPY_ERR_CUDA, "cudaHostRegister(%p, %zu) failed: %s", hptr, bytes,
+                cudaGetErrorString(e));
+  d.pinned[hptr] = bytes;
+  return APPY_OK;
+}
+
+int appy_unregister_host(void* hptr) {
+  int dev;
+  if (int rc = cur_device(&dev)) return rc;
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState& d = g_dev[dev];
+  auto it = d.pinned.find(hptr);
+  if (it == d.pinned.end()) return APPY_OK;
+  cudaHostUnregister(hptr);
+  d.pinned.erase(it);
+  return APPY_OK;
+}
+
+int appy_mirror(const void* hptr, size_t bytes, void** dptr, int* created) {
+  if (!hptr || !dptr) return fail(APPY_ERR_ARG, "appy_mirror: NULL argument");
+  int dev;
+  if (int rc = cur_device(&dev)) return rc;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& d = g_dev[dev];
+    auto it = d.mirrors.find(hptr);
+    if (it != d.mirrors.end()) {
+      if (it->second.second >= bytes && it->second.second <= 2 * round_block(bytes)) {
+        *dptr = it->second.first;
+        if (created) *created = 0;
+        return APPY_OK;
+      }
+      d.free_blocks.emplace(d.live_blocks[it->second.first], it->second.first);
+      d.mirrors.erase(it);
+    }
+  }
+  void* p = nullptr;
+  if (int rc = appy_malloc(&p, bytes)) return rc;
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_dev[dev].mirrors[hptr] = std::make_pair(p, round_block(bytes ? bytes : 1));
+  *dptr = p;
+  if (created) *created = 1;
+  return APPY_OK;
+}
+
+int appy_evict(const void* hptr) {
+  int dev;
+  if (int rc = cur_device(&dev)) return rc;
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState& d = g_dev[dev];
+  auto it = d.mirrors.find(hptr);
+  if (it == d.mirrors.end()) return APPY_OK;
+  d.free_blocks.emplace(d.live_blocks[it->second.first], it->second.first);
+  d.mirrors.erase(it);
+  return APPY_OK;
+}
+
+int appy_h2d_async(void* dptr, const void* hptr, size_t bytes, void* stream) {
+  if (!bytes) return APPY_OK;
+  CK(cudaMemcpyAsync(dptr, hptr, bytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+  return APPY_OK;
+}
+int appy_d2h_async(void* hptr, const void* dptr, size_t bytes, void* stream) {
+  if (!bytes) return APPY_OK;
+  CK(cudaMemcpyAsync(hptr, dptr, bytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+  return APPY_OK;
+}
+int appy_d2d_async(void* dst, const void* src, size_t bytes, void* stream) {
+  if (!bytes) return APPY_OK;
+  CK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+  return APPY_OK;
+}
+
+int appy_workspace(void* stream, void** dptr, size_t* bytes) {
+  int dev;
+  if (int rc = cur_device(&dev)) return rc;
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState& d = g_dev[dev];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  auto it = d.workspaces.find(s);
+  if (it == d.workspaces.end()) {
+    void* p = nullptr;
+    CK(cudaMalloc(&p, kWorkspaceBytes));
+    CK(cudaMemset(p, 0, kWorkspaceBytes));
+    it = d.workspaces.emplace(s, p).first;
+  }
+  if (dptr) *dptr = it->second;
+  if (bytes) *bytes = kWorkspaceBytes;
+  return APPY_OK;
+}
+
+// ---------------------------------------------------------------- compile / launch
+
+int appy_compile(const char* src, const char* kernel_name, const char* options,
+                 const char* cache_dir, void** handle) {
+  if (!src || !kernel_name || !handle) return fail(APPY_ERR_ARG, "appy_compile: NULL argument");
+  g_log.clear();
+  std::vector<std::string> opts = nvrtc_options(options);
+  int nv_major = 0, nv_minor = 0;
+  nvrtcVersion(&nv_major, &nv_minor);
+  std::string keystr = std::string(src) + "\x1f";
+  for (auto& o : opts) keystr += o + "\x1f";
+  keystr += std::to_string(nv_major) + "." + std::to_string(nv_minor);
+  char hex[32];
+  snprintf(hex, sizeof hex, "%016llx", (unsigned long long)fnv1a(keystr));
+  const std::string key = std::string(hex) + ":" + kernel_name;
+
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_kernels.find(key);
+  if (it != g_kernels.end()) {
+    *handle = it->second;
+    return APPY_OK;
+  }
+  std::vector<char> image;
+  std::string path;
+  if (cache_dir && *cache_dir) {
+    path = std::string(cache_dir) + "/" + hex + ".cubin";
+    std::ifstream f(path, std::ios::binary);
+    if (f) image.assign(std::istreambuf_iterator<char>(f), std::istreambuf_iterator<char>());
+  }
+  Kernel* k = nullptr;
+  if (!image.empty() && load_cubin(image, kernel_name, &k) != APPY_OK) {
+    image.clear();  // corrupt or stale cache entry: recompile
+    k = nullptr;
+  }
+  if (!k) {
+    if (int rc = nvrtc_build(src, kernel_name, opts, image)) return rc;
+    if (int rc = load_cubin(image, kernel_name, &k)) return rc;
+    if (!path.empty()) {  // best effort; write to a temp name then rename so readers never see a torn file
+      const std::string tmp = path + ".tmp" + std::to_string((unsigned long long)(uintptr_t)k);
+      std::ofstream f(tmp, std::ios::binary);
+      if (f) {
+        f.write(image.data(), (std::streamsize)image.size());
+        f.close();
+        if (f) std::rename(tmp.c_str(), path.c_str());
+        else std::remove(tmp.c_str());
+      }
+    }
+  }
+  g_kernels[key] = k;
+  *handle = k;
+  return APPY_OK;
+}
+
+int appy_compile_check(const char* src, const char* kernel_name, const char* options,
+                       size_t* cubin_bytes) {
+  if (!src || !kernel_name) return fail(APPY_ERR_ARG, "appy_compile_check: NULL argument");
+  g_log.clear();
+  std::vector<char> image;
+  if (int rc = nvrtc_build(src, kernel_name, nvrtc_options(options), image)) return rc;
+  if (cubin_bytes) *cubin_bytes = image.size();
+  return APPY_OK;
+}
+
+int appy_kernel_info(void* handle, int* regs, int* static_smem, int* max_threads) {
+  if (!handle) return fail(APPY_ERR_ARG, "NULL kernel handle");
+  Kernel* k = static_cast<Kernel*>(handle);
+  cudaFuncAttributes a;
+  CK(cudaFuncGetAttributes(&a, (const void*)k->kern));
+  if (regs) *regs = a.numRegs;
+  if (static_smem) *static_smem = (int)a.sharedSizeBytes;
+  if (max_threads) *max_threads = a.maxThreadsPerBlock;
+  return APPY_OK;
+}
+
+int appy_occupancy(void* handle, int block, size_t dyn_smem, int* blocks_per_sm) {
+  if (!handle || !blocks_per_sm) return fail(APPY_ERR_ARG, "NULL argument");
+  Kernel* k = static_cast<Kernel*>(handle);
+  CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, (const void*)k->kern, block,
+                                                   dyn_smem));
+  return APPY_OK;
+}
+
+int appy_launch(void* handle, unsigned grid, unsigned block, size_t dyn_smem, void** args,
+                void* stream) {
+  if (!handle) return fail(APPY_ERR_ARG, "NULL kernel handle");
+  if (grid == 0) return APPY_OK;
+  Kernel* k = static_cast<Kernel*>(handle);
+  if (dyn_smem > 48 * 1024)
+    CK(cudaFuncSetAttribute((const void*)k->kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                            (int)dyn_smem));
+  CK(cudaLaunchKernel((const void*)k->kern, dim3(grid), dim3(block), args, dyn_smem,
+                      static_cast<cudaStream_t>(stream)));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return APPY_OK;
+}
+
+int appy_time_launches(void* handle, unsigned grid, unsigned block, size_t dyn_smem, void** args,
+                       void* stream, int warmup, int iters, float* total_ms) {
+  if (!total_ms || iters <= 0) return fail(APPY_ERR_ARG, "bad timing arguments");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < warmup; ++i)
+    if (int rc = appy_launch(handle, grid, block, dyn_smem, args, stream)) return rc;
+  cudaEvent_t e0, e1;
+  CK(cudaEventCreate(&e0));
+  CK(cudaEventCreate(&e1));
+  CK(cudaEventRecord(e0, s));
+  for (int i = 0; i < iters; ++i)
+    if (int rc = appy_launch(handle, grid, block, dyn_smem, args, stream)) {
+      cudaEventDestroy(e0);
+      cudaEventDestroy(e1);
+      return rc;
+    }
+  CK(cudaEventRecord(e1, s));
+  CK(cudaEventSynchronize(e1));
+  CK(cudaEventElapsedTime(total_ms, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  return APPY_OK;
+}
+
+// ---------------------------------------------------------------- partitioning
+
+int appy_partition_range(int64_t lo, int64_t hi, int parts, int64_t align, int64_t* bounds) {
+  if (parts <= 0 || !bounds || align <= 0) return fail(APPY_ERR_ARG, "bad partition arguments");
+  if (hi < lo) hi = lo;
+  const int64_t n = hi - lo;
+  bounds[0] = lo;
+  for (int p = 1; p < parts; ++p) {
+    // ideal cut, then round to the nearest multiple of `align` in absolute index space
+    const int64_t ideal = lo + (int64_t)((__int128)n * p / parts);
+    int64_t cut = (ideal + align / 2) / align * align;
+    cut = std::max(cut, bounds[p - 1]);
+    cut = std::min(cut, hi);
+    bounds[p] = cut;
+  }
+  bounds[parts] = hi;
+  return APPY_OK;
+}
+
+int appy_partition_rows(const void* indptr, int idx_bytes, int64_t nrows, int parts,
+                        int64_t* bounds) {
+  if (!indptr || parts <= 0 || !bounds || nrows < 0 || (idx_bytes != 4 && idx_bytes != 8))
+    return fail(APPY_ERR_ARG, "bad partition arguments");
+  auto at = [&](int64_t i) -> int64_t {
+    return idx_bytes == 4 ? (int64_t) static_cast<const int32_t*>(indptr)[i]
+                          : static_cast<const int64_t*>(indptr)[i];
+  };
+  const int64_t first = at(0), nnz = at(nrows) - first;
+  bounds[0] = 0;
+  for (int p = 1; p < parts; ++p) {
+    const int64_t target = first + (int64_t)((__int128)nnz * p / parts);
+    // first row r with indptr[r] >= target
+    int64_t a = bounds[p - 1], b = nrows;
+    while (a < b) {
+      const int64_t m = a + (b - a) / 2;
+      if (at(m) < target) a = m + 1; else b = m;
+    }
+    // choose the nearer of the two neighbouring row boundaries
+    if (a > bounds[p - 1] && a <= nrows && (at(a) - target) > (target - at(a - 1))) --a;
+    bounds[p] = std::min(std::max(a, bounds[p - 1]), nrows);
+  }
+  bounds[parts] = nrows;
+  return APPY_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,124 @@
+// T1 / T2: flat lowering of `#pragma parallel for simd` loops
+// (reference lowering: appy/backends/triton/passes/block_loop.py:77-159 tiles the
+// loop by 256 and device_passes/remove_loop_head.py:3-55 gives one tile to each
+// program; device_passes/rewrite_par_reduce_to_atomics.py:10-88 issues one atomic
+// per tile for shared(...) reductions).
+//
+// Here one thread owns V consecutive iterations (one 16-byte access per array),
+// a CTA owns U such chunks per thread, and the grid strides over CTA tiles.
+// The body is a functor generated per loop (or hand-written for the prebuilt
+// kernels) with this interface:
+//
+//   struct Body {
+//     struct Regs { ... };                      // streamed operands of one chunk
+//     void load(i64 i0, Regs&) const;           // issue the 16-byte loads of chunk [i0, i0+V)
+//     void compute(i64 i0, const Regs&);        // evaluate V iterations, store, accumulate
+//     void one(i64 i);                          // one iteration, scalar accesses (ragged edges)
+//     void finish(void* smem);                  // reduction epilogue (empty for T1)
+//   };
+//
+// `load` for all U chunks is issued before any `compute`, so every thread keeps
+// U x (#streamed arrays) 16-byte loads in flight regardless of what the compiler
+// can prove about aliasing between inputs and outputs.
+#pragma once
+#include "appy_device.cuh"
+
+APPY_DEV i64 appy_floor_div_i64(i64 a, i64 b) {
+  i64 q = a / b;
+  return (a % b != 0 && ((a < 0) != (b < 0))) ? q - 1 : q;
+}
+
+template <int V, int U, class Body>
+APPY_DEV void appy_flat(Body& body, i64 lo, i64 hi, void* smem) {
+  if (hi > lo) {
+    // chunk c covers iterations [c*V, c*V+V); chunks are aligned to multiples of V in
+    // absolute index space so that 16-byte aligned bases stay aligned for any lo.
+    const i64 c_lo = appy_floor_div_i64(lo, V);
+    const i64 c_hi = appy_floor_div_i64(hi - 1, V) + 1;
+    const i64 c_full_lo = appy_floor_div_i64(lo + V - 1, V);   // first chunk fully inside
+    const i64 c_full_hi = appy_floor_div_i64(hi, V);           // one past last chunk fully inside
+    const i64 tile = (i64)blockDim.x * U;
+    for (i64 t = c_lo + (i64)blockIdx.x * tile; t < c_hi; t += (i64)gridDim.x * tile) {
+      if (t >= c_full_lo && t + tile <= c_full_hi) {
+        typename Body::Regs r[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) body.load((t + (i64)u * blockDim.x + threadIdx.x) * V, r[u]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) body.compute((t + (i64)u * blockDim.x + threadIdx.x) * V, r[u]);
+      } else {
+#pragma unroll 1
+        for (int u = 0; u < U; ++u) {
+          const i64 c = t + (i64)u * blockDim.x + threadIdx.x;
+          if (c >= c_full_lo && c < c_full_hi) {
+            typename Body::Regs r;
+            body.load(c * V, r);
+            body.compute(c * V, r);
+          } else if (c < c_hi) {
+#pragma unroll 1
+            for (int k = 0; k < V; ++k) {
+              const i64 i = c * V + k;
+              if (i >= lo && i < hi) body.one(i);
+            }
+          }
+        }
+      }
+    }
+  }
+  body.finish(smem);
+}
+
+// ---------------------------------------------------------------------------
+// Grid-level commit of one reduction variable.
+//
+// Mode A (atomic): thread 0 of every CTA issues one atomic on the target scalar.
+// Mode B (ordered): every CTA publishes its partial into a workspace slot; the CTA
+// that draws the last ticket folds the partials in slot order and updates the target
+// with a plain read-modify-write, so the result does not depend on CTA scheduling.
+// The ticket counter wraps back to zero by itself (atomicInc with limit gridDim.x-1),
+// so the workspace needs zeroing only once, when it is created.
+//
+// Workspace layout (bytes): [0,4) ticket, [256, 256 + 8*slots*gridDim.x) partials,
+// variable r using elements [r*gridDim.x, (r+1)*gridDim.x) of 8-byte cells.
+// ---------------------------------------------------------------------------
+struct appy_ws {
+  unsigned* ticket;
+  double* cells;   // 8-byte cells, reinterpret per variable type
+};
+APPY_DEV appy_ws appy_ws_from(void* base) {
+  appy_ws w;
+  w.ticket = reinterpret_cast<unsigned*>(base);
+  w.cells = reinterpret_cast<double*>(reinterpret_cast<char*>(base) + 256);
+  return w;
+}
+
+template <class T> APPY_DEV void appy_ws_publish(const appy_ws& w, int var, T v) {
+  if (threadIdx.x == 0) {
+    T* cell = reinterpret_cast<T*>(w.cells + (size_t)var * gridDim.x + blockIdx.x);
+    __stcg(cell, v);
+  }
+}
+// returns true (to every thread of the CTA) in the CTA that arrives last
+APPY_DEV bool appy_ws_arrive(const appy_ws& w, void* smem) {
+  int* flag = reinterpret_cast<int*>(smem);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned t = atomicInc(w.ticket, gridDim.x - 1);
+    *flag = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  const bool last = *flag != 0;
+  __syncthreads();
+  if (last) __threadfence();
+  return last;
+}
+template <class Op, class T> APPY_DEV T appy_ws_collect(const appy_ws& w, int var, void* smem) {
+  // fixed association order: thread t folds cells t, t+B, t+2B, ... then the block tree
+  const T* cells = reinterpret_cast<const T*>(w.cells + (size_t)var * gridDim.x);
+  T acc = Op::template id<T>();
+  for (unsigned b = threadIdx.x; b < gridDim.x; b += blockDim.x) {
+    const T* cell = reinterpret_cast<const T*>(reinterpret_cast<const double*>(cells) + b);
+    acc = Op::template op<T>(acc, __ldcg(cell));
+  }
+  return appy_block_reduce<Op, T>(acc, reinterpret_cast<T*>(smem));
+}

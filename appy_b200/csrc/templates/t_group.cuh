@@ -1,0 +1,75 @@
+// Group lowering of `#pragma parallel for` loops whose body holds inner
+// `#pragma simd` loops (reference lowering: one Triton program per outer
+// iteration, appy/backends/triton/passes/device_passes/remove_loop_head.py:3-55,
+// inner loops tiled by 256 lanes with a cross-warp tl.sum per tile,
+// appy/backends/triton/passes/block_loop.py:10-74).
+//
+// Here a *group* of G threads owns one outer iteration.  G is 1,2,4,8,16,32
+// (a slice of a warp: reductions are shuffles restricted to the group's lanes)
+// or 0, meaning the whole CTA (reductions through shared memory).  Inner simd
+// loops are strided over the group's lanes; a scalar statement is executed by
+// every lane redundantly and its memory stores by lane 0 only.
+//
+//   struct Body { template <class Grp> void iter(i64 i, const Grp& g); };
+#pragma once
+#include "appy_device.cuh"
+
+template <int G> struct appy_grp {
+  int lane;        // 0..G-1 inside the group
+  u32 mask;        // warp lanes that form this group
+  void* smem;      // unused for sub-warp groups
+  static const int size_static = G;
+  APPY_DEV int size() const { return G; }
+  APPY_DEV void init(void* s) {
+    const int wl = threadIdx.x & 31;
+    lane = wl & (G - 1);
+    mask = (G == 32) ? APPY_FULL_MASK : (((1u << G) - 1u) << (wl & ~(G - 1)));
+    smem = s;
+  }
+  APPY_DEV void barrier() const {
+    if (G > 1) __syncwarp(mask);
+  }
+  template <class Op, class T> APPY_DEV T reduce(T v) const {
+#pragma unroll
+    for (int m = G >> 1; m > 0; m >>= 1) {
+      T o;
+      if (sizeof(T) == 8) {
+        union { T t; u64 u; } x; x.t = v;
+        x.u = __shfl_xor_sync(mask, x.u, m, 32);
+        o = x.t;
+      } else {
+        o = __shfl_xor_sync(mask, v, m, 32);
+      }
+      v = Op::template op<T>(v, o);
+    }
+    return v;
+  }
+};
+
+// whole-CTA group
+template <> struct appy_grp<0> {
+  int lane;
+  u32 mask;
+  void* smem;
+  static const int size_static = 0;
+  APPY_DEV int size() const { return blockDim.x; }
+  APPY_DEV void init(void* s) { lane = threadIdx.x; mask = APPY_FULL_MASK; smem = s; }
+  APPY_DEV void barrier() const { __syncthreads(); }
+  template <class Op, class T> APPY_DEV T reduce(T v) const {
+    return appy_block_reduce<Op, T>(v, reinterpret_cast<T*>(smem));
+  }
+};
+
+template <int G, class Body>
+APPY_DEV void appy_group_rows(Body& body, i64 lo, i64 hi, void* smem) {
+  appy_grp<G> g;
+  g.init(smem);
+  if (G == 0) {
+    for (i64 i = lo + blockIdx.x; i < hi; i += gridDim.x) body.iter(i, g);
+  } else {
+    const int gpb = blockDim.x / (G ? G : 1);                 // groups per CTA
+    const i64 gid = (i64)blockIdx.x * gpb + threadIdx.x / (G ? G : 1);
+    const i64 ngroups = (i64)gridDim.x * gpb;
+    for (i64 i = lo + gid; i < hi; i += ngroups) body.iter(i, g);
+  }
+}

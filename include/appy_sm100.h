@@ -1,0 +1,157 @@
+/*
+ * libappy_sm100 — C ABI of the cuda_sm100 execution backend for APPy-style
+ * annotated loops.
+ *
+ * The reference (habanero-lab/APPy) is pure Python: a loop marked
+ * `#pragma parallel for` is turned into Triton source by
+ * appy/backends/triton/codegen.py:9-73, and the generated host function
+ * (appy/backends/triton/passes/gen_host_code.py:25-42) moves data with torch
+ * (host_passes/gen_data_movement.py:14-96) and launches through Triton
+ * (host_passes/gen_kernel_launch.py:4-73).  This library is what those three
+ * steps bind to instead: compile a CUDA C instantiation of a kernel template
+ * (NVRTC, sm_100a), move data (pinned registration, async copies, cached
+ * device mirrors), launch, and split an iteration space across GPUs.
+ *
+ * Conventions
+ *   - every function returns 0 on success and a negative code on failure;
+ *     appy_last_error() then returns a message for the calling thread;
+ *   - all pointers are plain C pointers; `stream` is a cudaStream_t passed as
+ *     void* (NULL = the legacy default stream, which orders with torch's
+ *     default stream);
+ *   - device pointers named d* must belong to the device made current by
+ *     appy_init();
+ *   - handles returned by appy_compile are immutable and may be launched from
+ *     any thread; the caches behind appy_compile / appy_mirror are guarded by
+ *     one mutex.
+ */
+#ifndef APPY_SM100_H
+#define APPY_SM100_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define APPY_OK 0
+#define APPY_ERR_CUDA (-1)
+#define APPY_ERR_NVRTC (-2)
+#define APPY_ERR_ARG (-3)
+#define APPY_ERR_STATE (-4)
+
+/* ---- runtime ----------------------------------------------------------- */
+
+/* Make `device` current for the calling thread, create the backend's streams and
+ * reduction workspaces on first use.  Replaces the implicit torch/Triton context
+ * set-up of the reference (appy/dispatcher.py:36-41). */
+int appy_init(int device);
+int appy_shutdown(void);
+const char* appy_last_error(void);
+int appy_device_count(int* count);
+/* sm_count, l2_bytes, cc (major*10+minor), total memory of `device` */
+int appy_device_info(int device, int* sm_count, int* l2_bytes, int* cc, size_t* total_mem);
+/* which: 0 = compute stream, 1 = copy stream of the current device */
+int appy_get_stream(int which, void** stream);
+int appy_sync(void* stream);
+/* number of kernel launches issued through this library since load (or last reset) */
+int64_t appy_launch_count(void);
+void appy_reset_launch_count(void);
+
+/* ---- memory ------------------------------------------------------------ */
+
+/* Cached device allocator (replaces `tensor.to('cuda')` allocations,
+ * host_passes/gen_data_movement.py:48-64). */
+int appy_malloc(void** dptr, size_t bytes);
+int appy_free(void* dptr);
+int appy_trim(void);
+int appy_memset(void* dptr, int value, size_t bytes, void* stream);
+/* Pin a caller-owned host range in place so copies from it are true DMA. */
+int appy_register_host(void* hptr, size_t bytes);
+int appy_unregister_host(void* hptr);
+/* Device mirror of a host range, created on first use and then reused
+ * (the residency cache).  `created` (optional) is set to 1 when the mirror is new. */
+int appy_mirror(const void* hptr, size_t bytes, void** dptr, int* created);
+int appy_evict(const void* hptr);
+int appy_h2d_async(void* dptr, const void* hptr, size_t bytes, void* stream);
+int appy_d2h_async(void* hptr, const void* dptr, size_t bytes, void* stream);
+int appy_d2d_async(void* dst, const void* src, size_t bytes, void* stream);
+
+/* ---- compile / launch -------------------------------------------------- */
+
+/* Compile CUDA C `src` with NVRTC for sm_100a and return a handle to the
+ * extern "C" kernel `kernel_name`.  `options` is a '\n'-separated list of extra
+ * NVRTC options (e.g. "-I<dir>\n-DNAME=1").  Results are cached in memory and,
+ * when `cache_dir` is not NULL, as cubin files under that directory.
+ * Replaces utils.load_module_from_str + Triton's JIT (appy/utils.py:46-80). */
+int appy_compile(const char* src, const char* kernel_name, const char* options,
+                 const char* cache_dir, void** handle);
+/* NVRTC step of appy_compile alone: needs no GPU.  Used to syntax-check generated
+ * sources on build machines. */
+int appy_compile_check(const char* src, const char* kernel_name, const char* options,
+                       size_t* cubin_bytes);
+/* compile log of the last appy_compile on this thread (warnings or errors) */
+const char* appy_compile_log(void);
+/* regs per thread, static shared bytes, max threads per block of a compiled kernel */
+int appy_kernel_info(void* handle, int* regs, int* static_smem, int* max_threads);
+int appy_occupancy(void* handle, int block, size_t dyn_smem, int* blocks_per_sm);
+/* args: array of pointers to the kernel arguments, as for cudaLaunchKernel.
+ * Replaces `_kernel[grid](..., num_warps=4)` (host_passes/gen_kernel_launch.py:56-69). */
+int appy_launch(void* handle, unsigned grid, unsigned block, size_t dyn_smem, void** args,
+                void* stream);
+/* Launch `iters` times back to back between two events; returns total milliseconds.
+ * Used by the block-size autotuner. */
+int appy_time_launches(void* handle, unsigned grid, unsigned block, size_t dyn_smem, void** args,
+                       void* stream, int warmup, int iters, float* total_ms);
+/* Zero-initialised reduction workspace of the current device for `stream`
+ * (ticket + per-CTA partial cells); `bytes` receives its size. */
+int appy_workspace(void* stream, void** dptr, size_t* bytes);
+
+/* ---- multi-GPU partitioning (host-side integer work) ------------------- */
+
+/* Split [lo, hi) into `parts` contiguous ranges whose cut points are multiples of
+ * `align` (relative to 0); bounds has parts+1 entries. */
+int appy_partition_range(int64_t lo, int64_t hi, int parts, int64_t align, int64_t* bounds);
+/* Split rows [0, nrows) of a CSR matrix into `parts` contiguous row ranges with
+ * near-equal non-zero counts; indptr is a host array of nrows+1 int32 or int64
+ * entries (idx_bytes = 4 or 8). */
+int appy_partition_rows(const void* indptr, int idx_bytes, int64_t nrows, int parts,
+                        int64_t* bounds);
+/* Row-length histogram of a device-resident indptr: counts[b] = rows whose length
+ * lies in [2^(b-1), 2^b) (b = 0: empty rows), 32 bins; also the longest row. */
+int appy_row_histogram(const void* d_indptr, int idx_bytes, int64_t nrows, int64_t* counts32,
+                       int64_t* max_len, void* stream);
+
+/* ---- prebuilt instantiations of the five templates (float32 / int32) ----
+ * Device pointers; asynchronous on `stream`.  Each is the canonical
+ * instantiation of a template that appy_compile would otherwise build from
+ * generated source. */
+
+/* c[i] = a[i] + b[i]            — examples/01-vec_add.py:7-13 */
+int appy_vec_add_f32(const float* da, const float* db, float* dc, int64_t n, void* stream);
+/* *dresult += sum(a[0:n]), double accumulator — examples/02-vec_sum.py:5-11
+ * (shared scalar is float64: appy/frontend/process_shared.py:37-41).
+ * ordered != 0 selects the scheduling-independent commit. */
+int appy_sum_f32(const float* da, int64_t n, double* dresult, int ordered, void* stream);
+/* *dresult += sum(a[i] for mask[i])          — examples/04-masked_sum.py:7-23 */
+int appy_masked_sum_f32(const float* da, const uint8_t* dmask, int64_t n, double* dresult,
+                        int ordered, void* stream);
+/* y[i] = sum_k data[k] * x[indices[k]], rows [row_lo,row_hi) — examples/03-spmv.py:5-16.
+ * strategy: 0 = row-tile streaming, 2..32 = that many lanes per row. */
+int appy_spmv_csr_f32(const float* ddata, const int32_t* dindptr, const int32_t* dindices,
+                      const float* dx, float* dy, int64_t row_lo, int64_t row_hi, int strategy,
+                      void* stream);
+/* y[i] = sum_j alpha * A[i,j] * x[j]          — examples/05-gemv.py:7-17.
+ * lda in elements; lanes: 32 = warp per row, 0 = CTA per row. */
+int appy_gemv_f32(float alpha, const float* dA, int64_t lda, const float* dx, float* dy,
+                  int64_t row_lo, int64_t row_hi, int64_t ncols, int lanes, void* stream);
+/* C[i,:] = sum_k data[k] * B[indices[k],:]    — examples/06-spmm.py:4-11.
+ * ncols <= 512; ldb/ldc in elements. */
+int appy_spmm_csr_f32(const float* ddata, const int32_t* dindptr, const int32_t* dindices,
+                      const float* dB, int64_t ldb, float* dC, int64_t ldc, int64_t row_lo,
+                      int64_t row_hi, int ncols, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* APPY_SM100_H */
