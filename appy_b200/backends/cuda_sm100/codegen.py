@@ -1,0 +1,487 @@
+"""Plugin entry of the cuda_sm100 backend.
+
+    codegen(loop_source, loop_name, val_map, options) -> (f, code_src)
+
+is the boundary the reference's dispatcher calls for its Triton backend
+(appy/backends/triton/codegen.py:9,73, selected in appy/dispatcher.py:19-43): `f` takes
+the non-module values of `val_map` positionally, in `val_map` order, mutates arrays in
+place and returns nothing; `code_src` is the generated source (here: CUDA C).
+
+What differs underneath: the generated host function of the reference copies every
+NumPy / CPU-tensor argument with ``tensor.to('cuda')`` and back with ``copy_`` on each
+call (appy/backends/triton/passes/host_passes/gen_data_movement.py:14-96) and launches
+``_kernel[grid](..., num_warps=4)`` (host_passes/gen_kernel_launch.py:56-69).  Here `f`
+is a ``CompiledLoop``: it keeps device mirrors of host arrays in the shim's residency
+cache, pins large host buffers that are seen repeatedly, copies asynchronously on a
+stream, specialises the kernel on what decides the code (dtypes, ranks, pointer
+alignment, stride divisibility, overlap of stored arrays with others) and can time
+candidate launch configurations once per specialisation (the block-size autotuner).
+CUDA tensors are used in place and never copied or synchronised.
+"""
+from __future__ import annotations
+
+import ast
+import ctypes as C
+import hashlib
+import json
+import os
+import sys
+import types as _types
+
+import numpy as np
+
+from ...frontend.loop_normalize import normalize
+from ...utils import pretty_dump
+from . import dtypes as T
+from . import runtime as rt
+from .lower import ArgInfo, KernelPlan, Lowering, stored_arrays
+
+code_cache: dict = {}          # (loop_source, signature, options) -> CompiledLoop
+_PIN_MIN_BYTES = 1 << 20
+_seen_host: dict = {}          # host ptr -> times seen (for the pin-on-second-use policy)
+_tune_cache: dict | None = None
+
+
+def _is_numpy(v) -> bool:
+    return isinstance(v, np.ndarray)
+
+
+def _is_torch(v) -> bool:
+    t = sys.modules.get("torch")
+    return t is not None and isinstance(v, t.Tensor)
+
+
+def _kind_of(v) -> tuple:
+    """Signature entry of one argument: decides which kernel source is generated."""
+    if isinstance(v, _types.ModuleType):
+        return ("M",)
+    if _is_numpy(v):
+        return ("A", "np", str(v.dtype), v.ndim)
+    if _is_torch(v):
+        return ("A", v.device.type, str(v.dtype), v.ndim)
+    if isinstance(v, (bool, np.bool_)):
+        return ("S", "bool")
+    if isinstance(v, int):
+        return ("S", "pyint")
+    if isinstance(v, float):
+        return ("S", "pyfloat")
+    if isinstance(v, np.generic):
+        return ("S", str(v.dtype))
+    raise TypeError(f"Unsupported argument of type {type(v).__name__} in a parallel loop")
+
+
+def _scalar_type(kind: str):
+    if kind == "bool":
+        return T.BOOL
+    if kind == "pyint":
+        return T.WEAK_INT
+    if kind == "pyfloat":
+        return T.WEAK_FLOAT
+    return T.from_numpy(np.dtype(kind))
+
+
+_CT = {("b", 8): C.c_bool, ("i", 8): C.c_int8, ("i", 16): C.c_int16, ("i", 32): C.c_int32, ("i", 64): C.c_int64,
+       ("u", 8): C.c_uint8, ("u", 16): C.c_uint16, ("u", 32): C.c_uint32, ("u", 64): C.c_uint64,
+       ("f", 32): C.c_float, ("f", 64): C.c_double}
+
+
+def _tune_store() -> dict:
+    global _tune_cache
+    if _tune_cache is None:
+        _tune_cache = {}
+        d = rt.default_cache_dir()
+        if d:
+            try:
+                with open(os.path.join(d, "autotune.json")) as fh:
+                    _tune_cache = json.load(fh)
+            except (OSError, ValueError):
+                _tune_cache = {}
+    return _tune_cache
+
+
+def _tune_save() -> None:
+    d = rt.default_cache_dir()
+    if not d or _tune_cache is None:
+        return
+    try:
+        tmp = os.path.join(d, f"autotune.json.{os.getpid()}")
+        with open(tmp, "w") as fh:
+            json.dump(_tune_cache, fh)
+        os.replace(tmp, os.path.join(d, "autotune.json"))
+    except OSError:
+        pass
+
+
+class _Array:
+    """One array argument resolved for a launch."""
+    __slots__ = ("name", "obj", "host", "dptr", "nbytes", "shape", "strides", "itemsize", "tmp", "hptr")
+
+
+class Variant:
+    def __init__(self, plan: KernelPlan):
+        self.plan = plan
+        self.handles: dict = {}       # tunables tuple -> kernel handle
+        self.tun = {k: v[0] for k, v in plan.tunables.items()}
+        self.tuned = False
+        self.lo_code = compile(ast.Expression(body=plan.lo_expr), "<lo>", "eval")
+        self.hi_code = compile(ast.Expression(body=plan.hi_expr), "<hi>", "eval")
+
+    def handle(self, tun: dict) -> int:
+        key = tuple(sorted(tun.items()))
+        h = self.handles.get(key)
+        if h is None:
+            opts = [f"-D{k}={v}" for k, v in tun.items()] + list(self.plan.info.get("nvrtc", []))
+            h = rt.compile_kernel(self.plan.source, self.plan.name, opts)
+            self.handles[key] = h
+        return h
+
+
+class CompiledLoop:
+    def __init__(self, loop_source: str, loop_name: str, names: list, signature: tuple, options: dict):
+        self.loop_source = loop_source
+        self.loop_name = loop_name
+        self.names = names                  # val_map names, modules included
+        self.signature = signature
+        self.options = dict(options)
+        self.variants: dict = {}
+        self.arg_names = [n for n, s in zip(names, signature) if s[0] != "M"]
+        self.arg_sigs = [s for s in signature if s[0] != "M"]
+        ndims = {n: s[3] for n, s in zip(names, signature) if s[0] == "A"}
+        self.ir = normalize(loop_source, lambda nm: ndims.get(nm))
+        self.stored = stored_arrays([self.ir.loop])
+        self.last_variant: Variant | None = None
+        self.device = None
+        self.sm_count = 148
+
+    # ------------------------------------------------------------------ specialisation
+    def _resolve_arrays(self, args):
+        arrays = []
+        torch = sys.modules.get("torch")
+        for name, sig, v in zip(self.arg_names, self.arg_sigs, args):
+            if sig[0] != "A":
+                continue
+            a = _Array()
+            a.name, a.obj, a.tmp, a.hptr = name, v, None, 0
+            if sig[1] == "cuda":
+                a.host = False
+                a.dptr = v.data_ptr()
+                a.shape, a.itemsize = tuple(v.shape), v.element_size()
+                a.strides = tuple(v.stride())
+                a.nbytes = 0
+            else:
+                h = v if sig[1] == "np" else v.numpy()
+                if not h.flags.c_contiguous:
+                    a.tmp = np.ascontiguousarray(h)
+                    h2 = a.tmp
+                else:
+                    h2 = h
+                a.host = True
+                a.obj = h
+                a.hptr = h2.ctypes.data
+                a.nbytes = h2.nbytes
+                a.shape, a.itemsize = tuple(h2.shape), h2.itemsize
+                a.strides = tuple(s // h2.itemsize for s in h2.strides)
+                a.dptr = 0
+            arrays.append(a)
+        return arrays
+
+    def _acquire_device(self, arrays, stream):
+        for a in arrays:
+            if not a.host:
+                continue
+            if a.nbytes == 0:
+                a.dptr = 0
+                continue
+            a.dptr, _created = rt.mirror(a.hptr, a.nbytes)
+            if a.nbytes >= _PIN_MIN_BYTES and a.tmp is None and self.options.get("pin_host", True):
+                seen = _seen_host.get(a.hptr, 0) + 1
+                _seen_host[a.hptr] = seen
+                if seen == 2:
+                    try:
+                        rt.check(rt.lib().appy_register_host(C.c_void_p(a.hptr), a.nbytes))
+                        _register_finalizer(a.obj, a.hptr)
+                    except rt.AppyRuntimeError:
+                        pass
+            rt.h2d(a.dptr, a.hptr, a.nbytes, stream)
+
+    def _spec_key(self, arrays):
+        key = []
+        for a in arrays:
+            nd = len(a.shape)
+            unit_last = nd == 0 or a.strides[-1] == 1 or a.shape[-1] <= 1
+            lead = a.strides[:-1] if nd > 1 else ()
+            vec = tuple(all(s % V == 0 for s in lead) for V in (2, 4, 8, 16))
+            key.append((a.dptr % 16 == 0 if a.dptr else True, unit_last, vec))
+        # overlap of a stored array with any other array disables the read-only path
+        noalias = True
+        spans = []
+        for a in arrays:
+            ext = sum((n - 1) * abs(s) for n, s in zip(a.shape, a.strides)) + 1 if all(a.shape) else 0
+            base = a.hptr if a.host else a.dptr
+            spans.append((base, base + ext * a.itemsize, a.name))
+        for (lo1, hi1, n1) in spans:
+            if n1 not in self.stored:
+                continue
+            for (lo2, hi2, n2) in spans:
+                if n2 != n1 and lo1 < hi2 and lo2 < hi1:
+                    noalias = False
+        shape_spec = ()
+        if self.options.get("_shape_spec", True):
+            shape_spec = tuple((a.name, a.shape[1]) for a in arrays if len(a.shape) == 2 and a.name in self.stored)
+        return (tuple(key), noalias, shape_spec)
+
+    def _variant(self, arrays, key) -> Variant:
+        v = self.variants.get(key)
+        if v is not None:
+            return v
+        infos = []
+        by_name = {a.name: a for a in arrays}
+        flags = dict(zip([a.name for a in arrays], key[0]))
+        for name, sig in zip(self.names, self.signature):
+            if sig[0] == "M":
+                infos.append(ArgInfo(name, "module"))
+            elif sig[0] == "S":
+                infos.append(ArgInfo(name, "scalar", _scalar_type(sig[1])))
+            else:
+                a = by_name[name]
+                dt = np.dtype(sig[2].replace("torch.", "")) if sig[1] != "np" else np.dtype(sig[2])
+                aligned, unit_last, vec = flags[name]
+                infos.append(ArgInfo(name, "array", T.from_numpy(dt), len(a.shape), unit_last, aligned,
+                                     dict(zip((2, 4, 8, 16), vec)), a.itemsize))
+        opts = dict(self.options)
+        opts["_noalias"] = key[1]
+        opts["_shape"] = {(n, 1): s for n, s in key[2]}
+        import copy as _copy
+        ir = _copy.deepcopy(self.ir)
+        plan = Lowering(ir, self.loop_name, infos, opts).lower()
+        if self.options.get("fp_contract", "numpy") == "numpy":
+            plan.info["nvrtc"] = ["--fmad=false", "--prec-div=true", "--prec-sqrt=true", "--ftz=false"]
+        else:
+            plan.info["nvrtc"] = ["--fmad=true"]
+        v = Variant(plan)
+        self.variants[key] = v
+        return v
+
+    # ------------------------------------------------------------------ launch
+    def _scope(self, args, arrays):
+        scope = {}
+        for name, sig, val in zip(self.arg_names, self.arg_sigs, args):
+            if sig[0] == "S":
+                scope[name] = val
+        for a in arrays:
+            for d, n in enumerate(a.shape):
+                scope.setdefault(f"{a.name}_shape_{d}", n)
+        return scope
+
+    def _pack(self, variant: Variant, args, arrays, lo, hi, stream):
+        by_name = {a.name: a for a in arrays}
+        scal = dict(zip(self.arg_names, args))
+        vals = []
+        for p in variant.plan.params:
+            if p.kind == "array":
+                vals.append(C.c_void_p(by_name[p.name].dptr))
+            elif p.kind == "scalar":
+                ty = p.ty.strong()
+                v = scal[p.name]
+                vals.append(_CT[(ty.kind, ty.bits)](v.item() if isinstance(v, np.generic) else v))
+            elif p.kind == "shape":
+                vals.append(C.c_int64(by_name[p.array].shape[p.dim]))
+            elif p.kind == "stride":
+                vals.append(C.c_int64(by_name[p.array].strides[p.dim]))
+            elif p.kind == "lo":
+                vals.append(C.c_int64(lo))
+            elif p.kind == "hi":
+                vals.append(C.c_int64(hi))
+            elif p.kind == "ws":
+                vals.append(C.c_void_p(rt.workspace(stream)))
+        return rt.ArgPack(vals)
+
+    def _heuristics(self, variant: Variant, scope, arrays):
+        """Pick the lanes-per-row default from the inner trip count when it is known."""
+        plan = variant.plan
+        if plan.kind in ("group", "rowdot") and not variant.tuned:
+            trip = None
+            hi_n, lo_n = plan.info.get("inner_hi"), plan.info.get("inner_lo")
+            try:
+                if hi_n is not None:
+                    trip = int(eval(compile(ast.Expression(body=hi_n), "<t>", "eval"), {}, scope)) - \
+                        int(eval(compile(ast.Expression(body=lo_n), "<t>", "eval"), {}, scope))
+            except Exception:
+                trip = None
+            if trip is not None:
+                per = 4 * max(1, plan.vec)
+                g = 1
+                while g < 32 and g * per < trip:
+                    g *= 2
+                if trip >= 8192 * max(1, plan.vec) // 4 and plan.kind == "group":
+                    g = 0
+                variant.tun["P_G"] = g
+        if plan.kind == "csr" and not variant.tuned and plan.info.get("indptr"):
+            by_name = {a.name: a for a in arrays}
+            ip = by_name.get(plan.info["indptr"])
+            if ip is not None and ip.shape[0] > 1:
+                counts, _mx = rt.row_histogram(ip.dptr, ip.itemsize, ip.shape[0] - 1)
+                total = sum(counts)
+                # median row-length bin decides the lanes per row
+                acc, med = 0, 0
+                for b, c in enumerate(counts):
+                    acc += c
+                    if acc * 2 >= total:
+                        med = b
+                        break
+                length = 1 << max(med - 1, 0)
+                variant.tun["P_G"] = 1 if length <= 2 else 2 if length <= 4 else 4 if length <= 16 else \
+                    8 if length <= 64 else 16 if length <= 256 else 32
+                variant.info_hist = counts
+            variant.tuned = variant.tuned or not self._want_autotune()
+
+    def _want_autotune(self) -> bool:
+        return bool(self.options.get("autotune", os.environ.get("APPY_AUTOTUNE", "0") == "1"))
+
+    def _autotune(self, variant: Variant, args, arrays, lo, hi, stream):
+        plan = variant.plan
+        n_iter = hi - lo
+        store = _tune_store()
+        bucket = max(n_iter, 1).bit_length()
+        tkey = hashlib.sha1((plan.source + "|".join(map(str, plan.info.get("nvrtc", [])))).encode()).hexdigest() \
+            + f":{bucket}"
+        if tkey in store:
+            variant.tun.update(store[tkey])
+            variant.tuned = True
+            return
+        # keep the stored arrays intact: run candidates, then restore
+        saved = []
+        for a in arrays:
+            if a.name in self.stored:
+                ext = (sum((n - 1) * abs(s) for n, s in zip(a.shape, a.strides)) + 1) * a.itemsize if all(a.shape) else 0
+                if ext:
+                    tmp = rt.malloc(ext)
+                    rt.check(rt.lib().appy_d2d_async(C.c_void_p(tmp), C.c_void_p(a.dptr), ext, C.c_void_p(stream)))
+                    saved.append((a, tmp, ext))
+        best, best_t = dict(variant.tun), float("inf")
+        names = list(plan.tunables)
+        # coordinate descent over the tunables, starting from the defaults
+        cur = dict(variant.tun)
+        pack = self._pack(variant, args, arrays, lo, hi, stream)
+        for name in names:
+            for cand in plan.tunables[name]:
+                trial = dict(cur)
+                trial[name] = cand
+                try:
+                    h = variant.handle(trial)
+                    grid, block, smem = plan.launch_config(trial, n_iter, self.sm_count)
+                    t = rt.time_launches(h, grid, block, pack, smem, stream, warmup=1, iters=5)
+                except rt.AppyRuntimeError:
+                    continue
+                if t < best_t:
+                    best_t, best = t, dict(trial)
+            cur = dict(best)
+        for a, tmp, ext in saved:
+            rt.check(rt.lib().appy_d2d_async(C.c_void_p(a.dptr), C.c_void_p(tmp), ext, C.c_void_p(stream)))
+        rt.sync(stream)
+        for _a, tmp, _e in saved:
+            rt.free(tmp)
+        variant.tun = best
+        variant.tuned = True
+        store[tkey] = best
+        _tune_save()
+
+    def __call__(self, *args):
+        if len(args) != len(self.arg_names):
+            raise TypeError(f"{self.loop_name} expects {len(self.arg_names)} arguments, got {len(args)}")
+        if self.device is None:
+            if rt.device_count() < 1:
+                raise RuntimeError("NVIDIA GPU not found")
+            torch = sys.modules.get("torch")
+            self.device = torch.cuda.current_device() if (torch is not None and torch.cuda.is_initialized()) else 0
+            rt.init(self.device)
+            self.sm_count = rt.device_info(self.device)["sm_count"]
+        arrays = self._resolve_arrays(args)
+        any_host = any(a.host for a in arrays)
+        torch = sys.modules.get("torch")
+        if torch is not None and any(not a.host for a in arrays):
+            stream = torch.cuda.current_stream().cuda_stream
+        else:
+            stream = rt.stream(0)
+        self._acquire_device(arrays, stream)
+        key = self._spec_key(arrays)
+        variant = self._variant(arrays, key)
+        self.last_variant = variant
+        scope = self._scope(args, arrays)
+        lo = int(eval(variant.lo_code, {}, scope))
+        hi = int(eval(variant.hi_code, {}, scope))
+        if hi > lo:
+            if not variant.tuned:
+                self._heuristics(variant, scope, arrays)
+                if self._want_autotune() and not variant.tuned:
+                    self._autotune(variant, args, arrays, lo, hi, stream)
+            pack = self._pack(variant, args, arrays, lo, hi, stream)
+            h = variant.handle(variant.tun)
+            grid, block, smem = variant.plan.launch_config(variant.tun, hi - lo, self.sm_count)
+            rt.launch(h, grid, block, pack, smem, stream)
+        if any_host:
+            for a in arrays:
+                if a.host and a.name in self.stored and a.nbytes:
+                    rt.d2h(a.hptr, a.dptr, a.nbytes, stream)
+            rt.sync(stream)
+            for a in arrays:
+                if a.host and a.tmp is not None and a.name in self.stored:
+                    a.obj[...] = a.tmp
+
+    # convenience for tests and dumps
+    def source_for(self, *args) -> str:
+        arrays = self._resolve_arrays(args)    # host arrays: dptr 0, mirrors are always aligned
+        return self._variant(arrays, self._spec_key(arrays)).plan.source
+
+
+_finalizers: dict = {}
+
+
+def _register_finalizer(obj, hptr: int) -> None:
+    """Unpin and evict the device mirror when the owner of the host buffer goes away."""
+    import weakref
+    base = obj
+    while getattr(base, "base", None) is not None and isinstance(base.base, np.ndarray):
+        base = base.base
+    if hptr in _finalizers:
+        return
+
+    def _drop(p=hptr):
+        _finalizers.pop(p, None)
+        _seen_host.pop(p, None)
+        try:
+            rt.lib().appy_unregister_host(C.c_void_p(p))
+            rt.lib().appy_evict(C.c_void_p(p))
+        except Exception:
+            pass
+
+    try:
+        _finalizers[hptr] = weakref.finalize(base, _drop)
+    except TypeError:
+        pass
+
+
+_OPTION_KEYS = ("ordered_reduction", "fp_contract", "autotune", "pin_host", "_generic_only", "_vectorize",
+                "_stream_hint", "_hoist_safe", "_shape_spec")
+
+
+def codegen(loop_source: str, loop_name: str, val_map: dict, options: dict):
+    """Backend plugin entry (see module docstring)."""
+    names = list(val_map)
+    signature = tuple(_kind_of(v) for v in val_map.values())
+    opt_key = tuple((k, options.get(k)) for k in _OPTION_KEYS if k in options)
+    cache_key = (loop_source, loop_name, tuple(names), signature, opt_key)
+    entry = code_cache.get(cache_key)
+    fresh = entry is None
+    if fresh:
+        entry = CompiledLoop(loop_source, loop_name, names, signature, options)
+        code_cache[cache_key] = entry
+    args = [v for v in val_map.values() if not isinstance(v, _types.ModuleType)]
+    code_src = entry.source_for(*args)
+    if fresh and (options.get("dump_code") or options.get("dump_code_to_file")):
+        if options.get("dump_code"):
+            pretty_dump(code_src, loop_name)
+        if options.get("dump_code_to_file"):
+            with open(options["dump_code_to_file"], "w") as fh:
+                fh.write(code_src)
+    return entry, code_src

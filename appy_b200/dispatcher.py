@@ -1,0 +1,66 @@
+"""Runtime dispatch of an annotated loop (runs every time the loop is reached).
+
+Mirrors appy/dispatcher.py:12-60: build ``val_map`` (name -> runtime value, in order of
+first use in the loop source, plus the ``np`` and ``math`` modules), pick the backend,
+honour ``dry_run`` by executing the plain loop in the caller's scope, otherwise call
+``f(*values)`` positionally with the modules filtered out.
+
+Differences: the reference re-parses the loop source twice on every launch; here the
+list of used names is computed once per loop source and cached, and the backend keeps
+a kernel cache keyed on (loop source, argument kinds and dtypes, options), refined per
+launch by the shape/alignment class of the arguments (see backends/cuda_sm100/codegen.py).
+The only backend is ``cuda_sm100``; there is no CPU fallback.
+"""
+from __future__ import annotations
+
+import math
+import types as _types
+
+import numpy as np
+
+from .frontend import pragma_ast
+from .frontend.loop_normalize import used_names
+
+_names_cache: dict = {}
+
+BACKENDS = ("cuda_sm100",)
+
+
+def _used_names(loop_source: str):
+    names = _names_cache.get(loop_source)
+    if names is None:
+        names = used_names(pragma_ast.parse(loop_source))
+        _names_cache[loop_source] = names
+    return names
+
+
+def build_val_map(loop_source: str, local_scope: dict, global_scope: dict) -> dict:
+    val_map = {}
+    for k in _used_names(loop_source):
+        if k in local_scope:
+            val_map[k] = local_scope[k]
+        elif k in global_scope:
+            val_map[k] = global_scope[k]
+    val_map.setdefault("np", np)
+    val_map.setdefault("math", math)
+    return val_map
+
+
+def codegen(backend_name, loop_source, loop_name, local_scope, global_scope, options):
+    val_map = build_val_map(loop_source, local_scope, global_scope)
+    if backend_name in (None, "cuda_sm100", "triton"):
+        # "triton" is accepted so that programs written for the reference run unchanged
+        from .backends.cuda_sm100.codegen import codegen as sm100_codegen
+        f, code_src = sm100_codegen(loop_source, loop_name, val_map, options)
+    else:
+        raise NotImplementedError("Unknown backend:" + str(backend_name))
+
+    if options.get("dry_run"):
+        try:
+            code_obj = compile(loop_source, filename=f"<{loop_name}>", mode="exec")
+            exec(code_obj, global_scope, local_scope)
+        except Exception as e:
+            raise RuntimeError(f"Error executing loop {loop_name} in dry_run mode: {e}")
+        return
+    args = [v for v in val_map.values() if not isinstance(v, _types.ModuleType)]
+    f(*args)

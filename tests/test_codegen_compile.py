@@ -1,0 +1,119 @@
+"""Generated CUDA C compiles with NVRTC for sm_100a (no GPU needed), and the right
+template is chosen for each loop shape."""
+import math
+import types
+
+import numpy as np
+import pytest
+
+from appy_b200 import dispatcher
+from appy_b200.backends.cuda_sm100 import codegen as cg
+from appy_b200.backends.cuda_sm100 import runtime as rt
+
+f32 = np.float32
+
+
+def build(src, scope, **opts):
+    vm = dispatcher.build_val_map(src, scope, {"np": np, "math": math})
+    entry = cg.CompiledLoop(src, "kernel_loop_1", list(vm), tuple(cg._kind_of(v) for v in vm.values()), opts)
+    args = [v for v in vm.values() if not isinstance(v, types.ModuleType)]
+    code = entry.source_for(*args)
+    variant = list(entry.variants.values())[0]
+    plan = variant.plan
+    for trial in range(2):   # default tunables and the last candidate of each
+        tun = {k: (v[0] if trial == 0 else v[-1]) for k, v in plan.tunables.items()}
+        rt.compile_check(code, "kernel_loop_1", [f"-D{k}={v}" for k, v in tun.items()] + plan.info["nvrtc"])
+    return plan, code
+
+
+A1 = np.ones(1000, f32)
+CASES = {
+    "vec_add": ("#pragma parallel for simd\nfor i in range(n):\n    c[i] = a[i] + b[i]",
+                dict(a=A1, b=A1.copy(), c=A1.copy(), n=1000), "flat", 4),
+    "vec_add_f64": ("#pragma parallel for simd\nfor i in range(n):\n    c[i] = a[i] + b[i]",
+                    dict(a=np.ones(10), b=np.ones(10), c=np.ones(10), n=10), "flat", 2),
+    "sum": ("#pragma parallel for simd shared(b)\nfor i in range(n):\n    b[0] += a[i]",
+            dict(a=A1, b=np.array([0.0]), n=1000), "flat", 4),
+    "masked_if": ("#pragma parallel for shared(b)\nfor i in range(n):\n    if m[i]:\n        b[0] += a[i]",
+                  dict(a=A1, m=np.ones(1000, bool), b=np.array([0.0]), n=1000), "flat", 4),
+    "masked_ternary": ("#pragma parallel for simd shared(b)\nfor i in range(n):\n    b[0] += a[i] if m[i] else 0.0",
+                       dict(a=A1, m=np.ones(1000, bool), b=np.array([0.0]), n=1000), "flat", 4),
+    "max": ("#pragma parallel for simd shared(m)\nfor i in range(n):\n    m[0] = max(m[0], a[i])",
+            dict(a=np.ones(10), m=np.array([-np.inf]), n=10), "flat", 2),
+    "stencil": ("#pragma parallel for simd\nfor i in range(1, n - 1):\n    B[i] = 0.33333 * (A[i-1] + A[i] + A[i+1])",
+                dict(A=np.ones(100), B=np.ones(100), n=100), "flat", 2),
+    "pi": ("#pragma parallel for simd shared(sum,step)\nfor i in range(1, num_steps + 1):\n    x = (i - 0.5) * step[0]\n    sum[0] += 4.0 / (1.0 + x * x)",
+           dict(sum=np.array([0.0]), step=np.array([1e-6]), num_steps=1000), "flat", 1),
+    "var_write": ("#pragma parallel for shared(a)\nfor i in range(10):\n    if i == 3:\n        a[0] = 1",
+                  dict(a=np.array([0])), "flat", 1),
+    "math": ("#pragma parallel for simd\nfor i in range(n):\n    c[i] = np.exp(a[i]) + math.sqrt(abs(a[i])) + np.tanh(a[i]) ** 2 + min(a[i], 2.0) + a[i] // 3 + a[i] % 2",
+             dict(a=A1, c=A1.copy(), n=1000), "flat", 4),
+    "mat_add": ("#pragma parallel for\nfor i in range(n):\n    #pragma simd\n    for j in range(m):\n        c[i, j] = a[i, j] + b[i, j]",
+                dict(a=np.ones((8, 8)), b=np.ones((8, 8)), c=np.ones((8, 8)), n=8, m=8), "group", 1),
+    "rowsum": ("#pragma parallel for\nfor i in range(n):\n    s = 0.0\n    #pragma simd\n    for j in range(m):\n        s += a[i, j]\n    b[i] = s",
+               dict(a=np.ones((8, 8)), b=np.ones(8), n=8, m=8), "rowdot", 2),
+    "rowmax_seq": ("#pragma parallel for\nfor i in range(n):\n    s = -1e308\n    for j in range(m):\n        s = max(s, a[i, j])\n    b[i] = s",
+                   dict(a=np.ones((8, 8)), b=np.ones(8), n=8, m=8), "flat", 2),
+    "gemv": ("#pragma parallel for\nfor i in range(n):\n    yi = 0.0\n    #pragma simd\n    for j in range(m):\n        yi += alpha * A[i, j] * x[j]\n    y[i] = yi",
+             dict(A=np.ones((64, 64), f32), x=np.ones(64, f32), y=np.ones(64, f32), alpha=1.0, n=64, m=64),
+             "rowdot", 4),
+    "spmv": ("#pragma parallel for\nfor i in range(M):\n    start, end = P[i], P[i+1]\n    s = 0.0\n    #pragma simd\n    for j in range(start, end):\n        s += D[j] * x[J[j]]\n    y[i] = s",
+             dict(D=A1, P=np.zeros(11, np.int32), J=np.zeros(1000, np.int32), x=A1, y=A1.copy(), M=10), "csr", 1),
+    "spmm": ("#pragma parallel for\nfor i in range(M):\n    start, end = P[i], P[i+1]\n    y[i, :] = 0\n    for k in range(start, end):\n        y[i, :] += D[k] * B[J[k], :]",
+             dict(D=A1, P=np.zeros(11, np.int32), J=np.zeros(1000, np.int32), B=np.ones((10, 128), f32),
+                  y=np.ones((10, 128), f32), M=10), "csrdense", 4),
+    "spmm_odd": ("#pragma parallel for\nfor i in range(M):\n    start, end = P[i], P[i+1]\n    y[i, :] = 0\n    for k in range(start, end):\n        y[i, :] += D[k] * B[J[k], :]",
+                 dict(D=np.ones(10), P=np.zeros(11, np.int64), J=np.zeros(10, np.int64), B=np.ones((10, 37)),
+                      y=np.ones((10, 37)), M=10), "csrdense", 1),
+    "triangular": ("#pragma parallel for\nfor i in range(n):\n    C[i, :i + 1] *= beta\n    for k in range(m):\n        C[i, :i + 1] += alpha * A[i, k] * A[:i + 1, k]",
+                   dict(C=np.ones((8, 8)), A=np.ones((8, 8)), alpha=1.5, beta=1.2, n=8, m=8), "group", 1),
+    "np_sum": ("#pragma parallel for\nfor i in range(n):\n    y[i] = np.sum(alpha * A[i, :] * x[:] + beta * B[i, :] * x[:])",
+               dict(A=np.ones((8, 8)), B=np.ones((8, 8)), x=np.ones(8), y=np.ones(8), alpha=1.5, beta=1.2, n=8),
+               "rowdot", 2),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_generated_cuda_compiles(name):
+    src, scope, kind, vec = CASES[name]
+    plan, code = build(src, scope)
+    assert plan.kind == kind, (plan.kind, code)
+    assert plan.vec == vec, (plan.vec, code)
+    assert f'extern "C" __global__' in code and "kernel_loop_1" in code
+
+
+def test_generic_group_lowering_is_available_for_every_template_case():
+    for name in ("gemv", "spmv", "spmm", "rowsum"):
+        src, scope, _k, _v = CASES[name]
+        plan, _code = build(src, scope, _generic_only=True)
+        assert plan.kind == "group"
+
+
+def test_ordered_reduction_uses_the_workspace():
+    src, scope, _k, _v = CASES["sum"]
+    plan, code = build(src, scope, ordered_reduction=True)
+    assert plan.uses_ws and "appy_ws_arrive" in code and "appy_atomic" not in code
+    assert plan.params[-1].kind == "ws"
+
+
+def test_unaligned_or_strided_arrays_fall_back_to_scalar_accesses():
+    a = np.ones(1001, f32)[1:]          # 4-byte aligned only: host arrays are mirrored, so still aligned
+    t = pytest.importorskip("torch")
+    src = "#pragma parallel for simd\nfor i in range(n):\n    c[i] = a[i] + b[i]"
+    big = np.ones((10, 7), f32)
+    plan, _ = build("#pragma parallel for simd\nfor i in range(n):\n    c[2, i] = a[1, i]",
+                    dict(a=big, c=big.copy(), n=7))
+    assert plan.vec == 1                 # row stride 7 is not a multiple of the vector width
+
+
+def test_unknown_function_raises_value_error():
+    with pytest.raises(ValueError) as e:
+        build("#pragma parallel for simd\nfor i in range(n):\n    c[i] = frobnicate(a[i])", dict(a=A1, c=A1.copy(), n=4))
+    assert "Unknown function" in str(e.value)
+
+
+def test_argument_order_follows_first_use():
+    src, scope, _k, _v = CASES["spmv"]
+    plan, _ = build(src, scope)
+    names = [p.name for p in plan.params]
+    assert names[:6] == ["M", "P", "D", "x", "J", "y"] and names[-2:] == ["__lo", "__hi"]

@@ -1,0 +1,595 @@
+"""End-to-end parity of ``@appy.jit`` loops on the GPU against NumPy/SciPy.
+
+The first block restates the reference's own result tests for this path
+(tests/integration/triton/tutorial/*.py and tests/unit/general/**: float64 NumPy
+inputs, ``np.allclose`` defaults or atol=1e-6).  The second block runs the five
+benchmark loops as written in examples/01..06 at float32 on seeded inputs against the
+oracle with the tolerances stated per kernel:
+  vec_add: bit-exact; reductions: rtol 1e-5 vs float64;
+  SpMV / GEMV / SpMM: |y - y64| <= 1e-5 * sum|a*x| per element.
+"""
+import numpy as np
+import pytest
+
+import appy_b200 as appy
+from appy_b200 import workloads as W
+from oracle import numpy_oracle as O
+from oracle import python_loops as PL
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _gpu(rt):
+    return rt
+
+
+# =========================================================================== reference tutorial tests
+
+@appy.jit(backend="triton", dump_code=True)
+def t_vec_add(a, b):
+    c = np.empty_like(a)
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        c[i] = a[i] + b[i]
+    return c
+
+
+def test_vec_add():
+    a = np.ones(100)
+    b = np.ones(100)
+    assert np.allclose(t_vec_add(a, b), a + b)
+
+
+@appy.jit(backend="triton", dump_code=True)
+def t_mat_add(a, b):
+    c = np.empty_like(a)
+    #pragma parallel for
+    for i in range(a.shape[0]):
+        #pragma simd
+        for j in range(a.shape[1]):
+            c[i, j] = a[i, j] + b[i, j]
+    return c
+
+
+def test_mat_add():
+    a = np.random.default_rng(0).random((100, 100))
+    b = np.ones((100, 100))
+    assert np.allclose(t_mat_add(a, b), a + b)
+
+
+@appy.jit(backend="triton")
+def t_sum(a):
+    sum = 0.0
+    #pragma parallel for simd shared(sum)
+    for i in range(a.shape[0]):
+        sum += a[i]
+    return sum
+
+
+@appy.jit(backend="triton")
+def t_max(a):
+    m = -np.inf
+    #pragma parallel for simd shared(m)
+    for i in range(a.shape[0]):
+        m = max(m, a[i])
+    return m
+
+
+@appy.jit(backend="triton")
+def t_min(a):
+    m = np.inf
+    #pragma parallel for simd shared(m)
+    for i in range(a.shape[0]):
+        m = min(m, a[i])
+    return m
+
+
+def test_global_reductions():
+    a = np.random.default_rng(1).random(1000)
+    assert np.allclose(t_sum(a), a.sum())
+    assert np.allclose(t_max(a), a.max())
+    assert np.allclose(t_min(a), a.min())
+
+
+@appy.jit(backend="triton")
+def t_rowwise_sum(a, b):
+    #pragma parallel for
+    for i in range(a.shape[0]):
+        #pragma simd
+        s = 0.0
+        for j in range(a.shape[1]):
+            s += a[i, j]
+        b[i] = s
+
+
+@appy.jit(backend="triton")
+def t_rowwise_max(a, b):
+    #pragma parallel for
+    for i in range(a.shape[0]):
+
+        s = -1e308
+        #pragma simd
+        for j in range(a.shape[1]):
+            s = max(s, a[i, j])
+        b[i] = s
+
+
+@appy.jit(backend="triton")
+def t_rowwise_min(a, b):
+    #pragma parallel for
+    for i in range(a.shape[0]):
+
+        s = 1e308
+        #pragma simd
+        for j in range(a.shape[1]):
+            s = min(s, a[i, j])
+        b[i] = s
+
+
+def test_rowwise_reductions():
+    a = np.random.default_rng(2).random((100, 100))
+    b = np.empty(100)
+    t_rowwise_sum(a, b)
+    assert np.allclose(b, a.sum(axis=1))
+    t_rowwise_max(a, b)
+    assert np.allclose(b, a.max(axis=1))
+    t_rowwise_min(a, b)
+    assert np.allclose(b, a.min(axis=1))
+
+
+@appy.jit(backend="triton", dump_code=True)
+def t_spmv(A_data, A_indptr, A_indices, x, M, N):
+    y = np.empty(M, dtype=x.dtype)
+    #pragma parallel for
+    for i in range(M):
+        start, end = A_indptr[i], A_indptr[i+1]
+        s = 0.0
+        #pragma simd
+        for j in range(start, end):
+            s += A_data[j] * x[A_indices[j]]
+        y[i] = s
+    return y
+
+
+def test_spmv_csr_scipy():
+    import scipy.sparse as sp
+    N = 1000
+    A = sp.rand(N, N, density=0.01, format="csr", random_state=3)
+    x = np.random.default_rng(3).random(N)
+    y = t_spmv(A.data, A.indptr, A.indices, x, N, N)
+    assert np.allclose(y, A @ x, atol=1e-6)
+
+
+@appy.jit(dump_code=True)
+def t_pi(num_steps, step):
+    sum = 0.0
+    #pragma parallel for simd shared(sum,step)
+    for i in range(1, num_steps + 1):
+        x = (i - 0.5) * step
+        sum += 4.0 / (1.0 + x * x)
+    return step * sum
+
+
+def test_pi():
+    n = 1_000_000
+    got = t_pi(n, 1.0 / n)
+    assert np.isclose(got, np.pi, rtol=1e-6, atol=1e-8)
+
+
+@appy.jit
+def t_var_write():
+    a = 0
+    #pragma parallel for shared(a)
+    for i in range(10):
+        if i == 3:
+            a = 1
+    return a
+
+
+def test_var_write():
+    assert t_var_write() == 1
+
+
+@appy.jit(backend="triton")
+def t_irregular(a, b):
+    c = np.empty_like(a)
+    #pragma parallel for simd
+    for i in range(0, a.shape[0], 2):
+        c[i] = a[i] + b[i]
+    return c
+
+
+def test_irregular_range_raises_at_first_execution():
+    with pytest.raises(Exception) as e:
+        t_irregular(np.ones(100), np.ones(100))
+    assert "range" in str(e.value) and "step" in str(e.value)
+
+
+@appy.jit(backend="triton")
+def t_bad_pragma(a, b):
+    c = np.empty_like(a)
+    #pragma parallel for simd my_directive
+    for i in range(a.shape[0]):
+        c[i] = a[i] + b[i]
+    return c
+
+
+@appy.jit(backend="triton")
+def t_blank_line_pragma(a, b):
+    c = np.empty_like(a)
+    #pragma parallel for simd
+
+    for i in range(a.shape[0]):
+        c[i] = a[i] + b[i]
+    return c
+
+
+def test_invalid_pragma():
+    a, b = np.ones(10), np.ones(10)
+    assert np.allclose(t_blank_line_pragma(a, b), a + b)
+    with pytest.raises(Exception) as e:
+        t_bad_pragma(a, b)
+    assert "my_directive" in str(e.value)
+
+
+def test_unknown_backend_raises():
+    @appy.jit(backend="metal")
+    def f(a):
+        #pragma parallel for simd
+        for i in range(a.shape[0]):
+            a[i] = 1
+        return a
+
+    with pytest.raises(NotImplementedError):
+        f(np.zeros(4))
+
+
+# =========================================================================== semantics of the front end
+
+@appy.jit
+def scalars_by_value(a, k):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        a[i] = a[i] + k
+        k2 = k + 1
+    return k
+
+
+def test_scalars_are_by_value_and_arrays_in_place():
+    a = np.zeros(33)
+    assert scalars_by_value(a, 5) == 5
+    assert np.all(a == 5)
+
+
+@appy.jit(dry_run=True)
+def dry(a):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        a[i] = a[i] * 2
+    return a
+
+
+def test_dry_run_executes_the_plain_loop():
+    assert np.all(dry(np.ones(7)) == 2)
+
+
+@appy.jit
+def jacobi_like(T, A, B):
+    for t in range(1, T):
+        #pragma parallel for simd
+        for i in range(1, A.shape[0] - 1):
+            B[i] = 0.33333 * (A[i-1] + A[i] + A[i+1])
+        #pragma parallel for simd
+        for i in range(1, B.shape[0] - 1):
+            A[i] = 0.33333 * (B[i-1] + B[i] + B[i+1])
+    return A, B
+
+
+def test_stencil_inside_a_python_time_loop():
+    n = 1000
+    A = (np.arange(n) + 2.0) / n
+    B = (np.arange(n) + 3.0) / n
+    A1, B1 = A.copy(), B.copy()
+    for t in range(1, 10):
+        B1[1:-1] = 0.33333 * (A1[:-2] + A1[1:-1] + A1[2:])
+        A1[1:-1] = 0.33333 * (B1[:-2] + B1[1:-1] + B1[2:])
+    A2, B2 = jacobi_like(10, A.copy(), B.copy())
+    assert np.allclose(A1, A2, atol=1e-6) and np.allclose(B1, B2, atol=1e-6)
+
+
+@appy.jit
+def slices_np_sum(alpha, beta, A, B, x):
+    y = np.empty((A.shape[0],), dtype=x.dtype)
+    #pragma parallel for
+    for i in range(A.shape[0]):
+        y[i] = np.sum(alpha * A[i, :] * x[:] + beta * B[i, :] * x[:])
+    return y
+
+
+@appy.jit
+def triangular_update(alpha, beta, C, A):
+    #pragma parallel for
+    for i in range(A.shape[0]):
+        C[i, :i + 1] *= beta
+        for k in range(A.shape[1]):
+            C[i, :i + 1] += alpha * A[i, k] * A[:i + 1, k]
+    return C
+
+
+def test_slice_expressions():
+    rng = np.random.default_rng(4)
+    n = 100
+    A, B, x = rng.random((n, n)), rng.random((n, n)), rng.random(n)
+    assert np.allclose(slices_np_sum(1.5, 1.2, A, B, x), 1.5 * A @ x + 1.2 * B @ x)
+    C = rng.random((n, n))
+    ref = C.copy()
+    for i in range(n):
+        ref[i, :i + 1] *= 1.2
+        for k in range(n):
+            ref[i, :i + 1] += 1.5 * A[i, k] * A[:i + 1, k]
+    assert np.allclose(triangular_update(1.5, 1.2, C.copy(), A), ref)
+
+
+@appy.jit
+def trace_tanh(a):
+    trace = 0.0
+    #pragma parallel for simd shared(trace)
+    for i in range(a.shape[0]):
+        trace += np.tanh(a[i, i])
+    return a + trace
+
+
+def test_math_functions_and_diagonal_access():
+    x = np.random.default_rng(42).random((100, 100))
+    assert np.allclose(trace_tanh(x), x + np.tanh(np.diag(x)).sum(), atol=1e-6)
+
+
+@appy.jit
+def int_histogram_total(idx, n):
+    total = 0
+    #pragma parallel for simd shared(total)
+    for i in range(n):
+        total += idx[i] % 3
+    return total
+
+
+def test_integer_shared_reduction():
+    idx = np.arange(1000, dtype=np.int32)
+    assert int_histogram_total(idx, 1000) == int((idx % 3).sum())
+
+
+@appy.jit
+def strided_rows(src, dst):
+    #pragma parallel for simd
+    for i in range(src.shape[1]):
+        dst[1, i] = 2.0 * src[0, i]
+
+
+def test_noncontiguous_numpy_views_round_trip():
+    big = np.arange(60, dtype=np.float64).reshape(6, 10)
+    src = big[::2, :7]           # non-contiguous view
+    dst_big = np.zeros((4, 9))
+    dst = dst_big[:, 1:8]
+    strided_rows(src, dst)
+    assert np.all(dst[1] == 2.0 * src[0]) and np.all(dst_big[:, 0] == 0) and np.all(dst[0] == 0)
+
+
+# =========================================================================== the five benchmark loops (float32)
+
+@appy.jit
+def k_vec_add(a, b, c):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        c[i] = a[i] + b[i]
+
+
+@appy.jit
+def k_sum(a):
+    b = 0.0
+    #pragma parallel for simd shared(b)
+    for i in range(a.shape[0]):
+        b += a[i]
+    return b
+
+
+@appy.jit(ordered_reduction=True)
+def k_sum_ordered(a):
+    b = 0.0
+    #pragma parallel for simd shared(b)
+    for i in range(a.shape[0]):
+        b += a[i]
+    return b
+
+
+@appy.jit
+def k_masked_if(a, mask):
+    b = 0.0
+    #pragma parallel for shared(b)
+    for i in range(a.shape[0]):
+        if mask[i]:
+            b += a[i]
+    return b
+
+
+@appy.jit
+def k_masked_ternary(a, mask):
+    b = 0.0
+    #pragma parallel for simd shared(b)
+    for i in range(a.shape[0]):
+        b += a[i] if mask[i] else 0.0
+    return b
+
+
+@appy.jit
+def k_spmv(A_data, A_indptr, A_indices, x, y, M):
+    #pragma parallel for
+    for i in range(M):
+        start, end = A_indptr[i], A_indptr[i+1]
+        s = 0.0
+        #pragma simd
+        for j in range(start, end):
+            s += A_data[j] * x[A_indices[j]]
+        y[i] = s
+
+
+@appy.jit
+def k_gemv(alpha, A, x, y):
+    #pragma parallel for
+    for i in range(A.shape[0]):
+        yi = 0.0
+        #pragma simd
+        for j in range(A.shape[1]):
+            yi += alpha * A[i, j] * x[j]
+        y[i] = yi
+
+
+@appy.jit
+def k_spmm(A_data, A_indptr, A_indices, B, y, M):
+    #pragma parallel for
+    for i in range(M):
+        start, end = A_indptr[i], A_indptr[i+1]
+        y[i, :] = 0
+        for k in range(start, end):
+            y[i, :] += A_data[k] * B[A_indices[k], :]
+
+
+@appy.jit(_generic_only=True)
+def k_spmm_generic(A_data, A_indptr, A_indices, B, y, M):
+    #pragma parallel for
+    for i in range(M):
+        start, end = A_indptr[i], A_indptr[i+1]
+        y[i, :] = 0
+        for k in range(start, end):
+            y[i, :] += A_data[k] * B[A_indices[k], :]
+
+
+@appy.jit(_generic_only=True)
+def k_spmv_generic(A_data, A_indptr, A_indices, x, y, M):
+    #pragma parallel for
+    for i in range(M):
+        start, end = A_indptr[i], A_indptr[i+1]
+        s = 0.0
+        #pragma simd
+        for j in range(start, end):
+            s += A_data[j] * x[A_indices[j]]
+        y[i] = s
+
+
+@pytest.mark.parametrize("n", [1, 5, 1023, 4096, (1 << 20) + 3])
+def test_c1_vec_add_bit_exact_numpy_and_torch(n):
+    import torch
+    a, b = W.vec_add(n, seed=n)
+    c = np.empty_like(a)
+    k_vec_add(a, b, c)
+    assert np.array_equal(c, a + b)
+    if n <= 1023:
+        assert np.array_equal(c, PL.vec_add(a, b))      # the reference's CPU semantics: the plain loop
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    dc = torch.empty_like(da)
+    k_vec_add(da, db, dc)
+    assert np.array_equal(dc.cpu().numpy(), a + b)
+    # an element offset of 1 leaves the pointer 4-byte aligned: scalar variant
+    dc.zero_()
+    k_vec_add(da[1:], db[1:], dc[1:])
+    assert np.array_equal(dc.cpu().numpy()[1:], (a + b)[1:])
+
+
+@pytest.mark.parametrize("n", [1, 1000, (1 << 21) + 5])
+def test_c2_reductions(n):
+    import torch
+    a, m = W.masked_sum(n, seed=n)
+    assert np.isclose(k_sum(a), O.vec_sum(a), rtol=1e-5, atol=0)
+    assert np.isclose(k_sum_ordered(a), O.vec_sum(a), rtol=1e-5, atol=0)
+    ref = O.masked_sum(a, m)
+    assert np.isclose(k_masked_if(a, m), ref, rtol=1e-5, atol=1e-12)
+    assert np.isclose(k_masked_ternary(a, m), ref, rtol=1e-5, atol=1e-12)
+    da, dm = torch.from_numpy(a).cuda(), torch.from_numpy(m).cuda()
+    assert np.isclose(k_masked_ternary(da, dm), ref, rtol=1e-5, atol=1e-12)
+    assert np.isclose(k_sum(da), O.vec_sum(a), rtol=1e-5, atol=0)
+
+
+def test_c2_ordered_reduction_is_reproducible():
+    a = W.vec_sum(1 << 20, seed=9)
+    vals = {k_sum_ordered(a) for _ in range(4)}
+    assert len(vals) == 1
+
+
+@pytest.mark.parametrize("kind", ["poisson", "zipf"])
+@pytest.mark.parametrize("fn", [k_spmv, k_spmv_generic])
+def test_c3_spmv(kind, fn):
+    import torch
+    A, x = W.spmv(1 << 14, 16, kind=kind, cap=4096, seed=7)
+    ref = O.spmv(A.data, A.indptr, A.indices, x)
+    scale = O.spmv_abs(A.data, A.indptr, A.indices, x)
+    y = np.full(A.shape[0], np.nan, np.float32)
+    fn(A.data, A.indptr, A.indices, x, y, A.shape[0])
+    assert np.all(np.abs(y - ref) <= 1e-5 * scale + 1e-30)
+    d = [torch.from_numpy(v).cuda() for v in (A.data, A.indptr, A.indices, x)]
+    dy = torch.empty(A.shape[0], device="cuda")
+    fn(d[0], d[1], d[2], d[3], dy, A.shape[0])
+    assert np.all(np.abs(dy.cpu().numpy() - ref) <= 1e-5 * scale + 1e-30)
+
+
+@pytest.mark.parametrize("m,n", [(257, 1027), (512, 4096)])
+def test_c4_gemv(m, n):
+    rng = np.random.default_rng(m)
+    A = rng.standard_normal((m, n), dtype=np.float32)
+    x = rng.uniform(-1, 1, n).astype(np.float32)
+    y = np.empty(m, np.float32)
+    k_gemv(1.0, A, x, y)
+    assert np.all(np.abs(y - O.gemv(1.0, A, x)) <= 1e-5 * O.gemv_abs(1.0, A, x) + 1e-30)
+    k_gemv(np.float32(0.5), A, x, y)
+    assert np.all(np.abs(y - O.gemv(0.5, A, x)) <= 1e-5 * O.gemv_abs(0.5, A, x) + 1e-30)
+
+
+@pytest.mark.parametrize("fn,nrows,ncols", [(k_spmm, 3000, 128), (k_spmm, 500, 200), (k_spmm, 300, 33),
+                                            (k_spmm_generic, 500, 128)])
+def test_c5_spmm(fn, nrows, ncols):
+    A, B = W.spmm(nrows, 32, 8192, ncols, seed=nrows)
+    ref = O.spmm(A.data, A.indptr, A.indices, B)
+    scale = O.spmm_abs(A.data, A.indptr, A.indices, B)
+    y = np.full((nrows, ncols), np.nan, np.float32)
+    fn(A.data, A.indptr, A.indices, B, y, nrows)
+    assert np.all(np.abs(y - ref) <= 1e-5 * scale + 1e-30)
+
+
+def test_small_loops_match_the_plain_python_loops():
+    """The reference's CPU execution of the same functions (decorator removed)."""
+    A, x = W.spmv(200, 8, seed=1)
+    y = np.empty(200, np.float32)
+    k_spmv(A.data, A.indptr, A.indices, x, y, 200)
+    assert np.allclose(y, PL.spmv(A.data, A.indptr, A.indices, x, 200), rtol=1e-5, atol=1e-6)
+    a, m = W.masked_sum(500, seed=2)
+    assert np.isclose(k_masked_if(a, m), PL.masked_sum_if(a, m), rtol=1e-5)
+    As, B = W.spmm(50, 4, 64, 16, seed=3)
+    y2 = np.empty((50, 16), np.float32)
+    k_spmm(As.data, As.indptr, As.indices, B, y2, 50)
+    assert np.allclose(y2, PL.spmm(As.data, As.indptr, As.indices, B, np.empty((50, 16), np.float32), 50),
+                       rtol=1e-5, atol=1e-6)
+
+
+def test_autotuner_preserves_results():
+    @appy.jit(autotune=True)
+    def saxpy_inplace(alpha, x, y):
+        #pragma parallel for simd
+        for i in range(x.shape[0]):
+            y[i] = y[i] + alpha * x[i]
+
+    n = 1 << 18
+    x = np.ones(n, np.float32)
+    y = np.full(n, 2.0, np.float32)
+    saxpy_inplace(3.0, x, y)          # tuning runs the kernel repeatedly; y must be updated exactly once
+    assert np.all(y == 5.0)
+    saxpy_inplace(3.0, x, y)
+    assert np.all(y == 8.0)
+
+
+def test_kernel_cache_is_reused():
+    from appy_b200.backends.cuda_sm100 import codegen as cg
+    a, b = W.vec_add(1000)
+    c = np.empty_like(a)
+    k_vec_add(a, b, c)
+    n_entries = len(cg.code_cache)
+    k_vec_add(a, b, c)
+    assert len(cg.code_cache) == n_entries
