@@ -51,23 +51,40 @@ def _is_torch(v) -> bool:
     return t is not None and isinstance(v, t.Tensor)
 
 
+_SIMPLE_KINDS = {bool: ("S", "bool"), int: ("S", "pyint"), float: ("S", "pyfloat"), np.bool_: ("S", "bool"),
+                 _types.ModuleType: ("M",)}
+
+
 def _kind_of(v) -> tuple:
-    """Signature entry of one argument: decides which kernel source is generated."""
-    if isinstance(v, _types.ModuleType):
-        return ("M",)
-    if _is_numpy(v):
-        return ("A", "np", str(v.dtype), v.ndim)
+    """Signature entry of one argument: decides which kernel source is generated.
+    Arrays: ("A", where, dtype object, rank); scalars: ("S", kind); modules: ("M",)."""
+    t = type(v)
+    k = _SIMPLE_KINDS.get(t)
+    if k is not None:
+        return k
+    if t is np.ndarray:
+        return ("A", "np", v.dtype, v.ndim)
     if _is_torch(v):
-        return ("A", v.device.type, str(v.dtype), v.ndim)
-    if isinstance(v, (bool, np.bool_)):
+        return ("A", v.device.type, v.dtype, v.ndim)
+    if isinstance(v, np.ndarray):
+        return ("A", "np", v.dtype, v.ndim)
+    if isinstance(v, np.generic):
+        return ("S", str(v.dtype))
+    if isinstance(v, bool):
         return ("S", "bool")
     if isinstance(v, int):
         return ("S", "pyint")
     if isinstance(v, float):
         return ("S", "pyfloat")
-    if isinstance(v, np.generic):
-        return ("S", str(v.dtype))
+    if isinstance(v, _types.ModuleType):
+        return ("M",)
     raise TypeError(f"Unsupported argument of type {type(v).__name__} in a parallel loop")
+
+
+def _elem_type(dtype):
+    if isinstance(dtype, np.dtype):
+        return T.from_numpy(dtype)
+    return T.from_torch(dtype)
 
 
 def _scalar_type(kind: str):
@@ -112,6 +129,14 @@ def _tune_save() -> None:
         pass
 
 
+def _torch_stream(torch, device: int) -> int:
+    """Raw handle of torch's current stream (kernels on CUDA tensors must order with torch)."""
+    try:
+        return torch._C._cuda_getCurrentRawStream(device)
+    except AttributeError:
+        return torch.cuda.current_stream().cuda_stream
+
+
 class _Array:
     """One array argument resolved for a launch."""
     __slots__ = ("name", "obj", "host", "dptr", "nbytes", "shape", "strides", "itemsize", "tmp", "hptr")
@@ -150,6 +175,8 @@ class CompiledLoop:
         self.ir = normalize(loop_source, lambda nm: ndims.get(nm))
         self.stored = stored_arrays([self.ir.loop])
         self.last_variant: Variant | None = None
+        self.last_source: str | None = None
+        self.memo: dict = {}
         self.device = None
         self.sm_count = 148
 
@@ -244,9 +271,8 @@ class CompiledLoop:
                 infos.append(ArgInfo(name, "scalar", _scalar_type(sig[1])))
             else:
                 a = by_name[name]
-                dt = np.dtype(sig[2].replace("torch.", "")) if sig[1] != "np" else np.dtype(sig[2])
                 aligned, unit_last, vec = flags[name]
-                infos.append(ArgInfo(name, "array", T.from_numpy(dt), len(a.shape), unit_last, aligned,
+                infos.append(ArgInfo(name, "array", _elem_type(sig[2]), len(a.shape), unit_last, aligned,
                                      dict(zip((2, 4, 8, 16), vec)), a.itemsize))
         opts = dict(self.options)
         opts["_noalias"] = key[1]
@@ -260,6 +286,7 @@ class CompiledLoop:
             plan.info["nvrtc"] = ["--fmad=true"]
         v = Variant(plan)
         self.variants[key] = v
+        self.last_source = plan.source
         return v
 
     # ------------------------------------------------------------------ launch
@@ -386,6 +413,20 @@ class CompiledLoop:
         store[tkey] = best
         _tune_save()
 
+    def _memo_key(self, args):
+        key = []
+        for sig, v in zip(self.arg_sigs, args):
+            if sig[0] == "A":
+                if sig[1] == "cuda":
+                    key.append((v.data_ptr(), v.shape, v.stride()))
+                elif sig[1] == "np":
+                    key.append((v.__array_interface__["data"][0], v.shape, v.strides))
+                else:
+                    key.append((v.data_ptr(), v.shape, v.stride()))
+            else:
+                key.append(v)
+        return tuple(key)
+
     def __call__(self, *args):
         if len(args) != len(self.arg_names):
             raise TypeError(f"{self.loop_name} expects {len(self.arg_names)} arguments, got {len(args)}")
@@ -396,11 +437,21 @@ class CompiledLoop:
             self.device = torch.cuda.current_device() if (torch is not None and torch.cuda.is_initialized()) else 0
             rt.init(self.device)
             self.sm_count = rt.device_info(self.device)["sm_count"]
+        mkey = self._memo_key(args)
+        memo = self.memo.get(mkey)
+        if memo is not None and not memo[5]:
+            # everything lives on the device and this exact call was seen before: launch straight away
+            handle, grid, block, smem, pack, _any_host = memo
+            torch = sys.modules.get("torch")
+            stream = _torch_stream(torch, self.device) if torch is not None else rt.stream(0)
+            if grid:
+                rt.launch(handle, grid, block, pack, smem, stream)
+            return
         arrays = self._resolve_arrays(args)
         any_host = any(a.host for a in arrays)
         torch = sys.modules.get("torch")
         if torch is not None and any(not a.host for a in arrays):
-            stream = torch.cuda.current_stream().cuda_stream
+            stream = _torch_stream(torch, self.device)
         else:
             stream = rt.stream(0)
         self._acquire_device(arrays, stream)
@@ -419,6 +470,12 @@ class CompiledLoop:
             h = variant.handle(variant.tun)
             grid, block, smem = variant.plan.launch_config(variant.tun, hi - lo, self.sm_count)
             rt.launch(h, grid, block, pack, smem, stream)
+            if not any_host and not variant.plan.uses_ws:
+                if len(self.memo) > 256:
+                    self.memo.clear()
+                self.memo[mkey] = (h, grid, block, smem, pack, False)
+        elif not any_host:
+            self.memo[mkey] = (0, 0, 0, 0, None, False)
         if any_host:
             for a in arrays:
                 if a.host and a.name in self.stored and a.nbytes:
@@ -467,17 +524,19 @@ _OPTION_KEYS = ("ordered_reduction", "fp_contract", "autotune", "pin_host", "_ge
 
 def codegen(loop_source: str, loop_name: str, val_map: dict, options: dict):
     """Backend plugin entry (see module docstring)."""
-    names = list(val_map)
-    signature = tuple(_kind_of(v) for v in val_map.values())
-    opt_key = tuple((k, options.get(k)) for k in _OPTION_KEYS if k in options)
-    cache_key = (loop_source, loop_name, tuple(names), signature, opt_key)
+    names = tuple(val_map)
+    signature = tuple([_kind_of(v) for v in val_map.values()])
+    opt_key = tuple([options.get(k) for k in _OPTION_KEYS])
+    cache_key = (loop_source, loop_name, names, signature, opt_key)
     entry = code_cache.get(cache_key)
     fresh = entry is None
     if fresh:
-        entry = CompiledLoop(loop_source, loop_name, names, signature, options)
+        entry = CompiledLoop(loop_source, loop_name, list(names), signature, options)
         code_cache[cache_key] = entry
-    args = [v for v in val_map.values() if not isinstance(v, _types.ModuleType)]
-    code_src = entry.source_for(*args)
+    code_src = entry.last_source
+    if code_src is None:
+        args = [v for v in val_map.values() if not isinstance(v, _types.ModuleType)]
+        code_src = entry.source_for(*args)
     if fresh and (options.get("dump_code") or options.get("dump_code_to_file")):
         if options.get("dump_code"):
             pretty_dump(code_src, loop_name)

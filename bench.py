@@ -1,0 +1,463 @@
+"""Benchmark of the generated-kernel path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-table]
+
+Headline workload (config C2): the two shared-scalar reductions over n = 2**26 float32
+elements — (a) ``b += a[i]`` and (b) ``b += a[i] if mask[i] else 0.0`` with a
+Bernoulli(0.5) bool mask — run through ``@appy_b200.jit``.  A step is one pass of (a)
+and one of (b).  ``value`` is effective HBM GB/s: algorithmic bytes (4n + 5n per step
+and GPU) divided by the device time of K steps, inputs resident in HBM, all GPUs
+summed (weak scaling: every rank owns a full-size shard; for N > 1 the two result
+scalars are combined by an NCCL all-reduce inside the timed region).  ``e2e`` is the
+same metric through the public API with NumPy host buffers: host-to-device copies of
+the inputs and the device-to-host read of the result are inside the timed region.
+``kernels`` adds one line per benchmark configuration (C1..C5) with the kernel's own
+duration, GB/s and fraction of the measured copy bandwidth.
+
+With ``--impl reference`` the same loops are timed on the host cores with the CPU
+port of the oracle (OpenMP, all cores) on a bounded sample; rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_HEADLINE = 1 << 26
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx.append(float(parts[1]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     parts[3:7]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out["sm_mhz"] = statistics.median(sm)
+            out["sm_max_mhz"] = max(mx)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# --------------------------------------------------------------------------- jitted loops (the product path)
+def define_loops():
+    import appy_b200 as appy
+    g = {"appy": appy, "np": np}
+    src = '''
+@appy.jit
+def sum_into(a, out):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        out[0] += a[i]
+
+@appy.jit
+def masked_sum_into(a, mask, out):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        out[0] += a[i] if mask[i] else 0.0
+
+@appy.jit
+def vec_sum(a):
+    b = 0.0
+    #pragma parallel for simd shared(b)
+    for i in range(a.shape[0]):
+        b += a[i]
+    return b
+
+@appy.jit
+def masked_sum(a, mask):
+    b = 0.0
+    #pragma parallel for simd shared(b)
+    for i in range(a.shape[0]):
+        b += a[i] if mask[i] else 0.0
+    return b
+
+@appy.jit
+def vec_add(a, b, c):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        c[i] = a[i] + b[i]
+
+@appy.jit
+def spmv(A_data, A_indptr, A_indices, x, y, M):
+    #pragma parallel for
+    for i in range(M):
+        start, end = A_indptr[i], A_indptr[i+1]
+        s = 0.0
+        #pragma simd
+        for j in range(start, end):
+            s += A_data[j] * x[A_indices[j]]
+        y[i] = s
+
+@appy.jit
+def gemv(alpha, A, x, y):
+    #pragma parallel for
+    for i in range(A.shape[0]):
+        yi = 0.0
+        #pragma simd
+        for j in range(A.shape[1]):
+            yi += alpha * A[i, j] * x[j]
+        y[i] = yi
+
+@appy.jit
+def spmm(A_data, A_indptr, A_indices, B, y, M):
+    #pragma parallel for
+    for i in range(M):
+        start, end = A_indptr[i], A_indptr[i+1]
+        y[i, :] = 0
+        for k in range(start, end):
+            y[i, :] += A_data[k] * B[A_indices[k], :]
+'''
+    # the decorator reads the function source with inspect, so the text has to live in a file
+    path = os.path.join(tempfile.gettempdir(), f"appy_bench_loops_{os.getpid()}.py")
+    with open(path, "w") as fh:
+        fh.write("import numpy as np\nimport appy_b200 as appy\n" + src)
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("appy_bench_loops", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def time_kernel(torch, fn, rot: int, iters: int, warm: int = 3):
+    """Average device time (us) of one call of fn(i), with CUDA events on the current stream."""
+    for i in range(warm):
+        fn(i % rot)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i % rot)
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
+def kernel_table(torch, L, peak, rank, quick=False):
+    """Per-configuration device timings through the jit path (device-resident inputs)."""
+    from appy_b200 import workloads as W
+    rows = {}
+    dev = "cuda"
+
+    def add(name, byts, us, extra=None):
+        rows[name] = {"us": round(us, 2), "gbs": round(byts / us / 1e3, 1), "frac": round(byts / us / 1e3 / peak, 4),
+                      "bytes": int(byts)}
+        if extra:
+            rows[name].update(extra)
+
+    # C1: 201 MB working set is close to the L2 size -> rotate 4 buffer sets
+    n = 1 << 24
+    a, b = W.vec_add(n, seed=rank)
+    sets = [(torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev), torch.empty(n, device=dev)) for _ in range(4)]
+    add("C1 vec_add f32 n=2^24", W.bytes_vec_add(n),
+        time_kernel(torch, lambda i: L.vec_add(*sets[i]), 4, 40), {"l2": "4 rotating buffer sets"})
+    assert np.array_equal(sets[0][2].cpu().numpy(), a + b)
+    del sets
+    # C4
+    al, A, x = W.gemv(16384, seed=rank)
+    dA, dx, dy = torch.from_numpy(A).to(dev), torch.from_numpy(x).to(dev), torch.empty(16384, device=dev)
+    add("C4 gemv f32 16384x16384", W.bytes_gemv(16384, 16384),
+        time_kernel(torch, lambda i: L.gemv(1.0, dA, dx, dy), 1, 20), {"l2": "1 GiB input"})
+    del dA
+    if quick:
+        return rows
+    # C3 (two row-length distributions); 147 MB working set -> rotate y only is not enough: rotate 2 full copies
+    for kind in ("poisson", "zipf"):
+        Am, xv = W.spmv(kind=kind, seed=rank)
+        sets = []
+        for _ in range(2):
+            sets.append([torch.from_numpy(v).to(dev) for v in (Am.data, Am.indptr, Am.indices, xv)] +
+                        [torch.empty(Am.shape[0], device=dev)])
+        byts = W.bytes_spmv(Am.shape[0], Am.shape[1], Am.nnz)
+        M = Am.shape[0]
+        add(f"C3 spmv {kind} M=2^20 nnz={Am.nnz}", byts,
+            time_kernel(torch, lambda i: L.spmv(sets[i][0], sets[i][1], sets[i][2], sets[i][3], sets[i][4], M), 2, 40),
+            {"l2": "2 rotating copies"})
+        del sets
+    # C5
+    Am, B = W.spmm(seed=rank)
+    d = [torch.from_numpy(v).to(dev) for v in (Am.data, Am.indptr, Am.indices, B)]
+    Cm = torch.empty((Am.shape[0], B.shape[1]), device=dev)
+    b1, b2 = W.bytes_spmm(Am.shape[0], B.shape[0], Am.nnz, B.shape[1])
+    M = Am.shape[0]
+    us = time_kernel(torch, lambda i: L.spmm(d[0], d[1], d[2], d[3], Cm, M), 1, 10)
+    add(f"C5 spmm M=2^18 nnz={Am.nnz} B=2^18x128", b1, us,
+        {"gather_bytes": int(b2), "gather_gbs": round(b2 / us / 1e3, 1), "l2": "403 MB working set"})
+    return rows
+
+
+# --------------------------------------------------------------------------- CPU arms
+def cpu_port_numbers(n_sample: int, reps: int):
+    """Oracle C port (OpenMP) of the two headline loops on a bounded sample."""
+    from appy_b200 import workloads as W
+    from oracle import c_loops
+    a, m = W.masked_sum(n_sample, seed=0)
+    c_loops.vec_sum(a)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        c_loops.vec_sum(a)
+        c_loops.masked_sum(a, m)
+    dt = (time.perf_counter() - t0) / reps
+    byts = 9 * n_sample
+    return byts / dt / 1e9, dt, c_loops.threads()
+
+
+def python_loop_number(n_sample: int):
+    """The reference's literal CPU execution: the undecorated Python loops."""
+    from appy_b200 import workloads as W
+    from oracle import python_loops as PL
+    a, m = W.masked_sum(n_sample, seed=0)
+    t0 = time.perf_counter()
+    PL.vec_sum(a)
+    PL.masked_sum_ternary(a, m)
+    dt = time.perf_counter() - t0
+    return 9 * n_sample / dt / 1e9, dt
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    n_sample = 1 << 24
+    for _ in range(max(args.warmup, 1)):
+        cpu_port_numbers(n_sample, 1)
+    t0 = time.perf_counter()
+    gbs, dt, threads = cpu_port_numbers(n_sample, args.steps)
+    py_gbs, py_dt = python_loop_number(1 << 20)
+    line = {
+        "impl": "reference", "metric": "effective HBM GB/s of the generated-kernel path (shared-scalar reductions)",
+        "value": round(gbs, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 data, f64 accumulate", "data": "synthetic",
+        "config": {"workload": "C2 shared-scalar reductions: (a) sum, (b) masked sum (Bernoulli 0.5 bool mask), "
+                               f"f32, n={N_HEADLINE} per GPU, host cores; each step a sample of n=2^24 per loop"},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"oracle/loops.c with OpenMP on n=2^24 of 2^26 elements per loop, {args.steps} "
+                                   f"passes; the interpreted Python loops (the reference's own CPU execution) reach "
+                                   f"{py_gbs:.5f} GB/s on n=2^20 on 1 core"},
+        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- main arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="appy_b200")
+    ap.add_argument("--no-table", action="store_true")
+    ap.add_argument("--quick-table", action="store_true")
+    ap.add_argument("--n", type=int, default=N_HEADLINE)
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from appy_b200 import workloads as W
+    from appy_b200.backends.cuda_sm100 import runtime as rt
+    rt.init(local_rank)
+    L = define_loops()
+    peak, peak_src = measured_peak()
+    n = args.n
+
+    a_h, m_h = W.masked_sum(n, seed=rank)
+    a = torch.from_numpy(a_h).cuda()
+    m = torch.from_numpy(m_h).cuda()
+    out = torch.zeros(2, dtype=torch.float64, device="cuda")
+    out_a, out_b = out[0:1], out[1:2]
+
+    def step():
+        L.sum_into(a, out_a)
+        L.masked_sum_into(a, m, out_b)
+        if world > 1:
+            dist.all_reduce(out)
+
+    for _ in range(args.warmup):
+        out.zero_()
+        step()
+    torch.cuda.synchronize()
+    # parity of the warm-up result (rank-local part is checked before the all-reduce mixes ranks)
+    out.zero_()
+    L.sum_into(a, out_a)
+    L.masked_sum_into(a, m, out_b)
+    got = out.cpu().numpy()
+    ref = [float(np.sum(a_h, dtype=np.float64)), float(np.sum(a_h[m_h], dtype=np.float64))]
+    assert np.allclose(got, ref, rtol=1e-5, atol=0), (got, ref)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    out.zero_()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches0 = rt.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    launches = rt.launch_count() - launches0
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    # keep the clocks sampler running through the per-kernel timings as well
+    bytes_step = (W.bytes_sum(n) + W.bytes_masked_sum(n)) * world
+    value = bytes_step * args.steps / (ms * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel, timed alone on the launch stream
+    us_sum = time_kernel(torch, lambda i: L.sum_into(a, out_a), 1, 100)
+    us_msk = time_kernel(torch, lambda i: L.masked_sum_into(a, m, out_b), 1, 100)
+    dom_bytes, dom_us, dom_name = (W.bytes_masked_sum(n), us_msk, "masked sum (T2 reduction template)") \
+        if us_msk >= us_sum else (W.bytes_sum(n), us_sum, "sum (T2 reduction template)")
+    achieved = dom_bytes / dom_us / 1e3
+    clocks = sampler.stop() if rank == 0 else {}
+
+    # ---- e2e: NumPy host buffers through the public API, copies inside the timed region
+    e2e_steps = max(3, min(10, args.steps))
+    L.vec_sum(a_h); L.masked_sum(a_h, m_h); L.vec_sum(a_h); L.masked_sum(a_h, m_h)   # mirrors + pinning settle
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        r1 = L.vec_sum(a_h)
+        r2 = L.masked_sum(a_h, m_h)
+    e2e_s = time.perf_counter() - t0
+    assert np.isclose(r1, ref[0], rtol=1e-5) and np.isclose(r2, ref[1], rtol=1e-5)
+    te = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_s = float(te.item())
+    e2e_val = bytes_step * e2e_steps / e2e_s / 1e9
+    h2d = 2 * a_h.nbytes + m_h.nbytes + 16
+    d2h = 16
+
+    table = {}
+    if not args.no_table:
+        table = kernel_table(torch, L, peak, rank, quick=args.quick_table)
+        table["C2a sum f32 n=2^26"] = {"us": round(us_sum, 2), "gbs": round(W.bytes_sum(n) / us_sum / 1e3, 1),
+                                       "frac": round(W.bytes_sum(n) / us_sum / 1e3 / peak, 4),
+                                       "bytes": W.bytes_sum(n), "l2": "256 MiB input"}
+        table["C2b masked sum f32+bool n=2^26"] = {"us": round(us_msk, 2),
+                                                   "gbs": round(W.bytes_masked_sum(n) / us_msk / 1e3, 1),
+                                                   "frac": round(W.bytes_masked_sum(n) / us_msk / 1e3 / peak, 4),
+                                                   "bytes": W.bytes_masked_sum(n), "l2": "320 MiB input"}
+
+    cpu = None
+    if rank == 0 and world == 1:
+        gbs, dt, threads = cpu_port_numbers(1 << 24, 20)
+        cpu = {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+               "sample": "oracle/loops.c (OpenMP) on n=2^24 of the 2^26 elements per loop, 20 passes"}
+
+    if rank == 0:
+        line = {
+            "metric": "effective HBM GB/s of the generated-kernel path (shared-scalar reductions)",
+            "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 data, f64 accumulate", "data": "synthetic",
+            "config": {"workload": "C2 shared-scalar reductions: (a) sum, (b) masked sum (Bernoulli 0.5 bool mask), "
+                                   f"f32, n={n} per GPU, through @appy_b200.jit",
+                       "l2": "inputs larger than L2 (256 MiB + 64 MiB read per step)",
+                       "collective": "NCCL all-reduce of the two result scalars per step" if world > 1 else "none"},
+            "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": round(achieved, 1), "peak": peak,
+                         "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
+                         "peak_source": f"{peak_src} copy bandwidth", "us_per_launch": round(dom_us, 2),
+                         "algorithmic_bytes": dom_bytes},
+            "cpu_baseline": cpu,
+            "e2e": {"value": round(e2e_val, 3), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "kernels": table,
+        }
+        traffic = os.path.join(ROOT, "profiles", "traffic.json")
+        try:
+            with open(traffic) as fh:
+                line["roofline"]["traffic"] = json.load(fh).get(dom_name.split(" (")[0])
+        except Exception:
+            pass
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
