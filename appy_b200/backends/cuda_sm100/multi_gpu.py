@@ -1,0 +1,61 @@
+"""Splitting an annotated loop across the GPUs of one box (one process per GPU).
+
+The reference is single-GPU.  Here the outermost parallel-for range is cut into
+contiguous pieces, one per rank: by iteration count for dense loops and by non-zero
+count for CSR row loops.  Arrays indexed by the outer index are sharded along it, gathered
+operands are replicated, and only ``shared(...)`` scalars are combined across ranks, with
+an all-reduce over ``torch.distributed`` (NCCL for CUDA tensors, gloo for CPU tensors).
+No kernel reads a peer's memory.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import runtime as rt
+
+
+def world():
+    """(rank, world_size) of the current process; (0, 1) when torch.distributed is not initialised."""
+    try:
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized():
+            return dist.get_rank(), dist.get_world_size()
+    except ImportError:
+        pass
+    return 0, 1
+
+
+def split_range(lo: int, hi: int, world_size: int, rank: int, align: int = 32):
+    """This rank's contiguous piece [lo_r, hi_r) of [lo, hi); inner cut points are multiples of
+    `align` so that 16-byte vector accesses stay aligned on every rank."""
+    b = rt.partition_range(lo, hi, world_size, align)
+    return b[rank], b[rank + 1]
+
+
+def split_rows(indptr, world_size: int, rank: int):
+    """This rank's contiguous row range of a CSR matrix, balanced by non-zero count."""
+    b = rt.partition_rows(np.asarray(indptr), world_size)
+    return b[rank], b[rank + 1]
+
+
+def shard_csr(data, indptr, indices, world_size: int, rank: int):
+    """Local CSR pieces for this rank: (data_r, indptr_r rebased to 0, indices_r, row_lo, row_hi).
+    Works on NumPy arrays and on torch tensors (indptr must be readable on the host)."""
+    ip = indptr.cpu().numpy() if hasattr(indptr, "cpu") else np.asarray(indptr)
+    r0, r1 = split_rows(ip, world_size, rank)
+    k0, k1 = int(ip[r0]), int(ip[r1])
+    indptr_r = indptr[r0:r1 + 1] - indptr[r0]
+    return data[k0:k1], indptr_r, indices[k0:k1], r0, r1
+
+
+def all_reduce(values, op: str = "+"):
+    """Combine per-rank partial results of ``shared`` scalars in place (tensor of any length).
+    `op` is one of + * max min, the reduction operators the front end detects."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return values
+    rop = {"+": dist.ReduceOp.SUM, "*": dist.ReduceOp.PRODUCT, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}[op]
+    t = values if isinstance(values, torch.Tensor) else torch.from_numpy(np.asarray(values))
+    dist.all_reduce(t, op=rop)
+    return values
