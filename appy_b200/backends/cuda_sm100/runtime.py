@@ -56,6 +56,7 @@ SIGNATURES = {
                                      C.POINTER(C.c_int64), C.c_void_p]),
     "appy_vec_add_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "appy_sum_f32": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_void_p]),
+    "appy_sum_f32_noalloc": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "appy_masked_sum_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int,
                                       C.c_void_p]),
     "appy_spmv_csr_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

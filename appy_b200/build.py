@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libappy_sm100.so")
 STAMP = os.path.join(HERE, "libappy_sm100.stamp")
 
-SOURCES = ["appy_shim.cu", "appy_prebuilt.cu"]
+SOURCES = ["appy_shim.cu", "appy_prebuilt.cu", "appy_noalloc.cu"]
 
 
 def _nvcc() -> str:

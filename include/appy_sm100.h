@@ -151,6 +151,25 @@ int appy_spmm_csr_f32(const float* ddata, const int32_t* dindptr, const int32_t*
                       const float* dB, int64_t ldb, float* dC, int64_t ldc, int64_t row_lo,
                       int64_t row_hi, int ncols, void* stream);
 
+/* ---- allocation-free variant ---------------------------------------------
+ * No counterpart in the reference (it has no native code and allocates through torch).
+ *
+ * Same result as appy_sum_f32(da, n, dresult, 1, stream): *dresult += sum(a[0:n]) with a
+ * float64 accumulator and a commit that does not depend on CTA scheduling — but for
+ * callers that must not allocate device memory where they reduce (inside a memory budget
+ * fixed by a host application, between a pool allocator's sync points, or where the
+ * device-wide synchronisation of a first-use cudaMalloc is unacceptable).  The scratch
+ * (one ticket + one 8-byte partial per 8192-element tile) is a 128.25 KiB array inside the
+ * library image, present on every GPU that loads the library.
+ *   - n may not exceed 134,217,728 elements (16384 tiles) for a 16-byte aligned `da`, a
+ *     quarter of that otherwise; longer inputs return APPY_ERR_ARG and launch nothing;
+ *   - the first call on a device looks up the array's device address; make it before any
+ *     stream capture begins;
+ *   - all calls share the array: calls that can overlap on the GPU race, so keep them
+ *     ordered (one stream, or events between streams);
+ *   - no cudaMalloc / cudaFree / allocating library routine is called. */
+int appy_sum_f32_noalloc(const float* da, int64_t n, double* dresult, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
