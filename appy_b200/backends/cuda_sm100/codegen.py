@@ -165,6 +165,8 @@ class CompiledLoop:
     def __init__(self, loop_source: str, loop_name: str, names: list, signature: tuple, options: dict):
         self.loop_source = loop_source
         self.loop_name = loop_name
+        fn = options.get("_fn")
+        self.kernel_name = f"{fn}_{loop_name}" if fn and str(fn).isidentifier() else loop_name
         self.names = names                  # val_map names, modules included
         self.signature = signature
         self.options = dict(options)
@@ -279,7 +281,7 @@ class CompiledLoop:
         opts["_shape"] = {(n, 1): s for n, s in key[2]}
         import copy as _copy
         ir = _copy.deepcopy(self.ir)
-        plan = Lowering(ir, self.loop_name, infos, opts).lower()
+        plan = Lowering(ir, self.kernel_name, infos, opts).lower()
         if self.options.get("fp_contract", "numpy") == "numpy":
             plan.info["nvrtc"] = ["--fmad=false", "--prec-div=true", "--prec-sqrt=true", "--ftz=false"]
         else:
@@ -527,7 +529,7 @@ def codegen(loop_source: str, loop_name: str, val_map: dict, options: dict):
     names = tuple(val_map)
     signature = tuple([_kind_of(v) for v in val_map.values()])
     opt_key = tuple([options.get(k) for k in _OPTION_KEYS])
-    cache_key = (loop_source, loop_name, names, signature, opt_key)
+    cache_key = (loop_source, loop_name, names, signature, opt_key, options.get("_fn"))
     entry = code_cache.get(cache_key)
     fresh = entry is None
     if fresh:

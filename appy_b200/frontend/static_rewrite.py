@@ -93,8 +93,10 @@ def _shared_names(pragma: str) -> list[str]:
 
 
 class _Rewriter:
-    def __init__(self, options: dict):
-        self.options = options
+    def __init__(self, options: dict, fn_name: str = ""):
+        self.options = dict(options)
+        if fn_name:
+            self.options["_fn"] = fn_name      # names the CUDA kernel after the function (profilers)
         self.counter = 0
 
     def _stub(self, loop_source: str, loop_name: str) -> ast.Expr:
@@ -160,9 +162,9 @@ def rewrite_function_source(source: str, options: dict) -> str:
     for node in ast.walk(tree):
         if isinstance(node, (ast.FunctionDef, ast.AsyncFunctionDef)):
             node.decorator_list = []
-    rw = _Rewriter(options)
     for node in tree.body:
         if isinstance(node, (ast.FunctionDef, ast.AsyncFunctionDef)):
+            rw = _Rewriter(options, node.name)
             node.body = rw.rewrite_block(node.body) or [ast.Pass()]
     ast.fix_missing_locations(tree)
     return pragma_ast.unparse(tree)

@@ -300,6 +300,61 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_only(args):
+    """One configuration, device-resident inputs, --warmup + --steps launches through the jit path."""
+    import torch
+    from appy_b200 import workloads as W
+    from appy_b200.backends.cuda_sm100 import runtime as rt
+    torch.cuda.set_device(0)
+    rt.init(0)
+    L = define_loops()
+    k, sc = args.only, max(1, args.scale)
+    dev = "cuda"
+    if k == "vec_add":
+        n = (1 << 24) // sc
+        a, b = W.vec_add(n)
+        d = (torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev), torch.empty(n, device=dev))
+        fn, byts = (lambda: L.vec_add(*d)), W.bytes_vec_add(n)
+    elif k in ("sum", "masked_sum"):
+        n = (1 << 26) // sc
+        a, m = W.masked_sum(n)
+        da, dm = torch.from_numpy(a).to(dev), torch.from_numpy(m).to(dev)
+        out = torch.zeros(1, dtype=torch.float64, device=dev)
+        fn = (lambda: L.sum_into(da, out)) if k == "sum" else (lambda: L.masked_sum_into(da, dm, out))
+        byts = W.bytes_sum(n) if k == "sum" else W.bytes_masked_sum(n)
+    elif k == "gemv":
+        n = 16384 // sc
+        _al, A, x = W.gemv(n)
+        dA, dx, dy = torch.from_numpy(A).to(dev), torch.from_numpy(x).to(dev), torch.empty(n, device=dev)
+        fn, byts = (lambda: L.gemv(1.0, dA, dx, dy)), W.bytes_gemv(n, n)
+    elif k in ("spmv_poisson", "spmv_zipf"):
+        Am, xv = W.spmv((1 << 20) // sc, kind=k.split("_")[1])
+        d = [torch.from_numpy(v).to(dev) for v in (Am.data, Am.indptr, Am.indices, xv)]
+        dy = torch.empty(Am.shape[0], device=dev)
+        M = Am.shape[0]
+        fn, byts = (lambda: L.spmv(d[0], d[1], d[2], d[3], dy, M)), W.bytes_spmv(M, M, Am.nnz)
+    elif k == "spmm":
+        Am, B = W.spmm((1 << 18) // sc)
+        d = [torch.from_numpy(v).to(dev) for v in (Am.data, Am.indptr, Am.indices, B)]
+        Cm = torch.empty((Am.shape[0], B.shape[1]), device=dev)
+        M = Am.shape[0]
+        fn, byts = (lambda: L.spmm(d[0], d[1], d[2], d[3], Cm, M)), W.bytes_spmm(M, M, Am.nnz, B.shape[1])[0]
+    else:
+        raise SystemExit(f"unknown --only {k}")
+    for _ in range(max(args.warmup, 1)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    e1.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    print(json.dumps({"only": k, "scale": sc, "us_per_launch": round(us, 2), "algorithmic_bytes": int(byts),
+                      "gbs": round(byts / us / 1e3, 1)}), flush=True)
+
+
 # --------------------------------------------------------------------------- main arm
 def main():
     ap = argparse.ArgumentParser()
@@ -310,12 +365,19 @@ def main():
     ap.add_argument("--no-table", action="store_true")
     ap.add_argument("--quick-table", action="store_true")
     ap.add_argument("--n", type=int, default=N_HEADLINE)
+    ap.add_argument("--only", default=None,
+                    help="run a single configuration's kernel --steps times and exit (for profilers): "
+                         "vec_add, sum, masked_sum, gemv, spmv_poisson, spmv_zipf, spmm")
+    ap.add_argument("--scale", type=int, default=1, help="with --only: divide the problem size by this factor")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.only:
+        run_only(args)
         return
     args.warmup = max(args.warmup, 3)
 

@@ -55,6 +55,7 @@ def f(a, n):
     return s
 '''
     out = rewrite_function_source(src, {"backend": None})
+    assert "'_fn': 'f'" in out
     assert "@appy.jit" not in out
     assert "a_shape_0 = a.shape[0]" in out
     assert "s = numpy.array([s])" in out and "s = s.item()" in out
