@@ -197,11 +197,34 @@ def time_kernel(torch, fn, rot: int, iters: int, warm: int = 3):
     return e0.elapsed_time(e1) * 1e3 / iters
 
 
-def kernel_table(torch, L, peak, rank, quick=False):
+def _triton_arm():
+    """The reference's generated Triton kernels, restated in baseline/triton_kernels.py."""
+    try:
+        from baseline import triton_kernels as TK
+        return TK
+    except Exception as e:      # Triton missing or unable to compile here: the column is left out
+        sys.stderr.write(f"[bench] Triton reference arm unavailable: {e!r}\n")
+        return None
+
+
+def kernel_table(torch, L, peak, rank, quick=False, with_triton=True):
     """Per-configuration device timings through the jit path (device-resident inputs)."""
     from appy_b200 import workloads as W
     rows = {}
     dev = "cuda"
+    TK = _triton_arm() if with_triton else None
+
+    def tri(name, byts, fn, rot, iters):
+        if TK is None:
+            return
+        try:
+            us = time_kernel(torch, fn, rot, iters, warm=2)
+            rows[name]["triton_us"] = round(us, 2)
+            rows[name]["triton_gbs"] = round(byts / us / 1e3, 1)
+            rows[name]["speedup_vs_triton"] = round(us / rows[name]["us"], 2)
+        except Exception as e:
+            rows[name]["triton_us"] = None
+            sys.stderr.write(f"[bench] Triton kernel for {name} failed: {e!r}\n")
 
     def add(name, byts, us, extra=None):
         rows[name] = {"us": round(us, 2), "gbs": round(byts / us / 1e3, 1), "frac": round(byts / us / 1e3 / peak, 4),
@@ -216,12 +239,14 @@ def kernel_table(torch, L, peak, rank, quick=False):
     add("C1 vec_add f32 n=2^24", W.bytes_vec_add(n),
         time_kernel(torch, lambda i: L.vec_add(*sets[i]), 4, 40), {"l2": "4 rotating buffer sets"})
     assert np.array_equal(sets[0][2].cpu().numpy(), a + b)
+    tri("C1 vec_add f32 n=2^24", W.bytes_vec_add(n), lambda i: TK.vec_add(*sets[i]), 4, 40)
     del sets
     # C4
     al, A, x = W.gemv(16384, seed=rank)
     dA, dx, dy = torch.from_numpy(A).to(dev), torch.from_numpy(x).to(dev), torch.empty(16384, device=dev)
     add("C4 gemv f32 16384x16384", W.bytes_gemv(16384, 16384),
         time_kernel(torch, lambda i: L.gemv(1.0, dA, dx, dy), 1, 20), {"l2": "1 GiB input"})
+    tri("C4 gemv f32 16384x16384", W.bytes_gemv(16384, 16384), lambda i: TK.gemv(1.0, dA, dx, dy), 1, 5)
     del dA
     if quick:
         return rows
@@ -237,6 +262,8 @@ def kernel_table(torch, L, peak, rank, quick=False):
         add(f"C3 spmv {kind} M=2^20 nnz={Am.nnz}", byts,
             time_kernel(torch, lambda i: L.spmv(sets[i][0], sets[i][1], sets[i][2], sets[i][3], sets[i][4], M), 2, 40),
             {"l2": "2 rotating copies"})
+        tri(f"C3 spmv {kind} M=2^20 nnz={Am.nnz}", byts,
+            lambda i: TK.spmv(sets[i][0], sets[i][1], sets[i][2], sets[i][3], sets[i][4], M), 2, 6)
         del sets
     # C5
     Am, B = W.spmm(seed=rank)
@@ -247,6 +274,7 @@ def kernel_table(torch, L, peak, rank, quick=False):
     us = time_kernel(torch, lambda i: L.spmm(d[0], d[1], d[2], d[3], Cm, M), 1, 10)
     add(f"C5 spmm M=2^18 nnz={Am.nnz} B=2^18x128", b1, us,
         {"gather_bytes": int(b2), "gather_gbs": round(b2 / us / 1e3, 1), "l2": "403 MB working set"})
+    tri(f"C5 spmm M=2^18 nnz={Am.nnz} B=2^18x128", b1, lambda i: TK.spmm(d[0], d[1], d[2], d[3], Cm, M), 1, 2)
     return rows
 
 
@@ -403,15 +431,24 @@ def main():
     out = torch.zeros(2, dtype=torch.float64, device="cuda")
     out_a, out_b = out[0:1], out[1:2]
 
+    # The two result cells of a step are combined across ranks by one all-reduce, ordered on the
+    # launch stream.  (Overlapping it with the next step's kernels through a second buffer was
+    # measured slower: the reduction kernels occupy every SM, so the NCCL kernel waits for them anyway.)
+    outs = [out]
+
     def step():
+        out.zero_()
         L.sum_into(a, out_a)
         L.masked_sum_into(a, m, out_b)
         if world > 1:
             dist.all_reduce(out)
 
+    def drain():
+        pass
+
     for _ in range(args.warmup):
-        out.zero_()
         step()
+    drain()
     torch.cuda.synchronize()
     # parity of the warm-up result (rank-local part is checked before the all-reduce mixes ranks)
     out.zero_()
@@ -434,12 +471,22 @@ def main():
     e0.record()
     for _ in range(args.steps):
         step()
+    drain()
     e1.record()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     ms = e0.elapsed_time(e1)
     launches = rt.launch_count() - launches0
+    # every rank's last buffers hold the all-reduced sums of the last two steps
+    if world > 1:
+        tot = torch.tensor(ref, dtype=torch.float64, device="cuda")
+        dist.all_reduce(tot)
+        for buf in outs:
+            assert np.allclose(buf.cpu().numpy(), tot.cpu().numpy(), rtol=1e-5, atol=0), (buf, tot)
+    else:
+        for buf in outs:
+            assert np.allclose(buf.cpu().numpy(), ref, rtol=1e-5, atol=0), (buf, ref)
     t = torch.tensor([ms], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -477,7 +524,17 @@ def main():
 
     table = {}
     if not args.no_table:
-        table = kernel_table(torch, L, peak, rank, quick=args.quick_table)
+        table = kernel_table(torch, L, peak, rank, quick=args.quick_table, with_triton=(rank == 0))
+        TK = _triton_arm() if rank == 0 else None
+        tri_sum = tri_msk = tri_if = None
+        if TK is not None:
+            try:
+                tb = torch.zeros(1, dtype=torch.float64, device="cuda")
+                tri_sum = time_kernel(torch, lambda i: TK.vec_sum(a, tb), 1, 5, warm=2)
+                tri_msk = time_kernel(torch, lambda i: TK.masked_sum_ternary(a, m, tb), 1, 5, warm=2)
+                tri_if = time_kernel(torch, lambda i: TK.masked_sum_if(a, m, tb), 1, 2, warm=1)
+            except Exception as e:
+                sys.stderr.write(f"[bench] Triton reduction kernels failed: {e!r}\n")
         table["C2a sum f32 n=2^26"] = {"us": round(us_sum, 2), "gbs": round(W.bytes_sum(n) / us_sum / 1e3, 1),
                                        "frac": round(W.bytes_sum(n) / us_sum / 1e3 / peak, 4),
                                        "bytes": W.bytes_sum(n), "l2": "256 MiB input"}
@@ -485,6 +542,15 @@ def main():
                                                    "gbs": round(W.bytes_masked_sum(n) / us_msk / 1e3, 1),
                                                    "frac": round(W.bytes_masked_sum(n) / us_msk / 1e3 / peak, 4),
                                                    "bytes": W.bytes_masked_sum(n), "l2": "320 MiB input"}
+        if tri_sum:
+            table["C2a sum f32 n=2^26"].update({"triton_us": round(tri_sum, 2),
+                                                "triton_gbs": round(W.bytes_sum(n) / tri_sum / 1e3, 1),
+                                                "speedup_vs_triton": round(tri_sum / us_sum, 2)})
+        if tri_msk:
+            table["C2b masked sum f32+bool n=2^26"].update({
+                "triton_us": round(tri_msk, 2), "triton_gbs": round(W.bytes_masked_sum(n) / tri_msk / 1e3, 1),
+                "speedup_vs_triton": round(tri_msk / us_msk, 2),
+                "triton_if_form_us": round(tri_if, 2) if tri_if else None})
 
     cpu = None
     if rank == 0 and world == 1:
