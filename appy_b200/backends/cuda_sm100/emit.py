@@ -266,10 +266,11 @@ class Emitter:
             return (f"({a} * {b})", rty)
         if isinstance(op, ast.Div):
             return (f"({a} / {b})", rty)
+        targ = "" if rty.is_float else f"<{rty.strong().c}>"    # integer literals are plain `int` in C
         if isinstance(op, ast.FloorDiv):
-            return (f"appy_floordiv({a}, {b})", rty)
+            return (f"appy_floordiv{targ}({a}, {b})", rty)
         if isinstance(op, ast.Mod):
-            return (f"appy_pymod({a}, {b})", rty)
+            return (f"appy_pymod{targ}({a}, {b})", rty)
         if isinstance(op, ast.Pow):
             if isinstance(node.right, ast.Constant) and node.right.value in (2, 3) and not isinstance(
                     node.right.value, bool):

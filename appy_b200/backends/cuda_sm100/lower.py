@@ -241,10 +241,10 @@ class Lowering:
         sig = ", ".join(self._c_param(p) for p in params)
         lines = [f'extern "C" __global__ void __launch_bounds__({launch_bounds}) {self.name}({sig}) {{',
                  f"  {smem_decl}",
-                 f"  {body_struct} body;"]
+                 f"  {body_struct} __body;"]
         for p in params:
             if p.kind not in ("lo", "hi"):
-                lines.append(f"  body.{p.name} = {p.name};")
+                lines.append(f"  __body.{p.name} = {p.name};")
         lines += ["  " + l for l in extra_init]
         lines += [f"  {call}", "}"]
         return lines
@@ -277,7 +277,7 @@ class Lowering:
         return [f"{ty.c} {acc};" for (_op, ty, acc, _n) in self.reductions.values()]
 
     def _reduction_init(self) -> list[str]:
-        return [f"body.{acc} = {OPS[op]}::id<{ty.c}>();" for (op, ty, acc, _n) in self.reductions.values()]
+        return [f"__body.{acc} = {OPS[op]}::id<{ty.c}>();" for (op, ty, acc, _n) in self.reductions.values()]
 
     def _reduction_finish(self, ordered: bool) -> list[str]:
         if not self.reductions:
@@ -285,7 +285,7 @@ class Lowering:
         out = []
         items = list(self.reductions.values())
         for op, ty, acc, _n in items:
-            out.append(f"{acc} = appy_block_reduce<{OPS[op]}, {ty.c}>({acc}, reinterpret_cast<{ty.c}*>(smem));")
+            out.append(f"{acc} = appy_block_reduce<{OPS[op]}, {ty.c}>({acc}, reinterpret_cast<{ty.c}*>(__smem));")
         em = Emitter(self.env)       # plain addresses of the targets (no overrides)
         addrs = []
         for op, ty, acc, node in items:
@@ -297,13 +297,13 @@ class Lowering:
                 out.append(f"  appy_atomic({OPS[op]}(), {addr}, {acc});")
             out.append("}")
         else:
-            out.append("const appy_ws w = appy_ws_from(__ws);")
+            out.append("const appy_ws __w = appy_ws_from(__ws);")
             for r, (op, ty, acc, _n) in enumerate(items):
-                out.append(f"appy_ws_publish<{ty.c}>(w, {r}, {acc});")
-            out.append("if (appy_ws_arrive(w, smem)) {")
+                out.append(f"appy_ws_publish<{ty.c}>(__w, {r}, {acc});")
+            out.append("if (appy_ws_arrive(__w, __smem)) {")
             for r, ((op, ty, acc, _n), addr) in enumerate(zip(items, addrs)):
-                out.append(f"  {{ const {ty.c} t = appy_ws_collect<{OPS[op]}, {ty.c}>(w, {r}, smem);")
-                out.append(f"    if (threadIdx.x == 0) *{addr} = {OPS[op]}::op<{ty.c}>(*{addr}, t); }}")
+                out.append(f"  {{ const {ty.c} __t = appy_ws_collect<{OPS[op]}, {ty.c}>(__w, {r}, __smem);")
+                out.append(f"    if (threadIdx.x == 0) *{addr} = {OPS[op]}::op<{ty.c}>(*{addr}, __t); }}")
             out.append("}")
         return out
 
@@ -429,31 +429,31 @@ class Lowering:
             off, _ = Emitter(env).offset(_replace_index(node, self.var, "__i0"))
             ld = "appy_ld_cs" if (arr.readonly and self.options.get("_stream_hint", True)) else \
                 ("appy_ld_nc" if arr.readonly else "appy_ld")
-            load_lines.append(f"r.{s} = {ld}<{arr.ty.c}, {V}>({name} + ({off}));")
+            load_lines.append(f"__rg.{s} = {ld}<{arr.ty.c}, {V}>({name} + ({off}));")
         if V > 1:
             saved_l, saved_s = dict(em.load_override), dict(em.store_override)
             for text, s in slot.items():
                 arr = env.arrays[loads[text][0]]
-                em.load_override[text] = (f"r.{s}.v[_k]", arr.ty)
+                em.load_override[text] = (f"__rg.{s}.v[__k]", arr.ty)
             for n_out, (text, (name, node)) in enumerate(stores.items()):
                 arr = env.arrays[name]
                 o = f"o{n_out}"
                 out_decl.append(f"appy_pack<{arr.ty.c}, {V}> {o};")
-                em.store_override[text] = (lambda code, t, o=o, ty=arr.ty: [f"{o}.v[_k] = {cast(code, t, ty)};"])
+                em.store_override[text] = (lambda code, t, o=o, ty=arr.ty: [f"{o}.v[__k] = {cast(code, t, ty)};"])
                 off, _ = Emitter(env).offset(_replace_index(node, self.var, "__i0"))
                 stc = "appy_st_cs" if self.options.get("_stream_hint", True) and name not in loaded_arrays(body) \
                     else "appy_st"
                 out_store.append(f"{stc}<{arr.ty.c}, {V}>({name} + ({off}), {o});")
-            inner = [f"const i64 {self.var} = __i0 + _k;"] + local_decl + [l.strip() for l in em.block(body, "")]
-            compute = ([f"APPY_DEV void compute(i64 __i0, const Regs& r) {{"] + ["  " + l for l in out_decl] +
-                       ["#pragma unroll", f"  for (int _k = 0; _k < {V}; ++_k) {{"] + ["    " + l for l in inner] +
+            inner = [f"const i64 {self.var} = __i0 + __k;"] + local_decl + [l.strip() for l in em.block(body, "")]
+            compute = ([f"APPY_DEV void compute(i64 __i0, const Regs& __rg) {{"] + ["  " + l for l in out_decl] +
+                       ["#pragma unroll", f"  for (int __k = 0; __k < {V}; ++__k) {{"] + ["    " + l for l in inner] +
                        ["  }"] + ["  " + l for l in out_store] + ["}"])
             em.load_override, em.store_override = saved_l, saved_s
-            load_fn = ["APPY_DEV void load(i64 __i0, Regs& r) const {"] + ["  " + l for l in load_lines] + ["}"]
+            load_fn = ["APPY_DEV void load(i64 __i0, Regs& __rg) const {"] + ["  " + l for l in load_lines] + ["}"]
         else:
             compute = [f"APPY_DEV void compute(i64 __i0, const Regs&) {{ one(__i0); }}"]
             load_fn = ["APPY_DEV void load(i64, Regs&) const {}"]
-        finish = ["APPY_DEV void finish(void* smem) {"] + ["  " + l for l in self._reduction_finish(ordered)] + ["}"]
+        finish = ["APPY_DEV void finish(void* __smem) {"] + ["  " + l for l in self._reduction_finish(ordered)] + ["}"]
 
         params = self._params(uses_ws=ordered)
         struct = f"{self.name}_body"
@@ -463,7 +463,7 @@ class Lowering:
         src += ["  struct Regs { " + " ".join(regs) + " };"]
         src += ["  " + l for l in load_fn + compute + one + finish]
         src += ["};"]
-        src += self._kernel_wrapper(params, struct, f"appy_flat<{V}, P_U>(body, __lo, __hi, __smem);",
+        src += self._kernel_wrapper(params, struct, f"appy_flat<{V}, P_U>(__body, __lo, __hi, __smem);",
                                     "__shared__ double __smem[33];", self._reduction_init())
         tun = {"P_BLOCK": [256, 128, 512], "P_U": [1, 2, 4, 8] if V > 1 else [1, 2, 4]}
         if self.reductions:
@@ -495,9 +495,9 @@ class Lowering:
         struct = f"{self.name}_body"
         src = ['#include "t_group.cuh"', f"struct {struct} {{"]
         src += ["  " + m for m in self._members(params)]
-        src += [f"  template <class Grp> APPY_DEV void iter(i64 {self.var}, const Grp& g) {{"]
+        src += [f"  template <class Grp> APPY_DEV void iter(i64 {self.var}, const Grp& __g) {{"]
         src += ["    " + l for l in decl] + lines + ["  }", "};"]
-        src += self._kernel_wrapper(params, struct, "appy_group_rows<P_G>(body, __lo, __hi, __smem);",
+        src += self._kernel_wrapper(params, struct, "appy_group_rows<P_G>(__body, __lo, __hi, __smem);",
                                     "__shared__ double __smem[33];")
         tun = {"P_G": [8, 1, 2, 4, 16, 32, 0], "P_BLOCK": [256, 128, 512]}
         return KernelPlan("group", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr,
@@ -597,7 +597,7 @@ class Lowering:
             smem = ("__shared__ __align__(16) unsigned char __smem[32 * sizeof(" + acc_ty.c +
                     ") + (2 * P_ROWS + 2) * sizeof(int)];")
             call = (f"appy_csr_vector<P_G, P_BLOCK, P_ROWS, P_G * 16, 2048, {ptr.ty.c}>"
-                    f"(body, {csr_ptr}, __lo, __hi, __smem);")
+                    f"(__body, {csr_ptr}, __lo, __hi, __smem);")
             src += self._kernel_wrapper(params, struct, call, smem)
             tun = {"P_G": [4, 2, 8, 1, 16, 32], "P_BLOCK": [256], "P_ROWS": [256, 128, 512]}
             return KernelPlan("csr", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr,
@@ -634,8 +634,8 @@ class Lowering:
             off, _ = Emitter(env).offset(_replace_index(node, jvar, "__j0"))
             big = self.args[node.value.id].ndim > 1
             ld = "appy_ld_cs" if big else "appy_ld_nc"
-            load_lines.append(f"r.l{n_s} = {ld}<{arr.ty.c}, {V}>({node.value.id} + ({off}));")
-            em.load_override[text] = (f"r.l{n_s}.v[_k]", arr.ty)
+            load_lines.append(f"__rg.l{n_s} = {ld}<{arr.ty.c}, {V}>({node.value.id} + ({off}));")
+            em.load_override[text] = (f"__rg.l{n_s}.v[__k]", arr.ty)
         vterm_c, vterm_t = em.expr(term)
         em.load_override = saved
         needs_pre = bool(pre_lines)
@@ -647,11 +647,11 @@ class Lowering:
         src += ["  struct Regs { " + " ".join(regs) + " };"]
         src += [f"  APPY_DEV void bounds(i64 {self.var}, i64& __jlo, i64& __jhi) const {{"] + \
                ["    " + l for l in pre_block] + [f"    __jlo = {lo_c}; __jhi = {hi_c};", "  }"]
-        src += [f"  APPY_DEV void load(i64 {self.var}, i64 __j0, Regs& r) const {{"] + \
+        src += [f"  APPY_DEV void load(i64 {self.var}, i64 __j0, Regs& __rg) const {{"] + \
                ["    " + l for l in pre_block] + ["    " + l for l in load_lines] + ["  }"]
-        src += [f"  APPY_DEV Acc fold(i64 {self.var}, i64 __j0, const Regs& r, Acc __a) const {{"] + \
+        src += [f"  APPY_DEV Acc fold(i64 {self.var}, i64 __j0, const Regs& __rg, Acc __a) const {{"] + \
                ["    " + l for l in pre_block] + \
-               ["#pragma unroll", f"    for (int _k = 0; _k < {V}; ++_k) {{ const i64 {jvar} = __j0 + _k;",
+               ["#pragma unroll", f"    for (int __k = 0; __k < {V}; ++__k) {{ const i64 {jvar} = __j0 + __k;",
                 f"      __a = {opc}::op<Acc>(__a, {cast(vterm_c, vterm_t, acc_ty)}); }}", "    return __a;", "  }"]
         src += [f"  APPY_DEV Acc one(i64 {self.var}, i64 {jvar}, Acc __a) const {{"] + \
                ["    " + l for l in pre_block] + \
@@ -660,7 +660,7 @@ class Lowering:
                ["    " + l for l in pre_block] + \
                [f"    {acc_ty.c} {acc_name} = {opc}::op<Acc>({init_c}, __total);"] + \
                ["    " + l for l in params_decl_suffix] + ["  }", "};"]
-        src += self._kernel_wrapper(params, struct, f"appy_rowdot<P_G, {V}, P_U>(body, __lo, __hi, __smem);",
+        src += self._kernel_wrapper(params, struct, f"appy_rowdot<P_G, {V}, P_U>(__body, __lo, __hi, __smem);",
                                     "__shared__ double __smem[33];")
         tun = {"P_G": [32, 0, 8, 4, 16], "P_BLOCK": [128, 256, 512], "P_U": [4, 2, 8]}
         return KernelPlan("rowdot", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr, vec=V,
@@ -772,13 +772,13 @@ class Lowering:
         src += ["  " + m for m in self._members(params)]
         src += [f"  APPY_DEV Elt coef(i64 {kvar}) const {{ return {coef_c}; }}",
                 f"  APPY_DEV Row brow(i64 {kvar}) const {{ return ({row_ty})({row_c}); }}",
-                f"  APPY_DEV const Elt* brow_ptr(Row r) const {{ return {bname} + (i64)r * {bname}_stride_0; }}",
+                f"  APPY_DEV const Elt* brow_ptr(Row __row) const {{ return {bname} + (i64)__row * {bname}_stride_0; }}",
                 f"  APPY_DEV Elt* crow_ptr(i64 {self.var}) const {{ return {cname} + {self.var} * {cname}_stride_0; }}",
                 f"  APPY_DEV Elt init() const {{ return {init_c}; }}", "};"]
         smem = (f"__shared__ __align__(16) unsigned char __smem[appy_csr_dense_smem<{V}, {Tn}, P_WARPS, P_ROWS, "
                 f"{elt.c}>::bytes];")
         call = (f"appy_csr_dense<{V}, {Tn}, P_D, P_WARPS, P_ROWS, {ptr.ty.c}>"
-                f"(body, {indptr}, __lo, __hi, {ncols}, __smem);")
+                f"(__body, {indptr}, __lo, __hi, {ncols}, __smem);")
         src += self._kernel_wrapper(params, struct, call, smem, launch_bounds="32 * P_WARPS, P_MINB")
         small = V * Tn <= 4
         tun = {"P_WARPS": [8, 4], "P_ROWS": [32, 16, 64], "P_D": [8, 4, 2] if small else [2, 4],
@@ -807,7 +807,7 @@ class GroupEmitter(Emitter):
         super().__init__(env)
         self.hazards = hazard_arrays
         self.in_simd = False
-        self.store_guard = "g.lane == 0"
+        self.store_guard = "__g.lane == 0"
         self.env.indices.setdefault("__i0", T.I64)
 
     def s_Assign(self, st):
@@ -815,7 +815,7 @@ class GroupEmitter(Emitter):
         tgt = st.targets[0]
         if not self.in_simd and isinstance(tgt, ast.Subscript) and isinstance(tgt.value, ast.Name) \
                 and tgt.value.id in self.hazards:
-            lines = lines + ["g.barrier();"]
+            lines = lines + ["__g.barrier();"]
         return lines
 
     def s_For(self, st):
@@ -836,10 +836,10 @@ class GroupEmitter(Emitter):
             out.append(f"  {ty.c} {p} = {OPS[op]}::id<{ty.c}>();")
             self.load_override[text] = (p, ty)
             self.store_override[text] = (lambda code, t, p=p, ty=ty: [f"{p} = {cast(code, t, ty)};"])
-            post.append(f"  {text} = {OPS[op]}::op<{ty.c}>({text}, g.template reduce<{OPS[op]}, {ty.c}>({p}));")
+            post.append(f"  {text} = {OPS[op]}::op<{ty.c}>({text}, __g.template reduce<{OPS[op]}, {ty.c}>({p}));")
         self.in_simd = True
         guard, self.store_guard = self.store_guard, None
-        out.append(f"  for (i64 {v} = ({lo}) + g.lane; {v} < {hi}; {v} += g.size()) {{")
+        out.append(f"  for (i64 {v} = ({lo}) + __g.lane; {v} < {hi}; {v} += __g.size()) {{")
         out += self.block(st.body, "    ")
         out.append("  }")
         self.store_guard = guard
@@ -847,6 +847,6 @@ class GroupEmitter(Emitter):
         self.load_override, self.store_override = saved_l, saved_s
         out += post
         if stored_arrays([st]) & self.hazards:
-            out.append("  g.barrier();")
+            out.append("  __g.barrier();")
         out.append("}")
         return out
