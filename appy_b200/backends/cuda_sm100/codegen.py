@@ -240,7 +240,8 @@ class CompiledLoop:
             unit_last = nd == 0 or a.strides[-1] == 1 or a.shape[-1] <= 1
             lead = a.strides[:-1] if nd > 1 else ()
             vec = tuple(all(s % V == 0 for s in lead) for V in (2, 4, 8, 16))
-            key.append((a.dptr % 16 == 0 if a.dptr else True, unit_last, vec))
+            ext = sum((n - 1) * abs(s) for n, s in zip(a.shape, a.strides)) + 1 if all(a.shape) else 0
+            key.append((a.dptr % 16 == 0 if a.dptr else True, unit_last, vec, ext < 2 ** 31))
         # overlap of a stored array with any other array disables the read-only path
         noalias = True
         spans = []
@@ -273,9 +274,9 @@ class CompiledLoop:
                 infos.append(ArgInfo(name, "scalar", _scalar_type(sig[1])))
             else:
                 a = by_name[name]
-                aligned, unit_last, vec = flags[name]
+                aligned, unit_last, vec, small = flags[name]
                 infos.append(ArgInfo(name, "array", _elem_type(sig[2]), len(a.shape), unit_last, aligned,
-                                     dict(zip((2, 4, 8, 16), vec)), a.itemsize))
+                                     dict(zip((2, 4, 8, 16), vec)), a.itemsize, small))
         opts = dict(self.options)
         opts["_noalias"] = key[1]
         opts["_shape"] = {(n, 1): s for n, s in key[2]}
@@ -345,24 +346,39 @@ class CompiledLoop:
                 if trip >= 8192 * max(1, plan.vec) // 4 and plan.kind == "group":
                     g = 0
                 variant.tun["P_G"] = g
-        if plan.kind == "csr" and not variant.tuned and plan.info.get("indptr"):
-            by_name = {a.name: a for a in arrays}
-            ip = by_name.get(plan.info["indptr"])
-            if ip is not None and ip.shape[0] > 1:
-                counts, _mx = rt.row_histogram(ip.dptr, ip.itemsize, ip.shape[0] - 1)
-                total = sum(counts)
-                # median row-length bin decides the lanes per row
-                acc, med = 0, 0
-                for b, c in enumerate(counts):
-                    acc += c
-                    if acc * 2 >= total:
-                        med = b
-                        break
-                length = 1 << max(med - 1, 0)
-                variant.tun["P_G"] = 1 if length <= 2 else 2 if length <= 4 else 4 if length <= 16 else \
-                    8 if length <= 64 else 16 if length <= 256 else 32
-                variant.info_hist = counts
-            variant.tuned = variant.tuned or not self._want_autotune()
+        return {}
+
+    def _csr_overrides(self, variant: Variant, arrays) -> dict:
+        """Lanes per row from the row-length histogram of this matrix (cached per indptr buffer)."""
+        plan = variant.plan
+        if plan.kind != "csr" or not plan.info.get("indptr"):
+            return {}
+        ip = next((a for a in arrays if a.name == plan.info["indptr"]), None)
+        if ip is None or ip.shape[0] <= 1:
+            return {}
+        ckey = (ip.dptr, ip.shape[0])
+        cache = variant.__dict__.setdefault("csr_choice", {})
+        if ckey not in cache:
+            if len(cache) > 64:
+                cache.clear()
+            counts, _mx = rt.row_histogram(ip.dptr, ip.itemsize, ip.shape[0] - 1)
+            total = sum(counts)
+            acc, med = 0, 0
+            for b, c in enumerate(counts):      # median row-length bin decides the lanes per row
+                acc += c
+                if acc * 2 >= total:
+                    med = b
+                    break
+            length = 1 << max(med - 1, 0)
+            g = 1 if length <= 1 else 2 if length <= 4 else 4 if length <= 16 else \
+                8 if length <= 64 else 16 if length <= 256 else 32
+            variant.row_class = f"med{med}max{max((b for b, c in enumerate(counts) if c), default=0)}"
+            cache[ckey] = {"P_G": g}
+        return cache[ckey]
+
+    def _settle(self, variant: Variant) -> None:
+        if not self._want_autotune():
+            variant.tuned = True
 
     def _want_autotune(self) -> bool:
         return bool(self.options.get("autotune", os.environ.get("APPY_AUTOTUNE", "0") == "1"))
@@ -373,7 +389,7 @@ class CompiledLoop:
         store = _tune_store()
         bucket = max(n_iter, 1).bit_length()
         tkey = hashlib.sha1((plan.source + "|".join(map(str, plan.info.get("nvrtc", [])))).encode()).hexdigest() \
-            + f":{bucket}"
+            + f":{bucket}:{getattr(variant, 'row_class', '')}"
         if tkey in store:
             variant.tun.update(store[tkey])
             variant.tuned = True
@@ -414,6 +430,9 @@ class CompiledLoop:
         variant.tuned = True
         store[tkey] = best
         _tune_save()
+        if os.environ.get("APPY_TUNE_LOG") == "1":
+            sys.stderr.write(f"[appy autotune] {plan.name} ({plan.info.get('template')}) n={n_iter}: {best} "
+                             f"{best_t * 1e3:.1f} us\n")
 
     def _memo_key(self, args):
         key = []
@@ -464,13 +483,19 @@ class CompiledLoop:
         lo = int(eval(variant.lo_code, {}, scope))
         hi = int(eval(variant.hi_code, {}, scope))
         if hi > lo:
+            tun = variant.tun
             if not variant.tuned:
+                ov = self._csr_overrides(variant, arrays)      # host arrays: mirrors are uploaded by now
                 self._heuristics(variant, scope, arrays)
+                self._settle(variant)
                 if self._want_autotune() and not variant.tuned:
                     self._autotune(variant, args, arrays, lo, hi, stream)
+                elif ov:
+                    variant.tuned = False                      # the choice is per matrix, not per variant
+                    tun = dict(variant.tun, **ov)
             pack = self._pack(variant, args, arrays, lo, hi, stream)
-            h = variant.handle(variant.tun)
-            grid, block, smem = variant.plan.launch_config(variant.tun, hi - lo, self.sm_count)
+            h = variant.handle(tun)
+            grid, block, smem = variant.plan.launch_config(tun, hi - lo, self.sm_count)
             rt.launch(h, grid, block, pack, smem, stream)
             if not any_host and not variant.plan.uses_ws:
                 if len(self.memo) > 256:

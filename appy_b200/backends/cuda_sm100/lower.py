@@ -89,6 +89,7 @@ class ArgInfo:
     aligned: bool = True      # base pointer is 16-byte aligned
     strides_vec_ok: dict = field(default_factory=dict)   # V -> all leading strides % V == 0
     itemsize: int = 0
+    small: bool = False       # every element offset fits in 31 bits
 
 
 # --------------------------------------------------------------------------- analysis helpers
@@ -596,10 +597,10 @@ class Lowering:
             src += ["  " + l for l in fin] + ["};"]
             smem = ("__shared__ __align__(16) unsigned char __smem[32 * sizeof(" + acc_ty.c +
                     ") + (2 * P_ROWS + 2) * sizeof(int)];")
-            call = (f"appy_csr_vector<P_G, P_BLOCK, P_ROWS, P_G * 16, 2048, {ptr.ty.c}>"
+            call = (f"appy_csr_vector<P_G, P_BLOCK, P_ROWS, P_G * 16, 512, {ptr.ty.c}>"
                     f"(__body, {csr_ptr}, __lo, __hi, __smem);")
             src += self._kernel_wrapper(params, struct, call, smem)
-            tun = {"P_G": [4, 2, 8, 1, 16, 32], "P_BLOCK": [256], "P_ROWS": [256, 128, 512]}
+            tun = {"P_G": [4, 2, 8, 1, 16, 32], "P_BLOCK": [128, 256], "P_ROWS": [64, 128, 256]}
             return KernelPlan("csr", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr,
                               info={"template": "T3 CSR row loop", "indptr": csr_ptr})
 
@@ -762,22 +763,23 @@ class Lowering:
         for nm in (f"{bname}_stride_0", f"{cname}_stride_0"):
             arr, kind, dim = nm.rsplit("_", 2)[0], "stride", 0
             env.implicit[nm] = (arr, kind, dim)
-        row_ty = "int" if (row_t.bits <= 32) else "i64"
+        off_ty = "unsigned int" if a_b.small else "i64"
+        nc = ncols if ncols == 32 * V * Tn else 0
         init_c = cast(*em.expr(z.body[0].value), elt)
         struct = f"{self.name}_body"
         params = self._params(uses_ws=False)
         ptr = env.arrays[indptr]
         src = ['#include "t_csr_dense.cuh"', f"struct {struct} {{",
-               f"  typedef {elt.c} Elt; typedef {row_ty} Row;"]
+               f"  typedef {elt.c} Elt; typedef {off_ty} Off;"]
         src += ["  " + m for m in self._members(params)]
         src += [f"  APPY_DEV Elt coef(i64 {kvar}) const {{ return {coef_c}; }}",
-                f"  APPY_DEV Row brow(i64 {kvar}) const {{ return ({row_ty})({row_c}); }}",
-                f"  APPY_DEV const Elt* brow_ptr(Row __row) const {{ return {bname} + (i64)__row * {bname}_stride_0; }}",
+                f"  APPY_DEV Off brow_off(i64 {kvar}) const {{ return (Off)({row_c}) * (Off){bname}_stride_0; }}",
+                f"  APPY_DEV const Elt* bbase() const {{ return {bname}; }}",
                 f"  APPY_DEV Elt* crow_ptr(i64 {self.var}) const {{ return {cname} + {self.var} * {cname}_stride_0; }}",
                 f"  APPY_DEV Elt init() const {{ return {init_c}; }}", "};"]
         smem = (f"__shared__ __align__(16) unsigned char __smem[appy_csr_dense_smem<{V}, {Tn}, P_WARPS, P_ROWS, "
                 f"{elt.c}>::bytes];")
-        call = (f"appy_csr_dense<{V}, {Tn}, P_D, P_WARPS, P_ROWS, {ptr.ty.c}>"
+        call = (f"appy_csr_dense<{V}, {Tn}, P_D, P_WARPS, P_ROWS, {nc}, {ptr.ty.c}>"
                 f"(__body, {indptr}, __lo, __hi, {ncols}, __smem);")
         src += self._kernel_wrapper(params, struct, call, smem, launch_bounds="32 * P_WARPS, P_MINB")
         small = V * Tn <= 4

@@ -135,11 +135,11 @@ __global__ void __launch_bounds__(BLOCK) k_spmv_stream(SpmvBody body, const int*
   __shared__ __align__(16) unsigned char smem[CHUNK * sizeof(float) + (BLOCK + 1) * sizeof(i64)];
   appy_csr_stream<BLOCK, CHUNK, LONG, int>(body, indptr, lo, hi, smem);
 }
-const int kSpmvRows = 256;
+const int kSpmvRows = 64, kSpmvBlock = 128;
 template <int G>
-__global__ void __launch_bounds__(256) k_spmv_vector(SpmvBody body, const int* indptr, i64 lo, i64 hi) {
+__global__ void __launch_bounds__(kSpmvBlock) k_spmv_vector(SpmvBody body, const int* indptr, i64 lo, i64 hi) {
   __shared__ __align__(16) unsigned char smem[32 * sizeof(float) + (2 * kSpmvRows + 2) * sizeof(int)];
-  appy_csr_vector<G, 256, kSpmvRows, 16 * G, 2048, int>(body, indptr, lo, hi, smem);
+  appy_csr_vector<G, kSpmvBlock, kSpmvRows, 16 * G, 512, int>(body, indptr, lo, hi, smem);
 }
 
 // ------------------------------------------------------------------ T4: GEMV
@@ -174,9 +174,9 @@ __global__ void __launch_bounds__(G == 32 ? 128 : 256) k_gemv(GemvBody<V> body, 
 }
 
 // ------------------------------------------------------------------ T5: SpMM
-struct SpmmBody {
+template <class OffT> struct SpmmBody {
   typedef float Elt;
-  typedef int Row;
+  typedef OffT Off;
   const float* __restrict__ data;
   const int* __restrict__ indices;
   const float* __restrict__ B;
@@ -184,26 +184,26 @@ struct SpmmBody {
   float* __restrict__ C;
   i64 ldc;
   APPY_DEV float coef(i64 k) const { return appy_ld_cs<float, 1>(data + k).v[0]; }
-  APPY_DEV int brow(i64 k) const { return appy_ld_cs<int, 1>(indices + k).v[0]; }
-  APPY_DEV const float* brow_ptr(int r) const { return B + (i64)r * ldb; }
+  APPY_DEV Off brow_off(i64 k) const { return (Off)appy_ld_cs<int, 1>(indices + k).v[0] * (Off)ldb; }
+  APPY_DEV const float* bbase() const { return B; }
   APPY_DEV float* crow_ptr(i64 i) const { return C + i * ldc; }
   APPY_DEV float init() const { return 0.f; }
 };
 
 const int kSpmmWarps = 8, kSpmmRows = 32;
 
-template <int V, int T, int D, int MINB>
+template <int V, int T, int D, int MINB, int NC, class OffT>
 __global__ void __launch_bounds__(32 * kSpmmWarps, MINB)
-k_spmm(SpmmBody body, const int* indptr, i64 lo, i64 hi, int ncols) {
+k_spmm(SpmmBody<OffT> body, const int* indptr, i64 lo, i64 hi, int ncols) {
   __shared__ __align__(16) unsigned char smem[appy_csr_dense_smem<V, T, kSpmmWarps, kSpmmRows, float>::bytes];
-  appy_csr_dense<V, T, D, kSpmmWarps, kSpmmRows, int>(body, indptr, lo, hi, ncols, smem);
+  appy_csr_dense<V, T, D, kSpmmWarps, kSpmmRows, NC, int>(body, indptr, lo, hi, ncols, smem);
 }
 
-template <int V, int T, int D, int MINB>
-int launch_spmm(const SpmmBody& body, const int* indptr, i64 lo, i64 hi, int ncols, cudaStream_t s) {
+template <int V, int T, int D, int MINB, int NC, class OffT>
+int launch_spmm(const SpmmBody<OffT>& body, const int* indptr, i64 lo, i64 hi, int ncols, cudaStream_t s) {
   const i64 tiles = (hi - lo + kSpmmRows - 1) / kSpmmRows;
   const unsigned grid = (unsigned)std::min<i64>(tiles, 1 << 30);
-  k_spmm<V, T, D, MINB><<<grid, 32 * kSpmmWarps, 0, s>>>(body, indptr, lo, hi, ncols);
+  k_spmm<V, T, D, MINB, NC, OffT><<<grid, 32 * kSpmmWarps, 0, s>>>(body, indptr, lo, hi, ncols);
   return finish_launch("spmm launch");
 }
 
@@ -301,7 +301,7 @@ int appy_spmv_csr_f32(const float* ddata, const int32_t* dindptr, const int32_t*
 #define APPY_SPMV_CASE(G)                                                              \
   case G: {                                                                            \
     const i64 blocks = (rows + kSpmvRows - 1) / kSpmvRows;                             \
-    k_spmv_vector<G><<<(unsigned)std::min<i64>(blocks, max_grid), 256, 0, s>>>(body, dindptr, row_lo, row_hi); \
+    k_spmv_vector<G><<<(unsigned)std::min<i64>(blocks, max_grid), kSpmvBlock, 0, s>>>(body, dindptr, row_lo, row_hi); \
   } break;
     switch (strategy) {
       APPY_SPMV_CASE(1)
@@ -344,23 +344,24 @@ int appy_spmm_csr_f32(const float* ddata, const int32_t* dindptr, const int32_t*
   if (row_hi <= row_lo || ncols <= 0) return APPY_OK;
   if (ncols > 512) return appy_fail_arg("appy_spmm_csr_f32: ncols > 512 is not prebuilt");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  SpmmBody body{ddata, dindices, dB, ldb, dC, ldc};
+  SpmmBody<i64> body{ddata, dindices, dB, ldb, dC, ldc};
   const bool vec = aligned16(dB) && aligned16(dC) && ldb % 4 == 0 && ldc % 4 == 0 && ncols % 4 == 0;
   if (vec) {
     const int T = (ncols + 127) / 128;
+    if (ncols == 128) return launch_spmm<4, 1, 8, 4, 128, i64>(body, dindptr, row_lo, row_hi, ncols, s);
     switch (T) {
-      case 1: return launch_spmm<4, 1, 8, 4>(body, dindptr, row_lo, row_hi, ncols, s);
-      case 2: return launch_spmm<4, 2, 4, 3>(body, dindptr, row_lo, row_hi, ncols, s);
-      case 3: return launch_spmm<4, 3, 2, 2>(body, dindptr, row_lo, row_hi, ncols, s);
-      default: return launch_spmm<4, 4, 2, 2>(body, dindptr, row_lo, row_hi, ncols, s);
+      case 1: return launch_spmm<4, 1, 8, 4, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+      case 2: return launch_spmm<4, 2, 4, 3, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+      case 3: return launch_spmm<4, 3, 2, 2, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+      default: return launch_spmm<4, 4, 2, 2, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
     }
   }
   const int T = (ncols + 31) / 32;
-  if (T <= 1) return launch_spmm<1, 1, 4, 5>(body, dindptr, row_lo, row_hi, ncols, s);
-  if (T <= 2) return launch_spmm<1, 2, 4, 5>(body, dindptr, row_lo, row_hi, ncols, s);
-  if (T <= 4) return launch_spmm<1, 4, 4, 4>(body, dindptr, row_lo, row_hi, ncols, s);
-  if (T <= 8) return launch_spmm<1, 8, 2, 3>(body, dindptr, row_lo, row_hi, ncols, s);
-  return launch_spmm<1, 16, 2, 2>(body, dindptr, row_lo, row_hi, ncols, s);
+  if (T <= 1) return launch_spmm<1, 1, 4, 5, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+  if (T <= 2) return launch_spmm<1, 2, 4, 5, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+  if (T <= 4) return launch_spmm<1, 4, 4, 4, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+  if (T <= 8) return launch_spmm<1, 8, 2, 3, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+  return launch_spmm<1, 16, 2, 2, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
 }
 
 int appy_row_histogram(const void* d_indptr, int idx_bytes, int64_t nrows, int64_t* counts32,

@@ -27,10 +27,10 @@
 //
 //   struct Body {
 //     typedef <T> Elt;
-//     typedef <int|i64> Row;
+//     typedef <unsigned|i64> Off;              // element offset of a B row (32-bit when B is small enough)
 //     Elt   coef(i64 k) const;                 // A_data[k]
-//     Row   brow(i64 k) const;                 // A_indices[k]
-//     const Elt* brow_ptr(Row r) const;        // &B[r, 0]
+//     Off   brow_off(i64 k) const;             // A_indices[k] * (row stride of B)
+//     const Elt* bbase() const;                // &B[0, 0]
 //     Elt*  crow_ptr(i64 i) const;             // &C[i, 0]
 //     Elt   init() const;
 //   };
@@ -49,15 +49,16 @@ struct appy_rowacc {
   }
 };
 
-template <int V, int T, class Body>
-APPY_DEV void appy_csr_dense_load(const Body& body, typename Body::Row r, int lane, int ncols,
+// NC > 0: the number of columns is the compile-time constant NC and equals 32*V*T exactly
+// (no column guard); NC == 0: `ncols` is a run-time value and every access is guarded.
+template <int V, int T, int NC, class Body>
+APPY_DEV void appy_csr_dense_load(const typename Body::Elt* blane, typename Body::Off off, int lane, int ncols,
                                   appy_pack<typename Body::Elt, V> (&b)[T]) {
   typedef typename Body::Elt Elt;
-  const Elt* p = body.brow_ptr(r);
+  const Elt* p = blane + off;
 #pragma unroll
   for (int t = 0; t < T; ++t) {
-    const int col = (t * 32 + lane) * V;
-    if (col < ncols) b[t] = appy_ld_nc<Elt, V>(p + col);
+    if (NC > 0 || (t * 32 + lane) * V < ncols) b[t] = appy_ld_nc<Elt, V>(p + t * 32 * V);
   }
 }
 
@@ -70,7 +71,7 @@ APPY_DEV void appy_csr_dense_fma(appy_rowacc<V, T, Body>& acc, typename Body::El
     for (int x = 0; x < V; ++x) acc.a[t].v[x] = acc.a[t].v[x] + c * b[t].v[x];
 }
 
-template <int V, int T, class Body>
+template <int V, int T, int NC, class Body>
 APPY_DEV void appy_csr_dense_store(const Body& body, i64 i, int lane, int ncols,
                                    const appy_rowacc<V, T, Body>& acc) {
   typedef typename Body::Elt Elt;
@@ -78,8 +79,16 @@ APPY_DEV void appy_csr_dense_store(const Body& body, i64 i, int lane, int ncols,
 #pragma unroll
   for (int t = 0; t < T; ++t) {
     const int col = (t * 32 + lane) * V;
-    if (col < ncols) appy_st_cs<Elt, V>(p + col, acc.a[t]);
+    if (NC > 0 || col < ncols) appy_st_cs<Elt, V>(p + col, acc.a[t]);
   }
+}
+
+template <int V, int T, class Body>
+APPY_DEV void appy_csr_dense_park(typename Body::Elt* dst, int lane, const appy_rowacc<V, T, Body>& acc) {
+#pragma unroll
+  for (int t = 0; t < T; ++t)
+#pragma unroll
+    for (int x = 0; x < V; ++x) dst[(t * 32 + lane) * V + x] = acc.a[t].v[x];
 }
 
 // shared memory bytes needed by appy_csr_dense
@@ -89,17 +98,52 @@ struct appy_csr_dense_smem {
                            (int)sizeof(int) * 2 * NWARPS;
 };
 
+// One group of up to D non-zeros of the current 32-wide block: D gathers are issued, then folded in
+// order; after a non-zero that ends its row (bit set in `ends`) the row is written out.
+// GUARD = false is the fast path for a full block (all 32 positions valid).
+template <int V, int T, int D, int NC, bool GUARD, class Body>
+APPY_DEV void appy_csr_dense_group(const Body& body, const typename Body::Elt* blane, int q, int n, unsigned ends,
+                                   typename Body::Elt my_c, typename Body::Off my_off, int my_row, i64 r0,
+                                   bool& entered, typename Body::Elt* park0, int* tag0, int lane, int ncols,
+                                   appy_rowacc<V, T, Body>& acc) {
+  typedef typename Body::Elt Elt;
+  typedef typename Body::Off Off;
+  appy_pack<Elt, V> b[D][T];
+#pragma unroll
+  for (int j = 0; j < D; ++j)
+    if (!GUARD || q + j < n)
+      appy_csr_dense_load<V, T, NC, Body>(blane, appy_shfl<Off>(my_off, q + j, 32), lane, ncols, b[j]);
+#pragma unroll
+  for (int j = 0; j < D; ++j) {
+    if (!GUARD || q + j < n) {
+      appy_csr_dense_fma<V, T, Body>(acc, appy_shfl<Elt>(my_c, q + j, 32), b[j]);
+      if ((ends >> (q + j)) & 1u) {
+        const int row = __shfl_sync(APPY_FULL_MASK, my_row, q + j, 32);
+        if (entered) {   // the row was already open when this warp's share began: park the partial
+          appy_csr_dense_park<V, T, Body>(park0, lane, acc);
+          if (lane == 0) *tag0 = row;
+          entered = false;
+        } else {
+          appy_csr_dense_store<V, T, NC, Body>(body, r0 + row, lane, ncols, acc);
+        }
+        acc.fill(body.init());
+      }
+    }
+  }
+}
+
 // blockDim.x == 32*NWARPS.
-template <int V, int T, int D, int NWARPS, int R, class IdxT, class Body>
+template <int V, int T, int D, int NWARPS, int R, int NC, class IdxT, class Body>
 APPY_DEV void appy_csr_dense(const Body& body, const IdxT* __restrict__ indptr, i64 lo, i64 hi,
                              int ncols, void* smem_raw) {
   typedef typename Body::Elt Elt;
-  typedef typename Body::Row Row;
+  typedef typename Body::Off Off;
   const int W = 32 * V * T;                                          // padded row width
   Elt* s_part = reinterpret_cast<Elt*>(smem_raw);                    // [NWARPS][2][W]
   i64* s_ptr = reinterpret_cast<i64*>(s_part + NWARPS * 2 * W);      // [R+1] row starts
   int* s_tag = reinterpret_cast<int*>(s_ptr + (R + 1));              // [NWARPS][2] row of each partial
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const Elt* blane = body.bbase() + lane * V;
 
   for (i64 r0 = lo + (i64)blockIdx.x * R; r0 < hi; r0 += (i64)gridDim.x * R) {
     const int nr = (hi - r0 < R) ? (int)(hi - r0) : R;
@@ -112,7 +156,7 @@ APPY_DEV void appy_csr_dense(const Body& body, const IdxT* __restrict__ indptr, 
       if (s_ptr[j + 1] == s_ptr[j]) {
         appy_rowacc<V, T, Body> z;
         z.fill(body.init());
-        appy_csr_dense_store<V, T, Body>(body, r0 + j, lane, ncols, z);
+        appy_csr_dense_store<V, T, NC, Body>(body, r0 + j, lane, ncols, z);
       }
     }
     // this warp's share [ks, ke) of the tile's non-zeros
@@ -121,72 +165,65 @@ APPY_DEV void appy_csr_dense(const Body& body, const IdxT* __restrict__ indptr, 
     const i64 ks = s + (i64)warp * chunk;
     const i64 ke = (ks + chunk < e) ? ks + chunk : e;
     if (ks < ke) {
-      int cur = 0;
-      {  // largest row index with s_ptr[row] <= ks (the non-empty row that holds non-zero ks)
-        int hi_r = nr;
-        while (hi_r - cur > 1) {
-          const int mid = (cur + hi_r) >> 1;
-          if (s_ptr[mid] <= ks) cur = mid; else hi_r = mid;
-        }
-      }
-      i64 cur_end = s_ptr[cur + 1];
       appy_rowacc<V, T, Body> acc;
-      acc.fill(s_ptr[cur] >= ks ? body.init() : Elt(0));
+      bool entered;       // the open row began before ks (its first part belongs to another warp)
+      {
+        int row = 0, hi_r = nr;      // largest row with s_ptr[row] <= ks: the row that holds non-zero ks
+        while (hi_r - row > 1) {
+          const int mid = (row + hi_r) >> 1;
+          if (s_ptr[mid] <= ks) row = mid; else hi_r = mid;
+        }
+        entered = s_ptr[row] < ks;
+      }
+      acc.fill(entered ? Elt(0) : body.init());
       Elt nxt_c = Elt(0);
-      Row nxt_r = 0;
+      Off nxt_off = 0;
       if (ks + lane < ke) {
         nxt_c = body.coef(ks + lane);
-        nxt_r = body.brow(ks + lane);
+        nxt_off = body.brow_off(ks + lane);
       }
+      int last_row = 0;
+      bool open = true;   // the row holding the last processed non-zero has not ended yet
       for (i64 kb = ks; kb < ke; kb += 32) {
         const int n = (ke - kb < 32) ? (int)(ke - kb) : 32;
         const Elt my_c = nxt_c;
-        const Row my_r = nxt_r;
-        if (kb + 32 + lane < ke) {   // next block's coefficients and row numbers, one block ahead
+        const Off my_off = nxt_off;
+        if (kb + 32 + lane < ke) {   // next block's coefficients and offsets, one block ahead
           nxt_c = body.coef(kb + 32 + lane);
-          nxt_r = body.brow(kb + 32 + lane);
+          nxt_off = body.brow_off(kb + 32 + lane);
         }
-#pragma unroll 1
-        for (int q = 0; q < n; q += D) {
-          appy_pack<Elt, V> b[D][T];
-#pragma unroll
-          for (int j = 0; j < D; ++j)
-            if (q + j < n) appy_csr_dense_load<V, T, Body>(body, appy_shfl<Row>(my_r, q + j, 32), lane, ncols, b[j]);
-#pragma unroll
-          for (int j = 0; j < D; ++j) {
-            if (q + j < n) {
-              if (kb + q + j >= cur_end) {
-                // row `cur` is complete: store it, or park it if a share boundary cut it
-                if (s_ptr[cur] >= ks) {
-                  appy_csr_dense_store<V, T, Body>(body, r0 + cur, lane, ncols, acc);
-                } else {
-                  Elt* mine = s_part + (size_t)(warp * 2) * W;
-#pragma unroll
-                  for (int t = 0; t < T; ++t)
-#pragma unroll
-                    for (int x = 0; x < V; ++x) mine[(t * 32 + lane) * V + x] = acc.a[t].v[x];
-                  if (lane == 0) s_tag[warp * 2] = cur;
-                }
-                do { ++cur; } while (s_ptr[cur + 1] == s_ptr[cur]);
-                cur_end = s_ptr[cur + 1];
-                acc.fill(body.init());
-              }
-              appy_csr_dense_fma<V, T, Body>(acc, appy_shfl<Elt>(my_c, q + j, 32), b[j]);
-            }
+        // lane j: which row holds non-zero kb+j, and is it that row's last one?
+        int my_row = 0;
+        bool is_last = false;
+        if (lane < n) {
+          const i64 pos = kb + lane;
+          int hi_r = nr;
+          while (hi_r - my_row > 1) {
+            const int mid = (my_row + hi_r) >> 1;
+            if (s_ptr[mid] <= pos) my_row = mid; else hi_r = mid;
           }
+          is_last = s_ptr[my_row + 1] == pos + 1;
         }
+        const unsigned ends = __ballot_sync(APPY_FULL_MASK, is_last);
+        Elt* park0 = s_part + (size_t)(warp * 2) * W;
+        if (n == 32) {
+#pragma unroll 1
+          for (int q = 0; q < 32; q += D)
+            appy_csr_dense_group<V, T, D, NC, false, Body>(body, blane, q, 32, ends, my_c, my_off, my_row, r0,
+                                                           entered, park0, &s_tag[warp * 2], lane, ncols, acc);
+        } else {
+#pragma unroll 1
+          for (int q = 0; q < n; q += D)
+            appy_csr_dense_group<V, T, D, NC, true, Body>(body, blane, q, n, ends, my_c, my_off, my_row, r0,
+                                                          entered, park0, &s_tag[warp * 2], lane, ncols, acc);
+        }
+        last_row = __shfl_sync(APPY_FULL_MASK, my_row, n - 1, 32);
+        open = ((ends >> (n - 1)) & 1u) == 0;
       }
-      // the row that was open when the share ended
-      if (s_ptr[cur] >= ks && cur_end <= ke) {
-        appy_csr_dense_store<V, T, Body>(body, r0 + cur, lane, ncols, acc);
-      } else {
-        const int slot = (s_ptr[cur] >= ks) ? 1 : 0;
-        Elt* mine = s_part + (size_t)(warp * 2 + slot) * W;
-#pragma unroll
-        for (int t = 0; t < T; ++t)
-#pragma unroll
-          for (int x = 0; x < V; ++x) mine[(t * 32 + lane) * V + x] = acc.a[t].v[x];
-        if (lane == 0) s_tag[warp * 2 + slot] = cur;
+      if (open) {   // the share ended inside a row: park what was gathered so far
+        const int slot = entered ? 0 : 1;
+        appy_csr_dense_park<V, T, Body>(s_part + (size_t)(warp * 2 + slot) * W, lane, acc);
+        if (lane == 0) s_tag[warp * 2 + slot] = last_row;
       }
     }
     __syncthreads();
@@ -210,7 +247,7 @@ APPY_DEV void appy_csr_dense(const Body& body, const IdxT* __restrict__ indptr, 
 #pragma unroll
           for (int x = 0; x < V; ++x) sum.a[t].v[x] = sum.a[t].v[x] + s_part[(size_t)bb * W + (t * 32 + lane) * V + x];
       }
-      appy_csr_dense_store<V, T, Body>(body, r0 + row, lane, ncols, sum);
+      appy_csr_dense_store<V, T, NC, Body>(body, r0 + row, lane, ncols, sum);
     }
     __syncthreads();
   }
