@@ -585,6 +585,34 @@ def test_autotuner_preserves_results():
     assert np.all(y == 8.0)
 
 
+def test_fp_contract_modes():
+    """`fp_contract="numpy"` (default) reproduces NumPy's two roundings of a*x+y bit for bit;
+    `fp_contract="triton"` may fuse them (one rounding), as the reference's Triton code does."""
+    @appy.jit
+    def axpy_np(alpha, x, y, out):
+        #pragma parallel for simd
+        for i in range(x.shape[0]):
+            out[i] = alpha * x[i] + y[i]
+
+    @appy.jit(fp_contract="triton")
+    def axpy_fused(alpha, x, y, out):
+        #pragma parallel for simd
+        for i in range(x.shape[0]):
+            out[i] = alpha * x[i] + y[i]
+
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal(100000).astype(np.float32)
+    y = rng.standard_normal(100000).astype(np.float32)
+    alpha = np.float32(1.2345678)
+    o1, o2 = np.empty_like(x), np.empty_like(x)
+    axpy_np(alpha, x, y, o1)
+    axpy_fused(alpha, x, y, o2)
+    assert np.array_equal(o1, alpha * x + y)
+    fused = (alpha.astype(np.float64) * x.astype(np.float64) + y.astype(np.float64)).astype(np.float32)
+    assert np.array_equal(o2, fused)
+    assert not np.array_equal(o1, o2)       # the two contracts really differ on this input
+
+
 def test_kernel_cache_is_reused():
     from appy_b200.backends.cuda_sm100 import codegen as cg
     a, b = W.vec_add(1000)
