@@ -779,12 +779,12 @@ class Lowering:
                 f"  APPY_DEV Elt init() const {{ return {init_c}; }}", "};"]
         smem = (f"__shared__ __align__(16) unsigned char __smem[appy_csr_dense_smem<{V}, {Tn}, P_WARPS, P_ROWS, "
                 f"{elt.c}>::bytes];")
-        call = (f"appy_csr_dense<{V}, {Tn}, P_D, P_WARPS, P_ROWS, {nc}, {ptr.ty.c}>"
+        call = (f"appy_csr_dense<{V}, {Tn}, P_D, P_WARPS, P_ROWS, {nc}, P_ROLL, {ptr.ty.c}>"
                 f"(__body, {indptr}, __lo, __hi, {ncols}, __smem);")
         src += self._kernel_wrapper(params, struct, call, smem, launch_bounds="32 * P_WARPS, P_MINB")
         small = V * Tn <= 4
         tun = {"P_WARPS": [8, 4], "P_ROWS": [32, 16, 64], "P_D": [8, 4, 2] if small else [2, 4],
-               "P_MINB": [4, 3, 5, 2] if small else [2, 1]}
+               "P_MINB": [4, 3, 5, 2] if small else [2, 1], "P_ROLL": [1, 0]}
         return KernelPlan("csrdense", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr, vec=V,
                           info={"template": "T5 CSR x dense", "ncols": ncols, "vector_width": V, "indptr": indptr})
 

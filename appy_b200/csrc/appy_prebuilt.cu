@@ -196,7 +196,8 @@ template <int V, int T, int D, int MINB, int NC, class OffT>
 __global__ void __launch_bounds__(32 * kSpmmWarps, MINB)
 k_spmm(SpmmBody<OffT> body, const int* indptr, i64 lo, i64 hi, int ncols) {
   __shared__ __align__(16) unsigned char smem[appy_csr_dense_smem<V, T, kSpmmWarps, kSpmmRows, float>::bytes];
-  appy_csr_dense<V, T, D, kSpmmWarps, kSpmmRows, NC, int>(body, indptr, lo, hi, ncols, smem);
+  // the rolling gather pipeline pays off when a row fits one 16-byte pack per lane (V*T <= 4)
+  appy_csr_dense<V, T, D, kSpmmWarps, kSpmmRows, NC, (V * T <= 4), int>(body, indptr, lo, hi, ncols, smem);
 }
 
 template <int V, int T, int D, int MINB, int NC, class OffT>
@@ -351,7 +352,7 @@ int appy_spmm_csr_f32(const float* ddata, const int32_t* dindptr, const int32_t*
     if (ncols == 128) return launch_spmm<4, 1, 8, 4, 128, i64>(body, dindptr, row_lo, row_hi, ncols, s);
     switch (T) {
       case 1: return launch_spmm<4, 1, 8, 4, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
-      case 2: return launch_spmm<4, 2, 4, 3, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+      case 2: return launch_spmm<4, 2, 4, 2, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
       case 3: return launch_spmm<4, 3, 2, 2, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
       default: return launch_spmm<4, 4, 2, 2, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
     }

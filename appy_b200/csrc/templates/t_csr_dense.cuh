@@ -132,8 +132,42 @@ APPY_DEV void appy_csr_dense_group(const Body& body, const typename Body::Elt* b
   }
 }
 
-// blockDim.x == 32*NWARPS.
-template <int V, int T, int D, int NWARPS, int R, int NC, class IdxT, class Body>
+// Rolling variant of the group above: `ring` always holds the gathers of the next D non-zeros.
+// Each pack is folded and at once refilled with the gather D positions ahead (from this block's
+// offsets, or from the next block's, which were fetched one block earlier), so the number of
+// gathers in flight does not drop to zero between groups.
+template <int V, int T, int D, int NC, bool GUARD, class Body>
+APPY_DEV void appy_csr_dense_roll(const Body& body, const typename Body::Elt* blane, i64 kb, i64 ke, int q, int n,
+                                  unsigned ends, typename Body::Elt my_c, typename Body::Off my_off,
+                                  typename Body::Off nxt_off, int my_row, i64 r0, bool& entered,
+                                  typename Body::Elt* park0, int* tag0, int lane, int ncols,
+                                  appy_pack<typename Body::Elt, V> (&ring)[D][T], appy_rowacc<V, T, Body>& acc) {
+  typedef typename Body::Elt Elt;
+  typedef typename Body::Off Off;
+  const Off src_off = (q + D < 32) ? my_off : nxt_off;
+#pragma unroll
+  for (int j = 0; j < D; ++j) {
+    if (!GUARD || q + j < n) {
+      appy_csr_dense_fma<V, T, Body>(acc, appy_shfl<Elt>(my_c, q + j, 32), ring[j]);
+      if ((ends >> (q + j)) & 1u) {
+        const int row = __shfl_sync(APPY_FULL_MASK, my_row, q + j, 32);
+        if (entered) {
+          appy_csr_dense_park<V, T, Body>(park0, lane, acc);
+          if (lane == 0) *tag0 = row;
+          entered = false;
+        } else {
+          appy_csr_dense_store<V, T, NC, Body>(body, r0 + row, lane, ncols, acc);
+        }
+        acc.fill(body.init());
+      }
+      if (kb + q + j + D < ke)
+        appy_csr_dense_load<V, T, NC, Body>(blane, appy_shfl<Off>(src_off, (q + j + D) & 31, 32), lane, ncols, ring[j]);
+    }
+  }
+}
+
+// blockDim.x == 32*NWARPS.  ROLL selects the rolling gather pipeline.
+template <int V, int T, int D, int NWARPS, int R, int NC, bool ROLL, class IdxT, class Body>
 APPY_DEV void appy_csr_dense(const Body& body, const IdxT* __restrict__ indptr, i64 lo, i64 hi,
                              int ncols, void* smem_raw) {
   typedef typename Body::Elt Elt;
@@ -184,6 +218,13 @@ APPY_DEV void appy_csr_dense(const Body& body, const IdxT* __restrict__ indptr, 
       }
       int last_row = 0;
       bool open = true;   // the row holding the last processed non-zero has not ended yet
+      appy_pack<Elt, V> ring[ROLL ? D : 1][T];
+      if (ROLL) {
+#pragma unroll
+        for (int j = 0; j < (ROLL ? D : 1); ++j)
+          if (ks + j < ke)
+            appy_csr_dense_load<V, T, NC, Body>(blane, appy_shfl<Off>(nxt_off, j, 32), lane, ncols, ring[j]);
+      }
       for (i64 kb = ks; kb < ke; kb += 32) {
         const int n = (ke - kb < 32) ? (int)(ke - kb) : 32;
         const Elt my_c = nxt_c;
@@ -206,7 +247,21 @@ APPY_DEV void appy_csr_dense(const Body& body, const IdxT* __restrict__ indptr, 
         }
         const unsigned ends = __ballot_sync(APPY_FULL_MASK, is_last);
         Elt* park0 = s_part + (size_t)(warp * 2) * W;
-        if (n == 32) {
+        if (ROLL) {
+          if (n == 32) {
+#pragma unroll 1
+            for (int q = 0; q < 32; q += D)
+              appy_csr_dense_roll<V, T, (ROLL ? D : 1), NC, false, Body>(
+                  body, blane, kb, ke, q, 32, ends, my_c, my_off, nxt_off, my_row, r0, entered, park0,
+                  &s_tag[warp * 2], lane, ncols, ring, acc);
+          } else {
+#pragma unroll 1
+            for (int q = 0; q < n; q += D)
+              appy_csr_dense_roll<V, T, (ROLL ? D : 1), NC, true, Body>(
+                  body, blane, kb, ke, q, n, ends, my_c, my_off, nxt_off, my_row, r0, entered, park0,
+                  &s_tag[warp * 2], lane, ncols, ring, acc);
+          }
+        } else if (n == 32) {
 #pragma unroll 1
           for (int q = 0; q < 32; q += D)
             appy_csr_dense_group<V, T, D, NC, false, Body>(body, blane, q, 32, ends, my_c, my_off, my_row, r0,
