@@ -324,6 +324,12 @@ class CompiledLoop:
                 vals.append(C.c_int64(hi))
             elif p.kind == "ws":
                 vals.append(C.c_void_p(rt.workspace(stream)))
+            elif p.kind == "mb":
+                from . import multi_gpu
+                vals.append(C.c_void_p(multi_gpu.combiner().descriptor))
+            elif p.kind == "seq":
+                from . import multi_gpu
+                vals.append(C.c_uint64(multi_gpu.combiner().next_seq()))
         return rt.ArgPack(vals)
 
     def _heuristics(self, variant: Variant, scope, arrays):
@@ -460,14 +466,18 @@ class CompiledLoop:
             self.sm_count = rt.device_info(self.device)["sm_count"]
         mkey = self._memo_key(args)
         memo = self.memo.get(mkey)
-        if memo is not None and not memo[5]:
+        if memo is not None:
             # everything lives on the device and this exact call was seen before: launch straight away
-            handle, grid, block, smem, pack, _any_host = memo
+            handle, grid, block, smem, pack, seq_slot, memo_stream = memo
             torch = sys.modules.get("torch")
             stream = _torch_stream(torch, self.device) if torch is not None else rt.stream(0)
-            if grid:
-                rt.launch(handle, grid, block, pack, smem, stream)
-            return
+            if memo_stream is None or memo_stream == stream:     # a workspace belongs to one stream
+                if grid:
+                    if seq_slot is not None:
+                        from . import multi_gpu
+                        pack.values[seq_slot].value = multi_gpu.combiner().next_seq()
+                    rt.launch(handle, grid, block, pack, smem, stream)
+                return
         arrays = self._resolve_arrays(args)
         any_host = any(a.host for a in arrays)
         torch = sys.modules.get("torch")
@@ -497,12 +507,14 @@ class CompiledLoop:
             h = variant.handle(tun)
             grid, block, smem = variant.plan.launch_config(tun, hi - lo, self.sm_count)
             rt.launch(h, grid, block, pack, smem, stream)
-            if not any_host and not variant.plan.uses_ws:
+            if not any_host:
                 if len(self.memo) > 256:
                     self.memo.clear()
-                self.memo[mkey] = (h, grid, block, smem, pack, False)
+                kinds = [p.kind for p in variant.plan.params]
+                seq_slot = kinds.index("seq") if "seq" in kinds else None
+                self.memo[mkey] = (h, grid, block, smem, pack, seq_slot, stream if variant.plan.uses_ws else None)
         elif not any_host:
-            self.memo[mkey] = (0, 0, 0, 0, None, False)
+            self.memo[mkey] = (0, 0, 0, 0, None, None, None)
         if any_host:
             for a in arrays:
                 if a.host and a.name in self.stored and a.nbytes:
@@ -545,7 +557,7 @@ def _register_finalizer(obj, hptr: int) -> None:
         pass
 
 
-_OPTION_KEYS = ("ordered_reduction", "fp_contract", "autotune", "pin_host", "_generic_only", "_vectorize",
+_OPTION_KEYS = ("ordered_reduction", "combine", "fp_contract", "autotune", "pin_host", "_generic_only", "_vectorize",
                 "_stream_hint", "_hoist_safe", "_shape_spec")
 
 

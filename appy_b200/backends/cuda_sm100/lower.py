@@ -222,6 +222,9 @@ class Lowering:
         ps.append(Param("__hi", "hi", T.I64))
         if uses_ws:
             ps.append(Param("__ws", "ws"))
+        if uses_ws and self.options.get("combine") == "p2p":
+            ps.append(Param("__mb", "mb"))
+            ps.append(Param("__seq", "seq", Ty("u", 64)))
         return ps
 
     def _c_param(self, p: Param) -> str:
@@ -232,6 +235,8 @@ class Lowering:
             return f"{a.ty.c}* {p.name}"
         if p.kind == "ws":
             return "void* __ws"
+        if p.kind == "mb":
+            return "const appy_mailbox* __mb"
         return f"{p.ty.strong().c} {p.name}"
 
     def _members(self, params) -> list[str]:
@@ -244,7 +249,9 @@ class Lowering:
                  f"  {smem_decl}",
                  f"  {body_struct} __body;"]
         for p in params:
-            if p.kind not in ("lo", "hi"):
+            if p.kind not in ("lo", "hi", "seq"):
+                lines.append(f"  __body.{p.name} = {p.name};")
+            elif p.kind == "seq":
                 lines.append(f"  __body.{p.name} = {p.name};")
         lines += ["  " + l for l in extra_init]
         lines += [f"  {call}", "}"]
@@ -302,9 +309,23 @@ class Lowering:
             for r, (op, ty, acc, _n) in enumerate(items):
                 out.append(f"appy_ws_publish<{ty.c}>(__w, {r}, {acc});")
             out.append("if (appy_ws_arrive(__w, __smem)) {")
-            for r, ((op, ty, acc, _n), addr) in enumerate(zip(items, addrs)):
-                out.append(f"  {{ const {ty.c} __t = appy_ws_collect<{OPS[op]}, {ty.c}>(__w, {r}, __smem);")
-                out.append(f"    if (threadIdx.x == 0) *{addr} = {OPS[op]}::op<{ty.c}>(*{addr}, __t); }}")
+            if self.options.get("combine") == "p2p":
+                # this GPU's totals, then the exchange with the other ranks inside the same kernel
+                for r, (op, ty, acc, _n) in enumerate(items):
+                    out.append(f"  {ty.c} __t{r} = appy_ws_collect<{OPS[op]}, {ty.c}>(__w, {r}, __smem);")
+                out.append("  if (threadIdx.x == 0) {")
+                for r, (op, ty, acc, _n) in enumerate(items):
+                    out.append(f"    appy_p2p_post<{ty.c}>(__mb, __seq, {r}, __t{r});")
+                out.append("    appy_p2p_publish(__mb, __seq);")
+                out.append("    appy_p2p_wait(__mb, __seq);")
+                for r, ((op, ty, acc, _n), addr) in enumerate(zip(items, addrs)):
+                    out.append(f"    __t{r} = appy_p2p_fold<{OPS[op]}, {ty.c}>(__mb, __seq, {r});")
+                    out.append(f"    *{addr} = {OPS[op]}::op<{ty.c}>(*{addr}, __t{r});")
+                out.append("  }")
+            else:
+                for r, ((op, ty, acc, _n), addr) in enumerate(zip(items, addrs)):
+                    out.append(f"  {{ const {ty.c} __t = appy_ws_collect<{OPS[op]}, {ty.c}>(__w, {r}, __smem);")
+                    out.append(f"    if (threadIdx.x == 0) *{addr} = {OPS[op]}::op<{ty.c}>(*{addr}, __t); }}")
             out.append("}")
         return out
 
@@ -411,7 +432,8 @@ class Lowering:
         body = self.loop.body
         self._reduction_setup()
         em.infer_locals(body)
-        ordered = bool(self.options.get("ordered_reduction", False)) and bool(self.reductions)
+        ordered = bool(self.options.get("ordered_reduction", False) or self.options.get("combine") == "p2p") \
+            and bool(self.reductions)
         V = self.pick_vector_width()
         loads, stores = self._stream_accesses(V)
         local_decl = em.declare_locals()

@@ -59,3 +59,78 @@ def all_reduce(values, op: str = "+"):
     t = values if isinstance(values, torch.Tensor) else torch.from_numpy(np.asarray(values))
     dist.all_reduce(t, op=rop)
     return values
+
+
+class P2PCombiner:
+    """Peer mailboxes for the in-kernel combine of ``shared(...)`` scalars
+    (``@jit(combine="p2p")``).  Collective to create: every rank of the process group calls
+    ``enable_p2p()`` once, after ``torch.cuda.set_device``.  Without a process group it is a
+    one-rank combiner (the kernel then exchanges with itself), which is what single-GPU tests use.
+
+    Every rank must execute the same sequence of combining loops on one stream: launch number
+    ``seq`` of one rank pairs with launch number ``seq`` of the others.
+    """
+
+    def __init__(self, spin_limit: int = 0, loopback_world: int = 0):
+        """`spin_limit`: polls (about 1 us each) a kernel waits for each rank before it gives up
+        and raises the time-out flag (0 = library default, about 8 s).  `loopback_world` > 1
+        builds a context whose other ranks do not exist, for exercising the time-out path."""
+        import ctypes as C
+        rank, world_size = world()
+        if loopback_world:
+            rank, world_size = 0, loopback_world
+        self.rank, self.world = rank, world_size
+        self._ctx = C.c_void_p()
+        handle = (C.c_char * 64)()
+        rt.check(rt.lib().appy_p2p_create(world_size, rank, C.byref(self._ctx), handle))
+        handles = [bytes(handle)]
+        if world_size > 1 and not loopback_world:
+            import torch.distributed as dist
+            gathered = [None] * world_size
+            dist.all_gather_object(gathered, bytes(handle))
+            handles = gathered
+        blob = None if loopback_world else b"".join(handles)
+        desc = C.c_void_p()
+        rt.check(rt.lib().appy_p2p_open(self._ctx, blob, spin_limit, C.byref(desc)))
+        self.descriptor = desc.value
+        self._seq = 0
+        if world_size > 1 and not loopback_world:
+            import torch.distributed as dist
+            dist.barrier()          # every rank has mapped every mailbox before the first launch
+
+    def next_seq(self) -> int:
+        self._seq += 1
+        return self._seq
+
+    def timed_out(self) -> bool:
+        import ctypes as C
+        flag = C.c_int()
+        rt.check(rt.lib().appy_p2p_status(self._ctx, C.byref(flag)))
+        return bool(flag.value)
+
+    def close(self):
+        if self._ctx:
+            rt.lib().appy_p2p_destroy(self._ctx)
+            self._ctx = None
+
+
+_COMBINER = None
+
+
+def enable_p2p(spin_limit: int = 0) -> P2PCombiner:
+    global _COMBINER
+    if _COMBINER is None:
+        _COMBINER = P2PCombiner(spin_limit)
+    return _COMBINER
+
+
+def set_combiner(c) -> None:
+    """Install (or with None remove) the combiner used by combine="p2p" loops."""
+    global _COMBINER
+    _COMBINER = c
+
+
+def combiner() -> P2PCombiner:
+    if _COMBINER is None:
+        raise RuntimeError('combine="p2p" needs multi_gpu.enable_p2p() to be called on every rank first')
+    return _COMBINER

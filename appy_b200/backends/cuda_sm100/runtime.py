@@ -54,6 +54,10 @@ SIGNATURES = {
                                       C.POINTER(C.c_int64)]),
     "appy_row_histogram": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.POINTER(C.c_int64),
                                      C.POINTER(C.c_int64), C.c_void_p]),
+    "appy_p2p_create": (C.c_int, [C.c_int, C.c_int, c_void_pp, C.c_void_p]),
+    "appy_p2p_open": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint, c_void_pp]),
+    "appy_p2p_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
+    "appy_p2p_destroy": (C.c_int, [C.c_void_p]),
     "appy_vec_add_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "appy_sum_f32": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_void_p]),
     "appy_sum_f32_noalloc": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),

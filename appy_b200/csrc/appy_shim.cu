@@ -580,4 +580,97 @@ int appy_partition_rows(const void* indptr, int idx_bytes, int64_t nrows, int pa
   return APPY_OK;
 }
 
+// ---------------------------------------------------------------- peer mailboxes (multi-GPU scalar combine)
+
+struct P2PContext {
+  int world = 0, rank = 0;
+  void* local = nullptr;        // this rank's mailbox (cudaMalloc)
+  void* peers[16] = {nullptr};  // mapped mailboxes of all ranks (peers[rank] == local)
+  void* d_desc = nullptr;       // device copy of the descriptor the kernels read
+  unsigned* d_err = nullptr;
+  bool loopback = false;
+};
+
+struct MailboxDesc {            // must match `appy_mailbox` in templates/t_flat.cuh
+  int world, rank;
+  unsigned spin_limit, reserved;
+  unsigned* err;
+  unsigned long long* peer[16];
+};
+
+int appy_p2p_create(int world, int rank, void** ctx, void* ipc_handle_out) {
+  if (!ctx || !ipc_handle_out || world < 1 || world > 16 || rank < 0 || rank >= world)
+    return fail(APPY_ERR_ARG, "appy_p2p_create: bad arguments");
+  P2PContext* c = new P2PContext;
+  c->world = world;
+  c->rank = rank;
+  const size_t bytes = (size_t)2 * world * 8 * sizeof(unsigned long long);
+  cudaError_t e = cudaMalloc(&c->local, bytes < 4096 ? 4096 : bytes);
+  if (e == cudaSuccess) e = cudaMemset(c->local, 0, bytes < 4096 ? 4096 : bytes);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&c->d_err), 256);
+  if (e == cudaSuccess) e = cudaMemset(c->d_err, 0, 256);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_desc, sizeof(MailboxDesc));
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, c->local);
+  if (e != cudaSuccess) {
+    cudaFree(c->local); cudaFree(c->d_err); cudaFree(c->d_desc);
+    delete c;
+    return fail(APPY_ERR_CUDA, "appy_p2p_create failed: %s", cudaGetErrorString(e));
+  }
+  memcpy(ipc_handle_out, &h, sizeof h);
+  c->peers[rank] = c->local;
+  *ctx = c;
+  return APPY_OK;
+}
+
+int appy_p2p_open(void* ctx, const void* all_handles, unsigned spin_limit, void** device_descriptor) {
+  if (!ctx || !device_descriptor) return fail(APPY_ERR_ARG, "appy_p2p_open: NULL argument");
+  P2PContext* c = static_cast<P2PContext*>(ctx);
+  const cudaIpcMemHandle_t* hs = static_cast<const cudaIpcMemHandle_t*>(all_handles);
+  for (int r = 0; r < c->world; ++r) {
+    if (r == c->rank) continue;
+    if (!hs) {                     // loop-back: no peer process; the other ranks never post
+      c->peers[r] = c->local;
+      c->loopback = true;
+      continue;
+    }
+    cudaError_t e = cudaIpcOpenMemHandle(&c->peers[r], hs[r], cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess)
+      return fail(APPY_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d) failed: %s", r, cudaGetErrorString(e));
+  }
+  MailboxDesc d;
+  memset(&d, 0, sizeof d);
+  d.world = c->world;
+  d.rank = c->rank;
+  d.spin_limit = spin_limit ? spin_limit : (1u << 23);
+  d.err = c->d_err;
+  for (int r = 0; r < c->world; ++r) d.peer[r] = static_cast<unsigned long long*>(c->peers[r]);
+  CK(cudaMemcpy(c->d_desc, &d, sizeof d, cudaMemcpyHostToDevice));
+  *device_descriptor = c->d_desc;
+  return APPY_OK;
+}
+
+int appy_p2p_status(void* ctx, int* timed_out) {
+  if (!ctx || !timed_out) return fail(APPY_ERR_ARG, "appy_p2p_status: NULL argument");
+  P2PContext* c = static_cast<P2PContext*>(ctx);
+  unsigned v = 0;
+  CK(cudaMemcpy(&v, c->d_err, sizeof v, cudaMemcpyDeviceToHost));
+  *timed_out = (int)v;
+  if (v) CK(cudaMemset(c->d_err, 0, sizeof v));   // reading clears the flag
+  return APPY_OK;
+}
+
+int appy_p2p_destroy(void* ctx) {
+  if (!ctx) return APPY_OK;
+  P2PContext* c = static_cast<P2PContext*>(ctx);
+  cudaDeviceSynchronize();
+  for (int r = 0; r < c->world; ++r)
+    if (r != c->rank && c->peers[r] && !c->loopback) cudaIpcCloseMemHandle(c->peers[r]);
+  cudaFree(c->local);
+  cudaFree(c->d_err);
+  cudaFree(c->d_desc);
+  delete c;
+  return APPY_OK;
+}
+
 }  // extern "C"

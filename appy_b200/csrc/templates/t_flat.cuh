@@ -122,3 +122,100 @@ template <class Op, class T> APPY_DEV T appy_ws_collect(const appy_ws& w, int va
   }
   return appy_block_reduce<Op, T>(acc, reinterpret_cast<T*>(smem));
 }
+
+// ---------------------------------------------------------------------------
+// Cross-GPU combine of shared(...) scalars, fused into the reduction kernel's tail.
+//
+// Every rank (one process per GPU) owns a mailbox in its own HBM and holds peer pointers to
+// the mailboxes of all ranks (CUDA IPC mappings; NVLink/NVSwitch).  After the ordered commit
+// has produced this GPU's totals, one thread of the last CTA
+//   1. writes the totals into its slot of EVERY rank's mailbox with plain stores over NVLink,
+//      then publishes them with a release store of the launch's sequence number;
+//   2. waits (bounded) until the slots of all ranks in its OWN mailbox carry that sequence
+//      number, and folds them in rank order, so every rank obtains the same bits.
+// No kernel reads a peer's memory for data-path operands; only these few words cross GPUs.
+// Slots are double-buffered by sequence parity: a rank can be at most one launch ahead of
+// the slowest rank, because finishing launch s needs every rank's flag s.
+// The wait is limited; on expiry the error word is set and the partial result is used, so
+// a missing rank makes the launch return with a status the host reads, never a hang.
+//
+// Mailbox of one rank: [parity 0..1][source rank 0..world-1] x 8 words of 8 bytes:
+// word 0 = sequence flag, words 1..4 = values of up to 4 reduction variables.
+// ---------------------------------------------------------------------------
+struct appy_mailbox {
+  int world;
+  int rank;
+  unsigned spin_limit;      // polls per source rank before giving up (about 1 us each)
+  unsigned reserved;
+  unsigned* err;            // set to 1 when a wait ran out
+  u64* peer[16];            // peer[r] = mailbox of rank r as mapped into this process
+};
+
+APPY_DEV void appy_st_release_sys(u64* p, u64 v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+APPY_DEV u64 appy_ld_acquire_sys(const u64* p) {
+  u64 v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+APPY_DEV void appy_st_relaxed_sys(u64* p, u64 v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+APPY_DEV u64 appy_ld_relaxed_sys(const u64* p) {
+  u64 v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <class T> APPY_DEV u64 appy_to_bits(T v) {
+  union { T t; u64 u; } x;
+  x.u = 0;
+  x.t = v;
+  return x.u;
+}
+template <class T> APPY_DEV T appy_from_bits(u64 u) {
+  union { T t; u64 u; } x;
+  x.u = u;
+  return x.t;
+}
+
+// step 1 for variable `var`; call for every variable, then appy_p2p_publish once
+template <class T> APPY_DEV void appy_p2p_post(const appy_mailbox* mb, u64 seq, int var, T v) {
+  const int world = mb->world, rank = mb->rank;
+  const u64 bits = appy_to_bits<T>(v);
+  for (int p = 0; p < world; ++p)
+    appy_st_relaxed_sys(mb->peer[p] + ((seq & 1) * world + rank) * 8 + 1 + var, bits);
+}
+APPY_DEV void appy_p2p_publish(const appy_mailbox* mb, u64 seq) {
+  const int world = mb->world, rank = mb->rank;
+  __threadfence_system();
+  for (int p = 0; p < world; ++p) appy_st_release_sys(mb->peer[p] + ((seq & 1) * world + rank) * 8, seq);
+}
+// step 2: returns false if some rank's flag did not arrive within the limit
+APPY_DEV bool appy_p2p_wait(const appy_mailbox* mb, u64 seq) {
+  const int world = mb->world, rank = mb->rank;
+  bool ok = true;
+  for (int r = 0; r < world; ++r) {
+    const u64* flag = mb->peer[rank] + ((seq & 1) * world + r) * 8;
+    unsigned spins = 0;
+    while (appy_ld_acquire_sys(flag) < seq) {
+      if (++spins > mb->spin_limit) {
+        ok = false;
+        break;
+      }
+      __nanosleep(spins < 64 ? 20 : 1000);
+    }
+    if (!ok) break;
+  }
+  if (!ok) atomicExch(mb->err, 1u);
+  return ok;
+}
+template <class Op, class T> APPY_DEV T appy_p2p_fold(const appy_mailbox* mb, u64 seq, int var) {
+  const int world = mb->world, rank = mb->rank;
+  T total = Op::template id<T>();
+  for (int r = 0; r < world; ++r)
+    total = Op::template op<T>(total, appy_from_bits<T>(appy_ld_relaxed_sys(
+                                          mb->peer[rank] + ((seq & 1) * world + r) * 8 + 1 + var)));
+  return total;
+}

@@ -120,6 +120,18 @@ def masked_sum_into(a, mask, out):
     for i in range(a.shape[0]):
         out[0] += a[i] if mask[i] else 0.0
 
+@appy.jit(combine="p2p")
+def sum_into_p2p(a, out):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        out[0] += a[i]
+
+@appy.jit(combine="p2p")
+def masked_sum_into_p2p(a, mask, out):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        out[0] += a[i] if mask[i] else 0.0
+
 @appy.jit
 def vec_sum(a):
     b = 0.0
@@ -400,6 +412,9 @@ def main():
                     help="run a single configuration's kernel --steps times and exit (for profilers): "
                          "vec_add, sum, masked_sum, gemv, spmv_poisson, spmv_zipf, spmm")
     ap.add_argument("--scale", type=int, default=1, help="with --only: divide the problem size by this factor")
+    ap.add_argument("--combine", default="nccl", choices=["nccl", "p2p"],
+                    help="N > 1: how the two result scalars are combined across GPUs: an NCCL all-reduce "
+                         "per step, or peer mailboxes inside the reduction kernels (no collective call)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -435,13 +450,21 @@ def main():
     # launch stream.  (Overlapping it with the next step's kernels through a second buffer was
     # measured slower: the reduction kernels occupy every SM, so the NCCL kernel waits for them anyway.)
     outs = [out]
+    use_p2p = world > 1 and args.combine == "p2p"
+    if use_p2p:
+        from appy_b200.backends.cuda_sm100 import multi_gpu as mg
+        combiner = mg.enable_p2p()
 
     def step():
         out.zero_()
-        L.sum_into(a, out_a)
-        L.masked_sum_into(a, m, out_b)
-        if world > 1:
-            dist.all_reduce(out)
+        if use_p2p:
+            L.sum_into_p2p(a, out_a)
+            L.masked_sum_into_p2p(a, m, out_b)
+        else:
+            L.sum_into(a, out_a)
+            L.masked_sum_into(a, m, out_b)
+            if world > 1:
+                dist.all_reduce(out)
 
     def drain():
         pass
@@ -487,6 +510,8 @@ def main():
     else:
         for buf in outs:
             assert np.allclose(buf.cpu().numpy(), ref, rtol=1e-5, atol=0), (buf, ref)
+    if use_p2p:
+        assert not combiner.timed_out(), "a peer-mailbox wait ran out"
     t = torch.tensor([ms], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -567,7 +592,9 @@ def main():
             "config": {"workload": "C2 shared-scalar reductions: (a) sum, (b) masked sum (Bernoulli 0.5 bool mask), "
                                    f"f32, n={n} per GPU, through @appy_b200.jit",
                        "l2": "inputs larger than L2 (256 MiB + 64 MiB read per step)",
-                       "collective": "NCCL all-reduce of the two result scalars per step" if world > 1 else "none"},
+                       "collective": ("none" if world == 1 else
+                                      "peer mailboxes inside the reduction kernels (P2P stores over NVLink)" if use_p2p
+                                      else "NCCL all-reduce of the two result scalars per step")},
             "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": round(achieved, 1), "peak": peak,
                          "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
                          "peak_source": f"{peak_src} copy bandwidth", "us_per_launch": round(dom_us, 2),

@@ -122,6 +122,23 @@ int appy_partition_rows(const void* indptr, int idx_bytes, int64_t nrows, int pa
 int appy_row_histogram(const void* d_indptr, int idx_bytes, int64_t nrows, int64_t* counts32,
                        int64_t* max_len, void* stream);
 
+/* ---- peer mailboxes: combining shared(...) scalars across the GPUs of one box ----
+ * No counterpart in the reference (it is single-GPU).  One process per GPU.  Each rank
+ * creates a small mailbox in its own HBM and exports it as a CUDA IPC handle (64 bytes);
+ * after the ranks exchanged their handles (any host transport), appy_p2p_open maps the
+ * peers' mailboxes and returns the device descriptor that reduction kernels built with the
+ * `combine="p2p"` option take as an argument: they write their totals into every rank's
+ * mailbox over NVLink and fold the slots of their own mailbox in rank order, inside the
+ * kernel's tail.  Waits are bounded (spin_limit polls of about 1 us per source rank, 0 = default
+ * of 2^23); appy_p2p_status reports, and clears, whether one ran out.  all_handles == NULL opens
+ * the context in loop-back: no peer process exists and the other ranks never post, which is how
+ * the time-out path is exercised on a single GPU. */
+int appy_p2p_create(int world, int rank, void** ctx, void* ipc_handle_out /* 64 bytes */);
+int appy_p2p_open(void* ctx, const void* all_handles /* world x 64 bytes */, unsigned spin_limit,
+                  void** device_descriptor);
+int appy_p2p_status(void* ctx, int* timed_out);
+int appy_p2p_destroy(void* ctx);
+
 /* ---- prebuilt instantiations of the five templates (float32 / int32) ----
  * Device pointers; asynchronous on `stream`.  Each is the canonical
  * instantiation of a template that appy_compile would otherwise build from

@@ -1,0 +1,106 @@
+"""The in-kernel combine of shared(...) scalars over peer mailboxes (`@jit(combine="p2p")`).
+
+* one rank: the kernel exchanges with its own mailbox — exercises the whole tail on one GPU;
+* time-out: a loop-back context of world 2 whose second rank does not exist, with a short
+  wait limit: the kernel returns, the status word reports the time-out, the context stays
+  usable.  No GPU is hung or faulted: the wait is a bounded poll;
+* two ranks on two GPUs (skipped on a one-GPU box): every rank ends with the global total.
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+import appy_b200 as appy
+from appy_b200 import workloads as W
+from appy_b200.backends.cuda_sm100 import multi_gpu as mg
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+@appy.jit(combine="p2p")
+def sum_and_max(a):
+    s = 0.0
+    m = -1.0
+    #pragma parallel for simd shared(s, m)
+    for i in range(a.shape[0]):
+        s += a[i]
+        m = max(m, a[i])
+    return s, m
+
+
+def test_one_rank_combines_with_itself(rt):
+    mg.set_combiner(None)
+    c = mg.enable_p2p()
+    try:
+        a = W.vec_sum((1 << 20) + 11, seed=4)
+        da = torch.from_numpy(a).cuda()
+        for _ in range(3):                      # both slot parities
+            s, m = sum_and_max(da)
+            assert np.isclose(s, float(np.sum(a, dtype=np.float64)), rtol=1e-5, atol=0) and m == float(a.max())
+        assert not c.timed_out()
+    finally:
+        c.close()
+        mg.set_combiner(None)
+
+
+def test_missing_rank_times_out_with_a_status_not_a_hang(rt):
+    c = mg.P2PCombiner(spin_limit=200_000, loopback_world=2)      # roughly 0.2 s
+    mg.set_combiner(c)
+    try:
+        a = W.vec_sum(1 << 16, seed=5)
+        da = torch.from_numpy(a).cuda()
+        s, m = sum_and_max(da)                  # returns: the wait for rank 1 runs out
+        torch.cuda.synchronize()
+        assert c.timed_out()
+        assert not c.timed_out()                # reading the status clears it
+        out = torch.ones(8, device="cuda") * 2  # the context is still usable
+        assert float(out.sum()) == 16.0
+    finally:
+        c.close()
+        mg.set_combiner(None)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_main(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from appy_b200.backends.cuda_sm100 import runtime as rt
+        rt.init(rank)
+        comb = mg.enable_p2p()
+        a = W.vec_sum(1 << 20, seed=100 + rank)
+        da = torch.from_numpy(a).cuda()
+        total = sum(float(np.sum(W.vec_sum(1 << 20, seed=100 + r), dtype=np.float64)) for r in range(world))
+        big = max(float(W.vec_sum(1 << 20, seed=100 + r).max()) for r in range(world))
+        for _ in range(5):
+            s, m = sum_and_max(da)
+            assert np.isclose(s, total, rtol=1e-5, atol=0), (rank, s, total)
+            assert m == big
+        assert not comb.timed_out()
+        dist.barrier()
+        comb.close()
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_two_gpus(tmp_path):
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
