@@ -222,16 +222,21 @@ class CompiledLoop:
                 a.dptr = 0
                 continue
             a.dptr, _created = rt.mirror(a.hptr, a.nbytes)
-            if a.nbytes >= _PIN_MIN_BYTES and a.tmp is None and self.options.get("pin_host", True):
+            pinned = a.hptr in _finalizers
+            if a.nbytes >= _PIN_MIN_BYTES and a.tmp is None and self.options.get("pin_host", True) and not pinned:
                 seen = _seen_host.get(a.hptr, 0) + 1
                 _seen_host[a.hptr] = seen
-                if seen == 2:
+                if seen == 2:      # a buffer that comes back is worth pinning in place
                     try:
                         rt.check(rt.lib().appy_register_host(C.c_void_p(a.hptr), a.nbytes))
                         _register_finalizer(a.obj, a.hptr)
+                        pinned = a.hptr in _finalizers
                     except rt.AppyRuntimeError:
                         pass
-            rt.h2d(a.dptr, a.hptr, a.nbytes, stream)
+            if pinned or a.nbytes < _PIN_MIN_BYTES:
+                rt.h2d(a.dptr, a.hptr, a.nbytes, stream)          # true DMA, or too small to matter
+            else:
+                rt.h2d_staged(a.dptr, a.hptr, a.nbytes, stream)   # pageable: pinned staging buffers
 
     def _spec_key(self, arrays):
         key = []

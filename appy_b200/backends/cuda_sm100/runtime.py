@@ -37,6 +37,7 @@ SIGNATURES = {
     "appy_evict": (C.c_int, [C.c_void_p]),
     "appy_h2d_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "appy_d2h_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "appy_h2d_staged": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "appy_d2d_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "appy_compile": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, c_void_pp]),
     "appy_compile_check": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, C.POINTER(C.c_size_t)]),
@@ -172,6 +173,10 @@ def mirror(hptr: int, nbytes: int) -> tuple[int, bool]:
 
 def h2d(dptr: int, hptr: int, nbytes: int, stream_: int = 0) -> None:
     check(lib().appy_h2d_async(C.c_void_p(dptr), C.c_void_p(hptr), nbytes, C.c_void_p(stream_)))
+
+
+def h2d_staged(dptr: int, hptr: int, nbytes: int, stream_: int = 0) -> None:
+    check(lib().appy_h2d_staged(C.c_void_p(dptr), C.c_void_p(hptr), nbytes, C.c_void_p(stream_)))
 
 
 def d2h(hptr: int, dptr: int, nbytes: int, stream_: int = 0) -> None:

@@ -59,6 +59,25 @@ struct DeviceState {
 };
 DeviceState g_dev[16];
 
+const size_t kStageBytes = 8u << 20;
+struct Staging {
+  void* buf[2] = {nullptr, nullptr};
+  cudaEvent_t done[2] = {nullptr, nullptr};
+};
+Staging g_stage[16];
+
+int staging_for(int dev, Staging** out) {
+  Staging& st = g_stage[dev];
+  if (!st.buf[0]) {
+    for (int i = 0; i < 2; ++i) {
+      CK(cudaHostAlloc(&st.buf[i], kStageBytes, cudaHostAllocPortable));
+      CK(cudaEventCreateWithFlags(&st.done[i], cudaEventDisableTiming));
+    }
+  }
+  *out = &st;
+  return APPY_OK;
+}
+
 int cur_device(int* dev) {
   CK(cudaGetDevice(dev));
   if (*dev < 0 || *dev >= 16) return fail(APPY_ERR_STATE, "device index %d out of range", *dev);
@@ -217,6 +236,10 @@ int appy_shutdown(void) {
     d.mirrors.clear();
     for (auto& kv : d.workspaces) cudaFree(kv.second);
     d.workspaces.clear();
+    for (int i = 0; i < 2; ++i) {
+      if (g_stage[dev].buf[i]) { cudaFreeHost(g_stage[dev].buf[i]); g_stage[dev].buf[i] = nullptr; }
+      if (g_stage[dev].done[i]) { cudaEventDestroy(g_stage[dev].done[i]); g_stage[dev].done[i] = nullptr; }
+    }
     for (auto& kv : d.live_blocks) cudaFree(kv.first);
     d.live_blocks.clear();
     d.free_blocks.clear();
@@ -391,6 +414,31 @@ int appy_d2h_async(void* hptr, const void* dptr, size_t bytes, void* stream) {
   CK(cudaMemcpyAsync(hptr, dptr, bytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
   return APPY_OK;
 }
+// Pageable host memory: stage through two pinned buffers so that the CPU copy of chunk k+1 overlaps
+// the DMA of chunk k (a plain cudaMemcpyAsync from pageable memory is staged by the driver and
+// blocks the calling thread for the whole transfer).
+int appy_h2d_staged(void* dptr, const void* hptr, size_t bytes, void* stream) {
+  if (!bytes) return APPY_OK;
+  int dev;
+  if (int rc = cur_device(&dev)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  std::lock_guard<std::mutex> lk(g_mu);     // the two buffers are shared by all callers of a device
+  Staging* st = nullptr;
+  if (int rc = staging_for(dev, &st)) return rc;
+  size_t off = 0;
+  int which = 0;
+  while (off < bytes) {
+    const size_t n = std::min(kStageBytes, bytes - off);
+    CK(cudaEventSynchronize(st->done[which]));          // the previous DMA out of this buffer is over
+    memcpy(st->buf[which], static_cast<const char*>(hptr) + off, n);
+    CK(cudaMemcpyAsync(static_cast<char*>(dptr) + off, st->buf[which], n, cudaMemcpyHostToDevice, s));
+    CK(cudaEventRecord(st->done[which], s));
+    off += n;
+    which ^= 1;
+  }
+  return APPY_OK;
+}
+
 int appy_d2d_async(void* dst, const void* src, size_t bytes, void* stream) {
   if (!bytes) return APPY_OK;
   CK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));

@@ -331,7 +331,7 @@ def run_reference(args, rank):
         "impl": "reference", "metric": "effective HBM GB/s of the generated-kernel path (shared-scalar reductions)",
         "value": round(gbs, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32 data, f64 accumulate", "data": "synthetic",
+        "dtype": "f32", "data": "synthetic",
         "config": {"workload": "C2 shared-scalar reductions: (a) sum, (b) masked sum (Bernoulli 0.5 bool mask), "
                                f"f32, n={N_HEADLINE} per GPU, host cores; each step a sample of n=2^24 per loop"},
         "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
@@ -588,10 +588,11 @@ def main():
             "metric": "effective HBM GB/s of the generated-kernel path (shared-scalar reductions)",
             "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32 data, f64 accumulate", "data": "synthetic",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "C2 shared-scalar reductions: (a) sum, (b) masked sum (Bernoulli 0.5 bool mask), "
                                    f"f32, n={n} per GPU, through @appy_b200.jit",
                        "l2": "inputs larger than L2 (256 MiB + 64 MiB read per step)",
+                       "accumulate": "float64 (the shared scalar is a float64 cell, as in the reference)",
                        "collective": ("none" if world == 1 else
                                       "peer mailboxes inside the reduction kernels (P2P stores over NVLink)" if use_p2p
                                       else "NCCL all-reduce of the two result scalars per step")},

@@ -75,6 +75,9 @@ int appy_mirror(const void* hptr, size_t bytes, void** dptr, int* created);
 int appy_evict(const void* hptr);
 int appy_h2d_async(void* dptr, const void* hptr, size_t bytes, void* stream);
 int appy_d2h_async(void* hptr, const void* dptr, size_t bytes, void* stream);
+/* Upload from PAGEABLE host memory through two pinned 8 MiB staging buffers: the CPU copy of one
+ * chunk overlaps the DMA of the previous one.  Returns when the last chunk has been queued. */
+int appy_h2d_staged(void* dptr, const void* hptr, size_t bytes, void* stream);
 int appy_d2d_async(void* dst, const void* src, size_t bytes, void* stream);
 
 /* ---- compile / launch -------------------------------------------------- */

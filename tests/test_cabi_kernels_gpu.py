@@ -209,3 +209,24 @@ def test_launch_counter_counts(rt):
     torch.cuda.synchronize()
     assert rt.launch_count() == before + 1
     assert float(c.sum()) == 2000.0
+
+
+def test_staged_upload_from_pageable_memory(rt):
+    """appy_h2d_staged: chunked upload through the pinned staging buffers (sizes around the 8 MiB chunk)."""
+    for nbytes in (1, 4097, (8 << 20) - 1, 8 << 20, (8 << 20) + 5, (20 << 20) + 3):
+        h = np.random.default_rng(nbytes % 97).integers(0, 256, nbytes, dtype=np.uint8)
+        d = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        rt.h2d_staged(d.data_ptr(), h.ctypes.data, nbytes, 0)
+        torch.cuda.synchronize()
+        assert np.array_equal(d.cpu().numpy(), h)
+
+
+def test_mirror_is_reused_and_evicted(rt):
+    h = np.arange(1000, dtype=np.float32)
+    p1, created1 = rt.mirror(h.ctypes.data, h.nbytes)
+    p2, created2 = rt.mirror(h.ctypes.data, h.nbytes)
+    assert created1 and not created2 and p1 == p2
+    rt.check(rt.lib().appy_evict(C.c_void_p(h.ctypes.data)))
+    _p3, created3 = rt.mirror(h.ctypes.data, h.nbytes)
+    assert created3
+    rt.check(rt.lib().appy_evict(C.c_void_p(h.ctypes.data)))
