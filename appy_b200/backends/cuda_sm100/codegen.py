@@ -224,6 +224,8 @@ class CompiledLoop:
             a.dptr, _created = rt.mirror(a.hptr, a.nbytes)
             pinned = a.hptr in _finalizers
             if a.nbytes >= _PIN_MIN_BYTES and a.tmp is None and self.options.get("pin_host", True) and not pinned:
+                if len(_seen_host) > 4096:
+                    _seen_host.clear()
                 seen = _seen_host.get(a.hptr, 0) + 1
                 _seen_host[a.hptr] = seen
                 if seen == 2:      # a buffer that comes back is worth pinning in place
@@ -526,8 +528,10 @@ class CompiledLoop:
                     rt.d2h(a.hptr, a.dptr, a.nbytes, stream)
             rt.sync(stream)
             for a in arrays:
-                if a.host and a.tmp is not None and a.name in self.stored:
-                    a.obj[...] = a.tmp
+                if a.host and a.tmp is not None:
+                    if a.name in self.stored:
+                        a.obj[...] = a.tmp
+                    rt.check(rt.lib().appy_evict(C.c_void_p(a.hptr)))    # the contiguous copy dies with this call
 
     # convenience for tests and dumps
     def source_for(self, *args) -> str:

@@ -54,7 +54,10 @@ struct DeviceState {
   std::unordered_map<cudaStream_t, void*> workspaces;
   std::multimap<size_t, void*> free_blocks;          // cached allocator: size -> block
   std::unordered_map<void*, size_t> live_blocks;     // block -> rounded size
-  std::unordered_map<const void*, std::pair<void*, size_t>> mirrors;  // host -> (dev, bytes)
+  struct Mirror { void* dptr; size_t bytes; uint64_t last_use; };
+  std::unordered_map<const void*, Mirror> mirrors;   // host pointer -> device mirror
+  size_t mirror_bytes = 0;
+  uint64_t tick = 0;
   std::unordered_map<const void*, size_t> pinned;    // host ranges registered by us
 };
 DeviceState g_dev[16];
@@ -232,8 +235,9 @@ int appy_shutdown(void) {
     cudaDeviceSynchronize();
     for (auto& kv : d.pinned) cudaHostUnregister(const_cast<void*>(kv.first));
     d.pinned.clear();
-    for (auto& kv : d.mirrors) d.free_blocks.emplace(d.live_blocks[kv.second.first], kv.second.first);
+    for (auto& kv : d.mirrors) d.free_blocks.emplace(d.live_blocks[kv.second.dptr], kv.second.dptr);
     d.mirrors.clear();
+    d.mirror_bytes = 0;
     for (auto& kv : d.workspaces) cudaFree(kv.second);
     d.workspaces.clear();
     for (int i = 0; i < 2; ++i) {
@@ -365,6 +369,19 @@ int appy_unregister_host(void* hptr) {
   return APPY_OK;
 }
 
+// Mirrors are a cache: beyond kMirrorMaxCount entries or kMirrorMaxBytes the least recently used ones
+// are dropped (their blocks return to the cached allocator).  A mirror is only referenced between the
+// appy_mirror call and the stream synchronisation that ends the same host-array launch, so dropping an
+// older one is safe.
+const size_t kMirrorMaxCount = 1024;
+const size_t kMirrorMaxBytes = (size_t)16 << 30;
+
+static void drop_mirror_locked(DeviceState& d, std::unordered_map<const void*, DeviceState::Mirror>::iterator it) {
+  d.mirror_bytes -= it->second.bytes;
+  d.free_blocks.emplace(d.live_blocks[it->second.dptr], it->second.dptr);
+  d.mirrors.erase(it);
+}
+
 int appy_mirror(const void* hptr, size_t bytes, void** dptr, int* created) {
   if (!hptr || !dptr) return fail(APPY_ERR_ARG, "appy_mirror: NULL argument");
   int dev;
@@ -374,19 +391,32 @@ int appy_mirror(const void* hptr, size_t bytes, void** dptr, int* created) {
     DeviceState& d = g_dev[dev];
     auto it = d.mirrors.find(hptr);
     if (it != d.mirrors.end()) {
-      if (it->second.second >= bytes && it->second.second <= 2 * round_block(bytes)) {
-        *dptr = it->second.first;
+      if (it->second.bytes >= bytes && it->second.bytes <= 2 * round_block(bytes)) {
+        it->second.last_use = ++d.tick;
+        *dptr = it->second.dptr;
         if (created) *created = 0;
         return APPY_OK;
       }
-      d.free_blocks.emplace(d.live_blocks[it->second.first], it->second.first);
-      d.mirrors.erase(it);
+      drop_mirror_locked(d, it);
+    }
+    const size_t want = round_block(bytes ? bytes : 1);
+    while (!d.mirrors.empty() &&
+           (d.mirrors.size() >= kMirrorMaxCount || d.mirror_bytes + want > kMirrorMaxBytes)) {
+      auto oldest = d.mirrors.begin();
+      for (auto jt = d.mirrors.begin(); jt != d.mirrors.end(); ++jt)
+        if (jt->second.last_use < oldest->second.last_use) oldest = jt;
+      // the 64 most recent acquisitions may belong to the launch being prepared: never drop those
+      if (oldest->second.last_use + 64 > d.tick) break;
+      drop_mirror_locked(d, oldest);
     }
   }
   void* p = nullptr;
   if (int rc = appy_malloc(&p, bytes)) return rc;
   std::lock_guard<std::mutex> lk(g_mu);
-  g_dev[dev].mirrors[hptr] = std::make_pair(p, round_block(bytes ? bytes : 1));
+  DeviceState& d = g_dev[dev];
+  const size_t got = round_block(bytes ? bytes : 1);
+  d.mirrors[hptr] = DeviceState::Mirror{p, got, ++d.tick};
+  d.mirror_bytes += got;
   *dptr = p;
   if (created) *created = 1;
   return APPY_OK;
@@ -399,8 +429,7 @@ int appy_evict(const void* hptr) {
   DeviceState& d = g_dev[dev];
   auto it = d.mirrors.find(hptr);
   if (it == d.mirrors.end()) return APPY_OK;
-  d.free_blocks.emplace(d.live_blocks[it->second.first], it->second.first);
-  d.mirrors.erase(it);
+  drop_mirror_locked(d, it);
   return APPY_OK;
 }
 

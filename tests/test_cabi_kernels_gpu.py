@@ -230,3 +230,19 @@ def test_mirror_is_reused_and_evicted(rt):
     _p3, created3 = rt.mirror(h.ctypes.data, h.nbytes)
     assert created3
     rt.check(rt.lib().appy_evict(C.c_void_p(h.ctypes.data)))
+
+
+def test_mirror_cache_is_bounded(rt):
+    """More distinct host buffers than the cache holds: old mirrors are dropped, recent ones survive."""
+    keep = [np.zeros(16, np.float32) for _ in range(1500)]
+    ptrs = []
+    for h in keep:
+        p, created = rt.mirror(h.ctypes.data, h.nbytes)
+        assert created
+        ptrs.append(p)
+    _p, created_recent = rt.mirror(keep[-1].ctypes.data, keep[-1].nbytes)
+    assert not created_recent                       # the newest is still cached
+    _p, created_old = rt.mirror(keep[0].ctypes.data, keep[0].nbytes)
+    assert created_old                              # the oldest was dropped and is rebuilt
+    for h in keep:
+        rt.check(rt.lib().appy_evict(C.c_void_p(h.ctypes.data)))
