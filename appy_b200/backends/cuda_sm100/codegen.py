@@ -142,6 +142,16 @@ class _Array:
     __slots__ = ("name", "obj", "host", "dptr", "nbytes", "shape", "strides", "itemsize", "tmp", "hptr")
 
 
+class _DevView:
+    """Minimal __cuda_array_interface__ holder so torch can wrap a device mirror without copying."""
+
+    def __init__(self, ptr: int, n: int, typestr: str):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+_IDENTITY = {"+": 0, "*": 1}
+
+
 class Variant:
     def __init__(self, plan: KernelPlan):
         self.plan = plan
@@ -447,6 +457,71 @@ class CompiledLoop:
             sys.stderr.write(f"[appy autotune] {plan.name} ({plan.info.get('template')}) n={n_iter}: {best} "
                              f"{best_t * 1e3:.1f} us\n")
 
+    # ------------------------------------------------------------------ distribution over ranks
+    def _check_distributable(self):
+        """Generic rule: arrays written by the loop must be indexed by the parallel index in their
+        leading dimension (then every rank writes a disjoint slice); reduction targets are combined;
+        anything else cannot be split across GPUs."""
+        if getattr(self, "_dist_checked", False):
+            return
+        from ...frontend.loop_normalize import reductions_of
+        loop = self.ir.loop
+        var = loop.target.id
+        red = set(reductions_of(loop))
+        for n in ast.walk(loop):
+            if isinstance(n, ast.Subscript) and isinstance(n.ctx, ast.Store) and isinstance(n.value, ast.Name):
+                if ast.unparse(n) in red:
+                    continue
+                first = n.slice.elts[0] if isinstance(n.slice, ast.Tuple) else n.slice
+                if not (isinstance(first, ast.Name) and first.id == var):
+                    raise NotImplementedError(
+                        f"cannot distribute this loop over GPUs: `{ast.unparse(n)}` is not written at the "
+                        f"parallel index `{var}` in its leading dimension")
+        self._dist_checked = True
+
+    def _rank_range(self, variant, arrays, lo, hi):
+        from . import multi_gpu
+        rank, world_size = multi_gpu.world()
+        if world_size == 1 or hi <= lo:
+            return lo, hi
+        self._check_distributable()
+        plan = variant.plan
+        if plan.kind in ("csr", "csrdense") and plan.info.get("indptr"):
+            ip = next(a for a in arrays if a.name == plan.info["indptr"])
+            key = (ip.dptr if not ip.host else ip.hptr, ip.shape[0], lo, hi, world_size)
+            cache = self.__dict__.setdefault("_row_split", {})
+            if key not in cache:
+                host = ip.obj if ip.host else ip.obj.detach().cpu().numpy()
+                b = rt.partition_rows(np.ascontiguousarray(host[lo:hi + 1]), world_size)
+                if len(cache) > 64:
+                    cache.clear()
+                cache[key] = [lo + x for x in b]
+            b = cache[key]
+            return b[rank], b[rank + 1]
+        return multi_gpu.split_range(lo, hi, world_size, rank, 32)
+
+    def _reduction_cells(self, args, arrays):
+        """(torch view of the 1-element target cell, operator) for every reduction of the loop."""
+        import torch
+        from ...frontend.loop_normalize import reductions_of
+        cells = []
+        by_name = {a.name: a for a in arrays}
+        tens = dict(zip(self.arg_names, args))
+        for text, op in reductions_of(self.ir.loop).items():
+            node = ast.parse(text, mode="eval").body
+            if not (isinstance(node, ast.Subscript) and isinstance(node.value, ast.Name)
+                    and isinstance(node.slice, ast.Constant) and node.value.id in by_name):
+                raise NotImplementedError(f"distributed reduction target must be `name[<constant>]`: {text}")
+            a = by_name[node.value.id]
+            idx = int(node.slice.value)
+            if a.host:
+                dt = np.dtype(a.obj.dtype)
+                view = torch.as_tensor(_DevView(a.dptr + idx * a.itemsize, 1, dt.str), device="cuda")
+            else:
+                view = tens[a.name].view(-1)[idx:idx + 1]
+            cells.append((view, op))
+        return cells
+
     def _memo_key(self, args):
         key = []
         for sig, v in zip(self.arg_sigs, args):
@@ -475,21 +550,25 @@ class CompiledLoop:
         memo = self.memo.get(mkey)
         if memo is not None:
             # everything lives on the device and this exact call was seen before: launch straight away
-            handle, grid, block, smem, pack, seq_slot, memo_stream = memo
+            handle, grid, block, smem, pack, seq_slot, memo_stream, cells = memo
             torch = sys.modules.get("torch")
             stream = _torch_stream(torch, self.device) if torch is not None else rt.stream(0)
             if memo_stream is None or memo_stream == stream:     # a workspace belongs to one stream
+                if cells:
+                    self._pre_combine(cells)
                 if grid:
                     if seq_slot is not None:
                         from . import multi_gpu
                         pack.values[seq_slot].value = multi_gpu.combiner().next_seq()
                     rt.launch(handle, grid, block, pack, smem, stream)
+                if cells:
+                    self._post_combine(cells)
                 return
         arrays = self._resolve_arrays(args)
         any_host = any(a.host for a in arrays)
         torch = sys.modules.get("torch")
-        if torch is not None and any(not a.host for a in arrays):
-            stream = _torch_stream(torch, self.device)
+        if torch is not None and (any(not a.host for a in arrays) or self.options.get("distribute")):
+            stream = _torch_stream(torch, self.device)     # orders with torch ops and with collectives
         else:
             stream = rt.stream(0)
         self._acquire_device(arrays, stream)
@@ -499,6 +578,13 @@ class CompiledLoop:
         scope = self._scope(args, arrays)
         lo = int(eval(variant.lo_code, {}, scope))
         hi = int(eval(variant.hi_code, {}, scope))
+        cells = []
+        if self.options.get("distribute"):
+            lo, hi = self._rank_range(variant, arrays, lo, hi)
+            from . import multi_gpu
+            if multi_gpu.world()[1] > 1 and self.options.get("combine") != "p2p":
+                cells = self._reduction_cells(args, arrays)
+                self._pre_combine(cells)
         if hi > lo:
             tun = variant.tun
             if not variant.tuned:
@@ -519,9 +605,12 @@ class CompiledLoop:
                     self.memo.clear()
                 kinds = [p.kind for p in variant.plan.params]
                 seq_slot = kinds.index("seq") if "seq" in kinds else None
-                self.memo[mkey] = (h, grid, block, smem, pack, seq_slot, stream if variant.plan.uses_ws else None)
+                self.memo[mkey] = (h, grid, block, smem, pack, seq_slot,
+                                   stream if variant.plan.uses_ws else None, cells)
         elif not any_host:
-            self.memo[mkey] = (0, 0, 0, 0, None, None, None)
+            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells)
+        if cells:
+            self._post_combine(cells)
         if any_host:
             for a in arrays:
                 if a.host and a.name in self.stored and a.nbytes:
@@ -532,6 +621,21 @@ class CompiledLoop:
                     if a.name in self.stored:
                         a.obj[...] = a.tmp
                     rt.check(rt.lib().appy_evict(C.c_void_p(a.hptr)))    # the contiguous copy dies with this call
+
+    def _pre_combine(self, cells):
+        """Every rank starts from the same initial value b0; only rank 0 keeps it, so that the
+        all-reduce after the kernel yields b0 (op) total and not world * b0 (op) total."""
+        from . import multi_gpu
+        if multi_gpu.world()[0] == 0:
+            return
+        for view, op in cells:
+            if op in _IDENTITY:
+                view.fill_(_IDENTITY[op])
+
+    def _post_combine(self, cells):
+        from . import multi_gpu
+        for view, op in cells:
+            multi_gpu.all_reduce(view, op)
 
     # convenience for tests and dumps
     def source_for(self, *args) -> str:
@@ -566,7 +670,7 @@ def _register_finalizer(obj, hptr: int) -> None:
         pass
 
 
-_OPTION_KEYS = ("ordered_reduction", "combine", "fp_contract", "autotune", "pin_host", "_generic_only", "_vectorize",
+_OPTION_KEYS = ("ordered_reduction", "combine", "distribute", "fp_contract", "autotune", "pin_host", "_generic_only", "_vectorize",
                 "_stream_hint", "_hoist_safe", "_shape_spec")
 
 

@@ -63,6 +63,58 @@ def test_missing_rank_times_out_with_a_status_not_a_hang(rt):
         mg.set_combiner(None)
 
 
+@appy.jit(distribute=True)
+def d_vec_add(a, b, c):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        c[i] = a[i] + b[i]
+
+
+@appy.jit(distribute=True)
+def d_sum(a):
+    s = 1.5
+    #pragma parallel for simd shared(s)
+    for i in range(a.shape[0]):
+        s += a[i]
+    return s
+
+
+@appy.jit(distribute=True, combine="p2p")
+def d_sum_p2p(a):
+    s = 1.5
+    #pragma parallel for simd shared(s)
+    for i in range(a.shape[0]):
+        s += a[i]
+    return s
+
+
+@appy.jit(distribute=True)
+def d_spmv(A_data, A_indptr, A_indices, x, y, M):
+    #pragma parallel for
+    for i in range(M):
+        start, end = A_indptr[i], A_indptr[i+1]
+        s = 0.0
+        #pragma simd
+        for j in range(start, end):
+            s += A_data[j] * x[A_indices[j]]
+        y[i] = s
+
+
+@appy.jit(distribute=True)
+def d_scatter(idx, out):
+    #pragma parallel for simd
+    for i in range(idx.shape[0]):
+        out[idx[i]] = 1.0
+
+
+def test_distribute_on_one_rank_is_the_plain_loop(rt):
+    a, b = W.vec_add(10001, seed=1)
+    c = np.empty_like(a)
+    d_vec_add(a, b, c)
+    assert np.array_equal(c, a + b)
+    assert np.isclose(d_sum(a), 1.5 + float(np.sum(a, dtype=np.float64)), rtol=1e-6)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -91,6 +143,33 @@ def _rank_main(rank, world, port, out_dir):
             assert np.isclose(s, total, rtol=1e-5, atol=0), (rank, s, total)
             assert m == big
         assert not comb.timed_out()
+        # ---- the iteration space split over the ranks (`distribute=True`), replicated inputs
+        x, y = W.vec_add(100003, seed=7)
+        z = np.full_like(x, np.nan)
+        d_vec_add(x, y, z)                                   # every rank fills only its range
+        lo, hi = mg.split_range(0, x.size, world, rank)
+        assert np.array_equal(z[lo:hi], (x + y)[lo:hi]) and np.all(np.isnan(np.delete(z, np.s_[lo:hi])))
+        ref = 1.5 + float(np.sum(x, dtype=np.float64))
+        assert np.isclose(d_sum(x), ref, rtol=1e-6)          # NCCL/gloo combine of the shared scalar
+        assert np.isclose(d_sum(torch.from_numpy(x).cuda()), ref, rtol=1e-6)
+        assert np.isclose(d_sum_p2p(torch.from_numpy(x).cuda()), ref, rtol=1e-6)   # mailbox combine
+        A, xv = W.spmv(20000, 16, kind="zipf", cap=2048, seed=8)
+        yv = np.full(A.shape[0], np.nan, np.float32)
+        d_spmv(A.data, A.indptr, A.indices, xv, yv, A.shape[0])
+        r0, r1 = mg.split_rows(A.indptr, world, rank)        # rows balanced by non-zeros
+        from oracle import numpy_oracle as O
+        full = O.spmv(A.data, A.indptr, A.indices, xv)
+        scale = O.spmv_abs(A.data, A.indptr, A.indices, xv)
+        assert np.all(np.abs(yv[r0:r1] - full[r0:r1]) <= 1e-5 * scale[r0:r1] + 1e-30)
+        assert np.all(np.isnan(yv[:r0])) and np.all(np.isnan(yv[r1:]))
+        pieces = [None] * world
+        dist.all_gather_object(pieces, (r0, r1))
+        assert sorted(pieces)[0][0] == 0 and sorted(pieces)[-1][1] == A.shape[0]
+        try:
+            d_scatter(np.arange(10, dtype=np.int64), np.zeros(10))
+            raise AssertionError("a scattered store must not be distributable")
+        except NotImplementedError:
+            pass
         dist.barrier()
         comb.close()
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
