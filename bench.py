@@ -219,8 +219,10 @@ def _triton_arm():
         return None
 
 
-def kernel_table(torch, L, peak, rank, quick=False, with_triton=True):
-    """Per-configuration device timings through the jit path (device-resident inputs)."""
+def kernel_table(torch, L, peak, rank, quick=False, with_triton=True, world=1):
+    """Per-configuration device timings through the jit path (device-resident inputs).
+    With several ranks every rank runs its own full-size shard (weak scaling): the time is the
+    maximum over ranks and GB/s is the sum over ranks; `frac` stays per GPU."""
     from appy_b200 import workloads as W
     rows = {}
     dev = "cuda"
@@ -239,8 +241,13 @@ def kernel_table(torch, L, peak, rank, quick=False, with_triton=True):
             sys.stderr.write(f"[bench] Triton kernel for {name} failed: {e!r}\n")
 
     def add(name, byts, us, extra=None):
-        rows[name] = {"us": round(us, 2), "gbs": round(byts / us / 1e3, 1), "frac": round(byts / us / 1e3 / peak, 4),
-                      "bytes": int(byts)}
+        if world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([us], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t.item())
+        rows[name] = {"us": round(us, 2), "gbs": round(world * byts / us / 1e3, 1),
+                      "frac": round(byts / us / 1e3 / peak, 4), "bytes": int(byts)}
         if extra:
             rows[name].update(extra)
 
@@ -432,6 +439,8 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # NCCL writes its version banner to stdout; stdout is reserved for the one JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", os.path.join(tempfile.gettempdir(), "appy_bench_nccl.%h.%p.log"))
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     from appy_b200 import workloads as W
     from appy_b200.backends.cuda_sm100 import runtime as rt
@@ -523,6 +532,10 @@ def main():
     # ---- roofline of the dominant kernel, timed alone on the launch stream
     us_sum = time_kernel(torch, lambda i: L.sum_into(a, out_a), 1, 100)
     us_msk = time_kernel(torch, lambda i: L.masked_sum_into(a, m, out_b), 1, 100)
+    if world > 1:      # per-kernel times: maximum over ranks
+        tk = torch.tensor([us_sum, us_msk], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tk, op=dist.ReduceOp.MAX)
+        us_sum, us_msk = float(tk[0].item()), float(tk[1].item())
     dom_bytes, dom_us, dom_name = (W.bytes_masked_sum(n), us_msk, "masked sum (T2 reduction template)") \
         if us_msk >= us_sum else (W.bytes_sum(n), us_sum, "sum (T2 reduction template)")
     achieved = dom_bytes / dom_us / 1e3
@@ -549,8 +562,9 @@ def main():
 
     table = {}
     if not args.no_table:
-        table = kernel_table(torch, L, peak, rank, quick=args.quick_table, with_triton=(rank == 0))
-        TK = _triton_arm() if rank == 0 else None
+        table = kernel_table(torch, L, peak, rank, quick=args.quick_table, with_triton=(rank == 0 and world == 1),
+                             world=world)
+        TK = _triton_arm() if (rank == 0 and world == 1) else None
         tri_sum = tri_msk = tri_if = None
         if TK is not None:
             try:
@@ -560,11 +574,11 @@ def main():
                 tri_if = time_kernel(torch, lambda i: TK.masked_sum_if(a, m, tb), 1, 2, warm=1)
             except Exception as e:
                 sys.stderr.write(f"[bench] Triton reduction kernels failed: {e!r}\n")
-        table["C2a sum f32 n=2^26"] = {"us": round(us_sum, 2), "gbs": round(W.bytes_sum(n) / us_sum / 1e3, 1),
+        table["C2a sum f32 n=2^26"] = {"us": round(us_sum, 2), "gbs": round(world * W.bytes_sum(n) / us_sum / 1e3, 1),
                                        "frac": round(W.bytes_sum(n) / us_sum / 1e3 / peak, 4),
                                        "bytes": W.bytes_sum(n), "l2": "256 MiB input"}
         table["C2b masked sum f32+bool n=2^26"] = {"us": round(us_msk, 2),
-                                                   "gbs": round(W.bytes_masked_sum(n) / us_msk / 1e3, 1),
+                                                   "gbs": round(world * W.bytes_masked_sum(n) / us_msk / 1e3, 1),
                                                    "frac": round(W.bytes_masked_sum(n) / us_msk / 1e3 / peak, 4),
                                                    "bytes": W.bytes_masked_sum(n), "l2": "320 MiB input"}
         if tri_sum:
