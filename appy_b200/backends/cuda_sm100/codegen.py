@@ -139,7 +139,8 @@ def _torch_stream(torch, device: int) -> int:
 
 class _Array:
     """One array argument resolved for a launch."""
-    __slots__ = ("name", "obj", "host", "dptr", "nbytes", "shape", "strides", "itemsize", "tmp", "hptr")
+    __slots__ = ("name", "obj", "host", "dptr", "nbytes", "shape", "strides", "itemsize", "tmp", "hptr",
+                 "pinnable")
 
 
 class _DevView:
@@ -201,6 +202,7 @@ class CompiledLoop:
                 continue
             a = _Array()
             a.name, a.obj, a.tmp, a.hptr = name, v, None, 0
+            a.pinnable = sig[1] == "np"      # NumPy owners can be tracked by a finaliser; tensor views cannot
             if sig[1] == "cuda":
                 a.host = False
                 a.dptr = v.data_ptr()
@@ -233,7 +235,8 @@ class CompiledLoop:
                 continue
             a.dptr, _created = rt.mirror(a.hptr, a.nbytes)
             pinned = a.hptr in _finalizers
-            if a.nbytes >= _PIN_MIN_BYTES and a.tmp is None and self.options.get("pin_host", True) and not pinned:
+            if a.nbytes >= _PIN_MIN_BYTES and a.tmp is None and a.pinnable and self.options.get("pin_host", True) \
+                    and not pinned:
                 if len(_seen_host) > 4096:
                     _seen_host.clear()
                 seen = _seen_host.get(a.hptr, 0) + 1
@@ -369,9 +372,8 @@ class CompiledLoop:
                 if trip >= 8192 * max(1, plan.vec) // 4 and plan.kind == "group":
                     g = 0
                 variant.tun["P_G"] = g
-        return {}
 
-    def _csr_overrides(self, variant: Variant, arrays) -> dict:
+    def _csr_overrides(self, variant: Variant, arrays, stream) -> dict:
         """Lanes per row from the row-length histogram of this matrix (cached per indptr buffer)."""
         plan = variant.plan
         if plan.kind != "csr" or not plan.info.get("indptr"):
@@ -384,7 +386,7 @@ class CompiledLoop:
         if ckey not in cache:
             if len(cache) > 64:
                 cache.clear()
-            counts, _mx = rt.row_histogram(ip.dptr, ip.itemsize, ip.shape[0] - 1)
+            counts, _mx = rt.row_histogram(ip.dptr, ip.itemsize, ip.shape[0] - 1, stream)
             total = sum(counts)
             acc, med = 0, 0
             for b, c in enumerate(counts):      # median row-length bin decides the lanes per row
@@ -588,7 +590,7 @@ class CompiledLoop:
         if hi > lo:
             tun = variant.tun
             if not variant.tuned:
-                ov = self._csr_overrides(variant, arrays)      # host arrays: mirrors are uploaded by now
+                ov = self._csr_overrides(variant, arrays, stream)   # on the stream the uploads were queued on
                 self._heuristics(variant, scope, arrays)
                 self._settle(variant)
                 if self._want_autotune() and not variant.tuned:

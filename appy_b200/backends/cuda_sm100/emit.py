@@ -109,7 +109,6 @@ class Emitter:
         self.load_override: dict[str, tuple[str, Ty]] = {}     # text of a Subscript/Name -> (code, type)
         self.store_override: dict[str, object] = {}            # text of a target -> callable(code, ty) -> [lines]
         self.store_guard: str | None = None                    # e.g. "g.lane == 0" for scalar stores in group mode
-        self.idx32 = False
 
     # ------------------------------------------------------------------ names
     def _implicit(self, name: str):
@@ -124,9 +123,8 @@ class Emitter:
 
     def name(self, node: ast.Name):
         n = node.id
-        key = n
-        if key in self.load_override:
-            return self.load_override[key]
+        if n in self.load_override:
+            return self.load_override[n]
         e = self.env
         if n in e.indices:
             return (n, e.indices[n])

@@ -26,7 +26,7 @@ from dataclasses import dataclass, field
 from ...frontend.loop_normalize import LoopIR, reductions_of
 from . import dtypes as T
 from .dtypes import Ty
-from .emit import ArraySym, Emitter, Env, ScalarSym, cast, float_literal
+from .emit import ArraySym, Emitter, Env, ScalarSym, cast
 
 OPS = {"+": "appy_add", "*": "appy_mul", "max": "appy_max", "min": "appy_min"}
 
@@ -774,7 +774,7 @@ class Lowering:
         coef_c = em.as_type(coef, elt)
         row_c, row_t = em.expr(belts[0])
         a_b, a_c = self.args[bname], self.args[cname]
-        V = max(1, 16 // elt.bits * 8 // 8) if False else (16 // (elt.bits // 8))
+        V = 16 // (elt.bits // 8)              # elements per 16-byte pack
         vec_ok = (a_b.aligned and a_c.aligned and a_b.strides_vec_ok.get(V, False)
                   and a_c.strides_vec_ok.get(V, False) and ncols % V == 0 and self.options.get("_vectorize", True))
         if not vec_ok:
@@ -782,9 +782,8 @@ class Lowering:
         Tn = (ncols + 32 * V - 1) // (32 * V)
         if Tn > 16:
             return None
-        for nm in (f"{bname}_stride_0", f"{cname}_stride_0"):
-            arr, kind, dim = nm.rsplit("_", 2)[0], "stride", 0
-            env.implicit[nm] = (arr, kind, dim)
+        env.implicit[f"{bname}_stride_0"] = (bname, "stride", 0)
+        env.implicit[f"{cname}_stride_0"] = (cname, "stride", 0)
         off_ty = "unsigned int" if a_b.small else "i64"
         nc = ncols if ncols == 32 * V * Tn else 0
         init_c = cast(*em.expr(z.body[0].value), elt)

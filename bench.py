@@ -105,8 +105,6 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------- jitted loops (the product path)
 def define_loops():
-    import appy_b200 as appy
-    g = {"appy": appy, "np": np}
     src = '''
 @appy.jit
 def sum_into(a, out):
