@@ -132,6 +132,37 @@ def _has_inner_simd(stmts) -> bool:
     return False
 
 
+def conditional_loads(stmts) -> set:
+    """ids of Subscript nodes that Python evaluates only under a condition: inside a nested
+    if/while/for statement, in a branch of a ternary, or after the first operand of and/or."""
+    out = set()
+
+    def mark(node):
+        for n in ast.walk(node):
+            if isinstance(n, ast.Subscript):
+                out.add(id(n))
+
+    def expr(node):
+        for n in ast.walk(node):
+            if isinstance(n, ast.IfExp):
+                mark(n.body)
+                mark(n.orelse)
+            elif isinstance(n, ast.BoolOp):
+                for v in n.values[1:]:
+                    mark(v)
+
+    for st in stmts:
+        if isinstance(st, (ast.If, ast.While, ast.For)):
+            for fld in ("body", "orelse"):
+                for inner in getattr(st, fld, []) or []:
+                    mark(inner)
+            if isinstance(st, (ast.If, ast.While)):
+                expr(st.test)
+        else:
+            expr(st)
+    return out
+
+
 def _last_index_offset(sub: ast.Subscript, var: str):
     """If the last index of `sub` is `var`, `var + c` or `var - c` (c an int literal) and no
     other index mentions `var`, return c; else None."""
@@ -444,6 +475,11 @@ class Lowering:
         # ---- vector path
         regs, load_lines, out_decl, out_store = [], [], [], []
         slot = {}
+        cond = conditional_loads(body)
+        cond_texts = {ast.unparse(n) for st in body for n in ast.walk(st)
+                      if isinstance(n, ast.Subscript) and id(n) in cond}
+        uncond_texts = {ast.unparse(n) for st in body for n in ast.walk(st)
+                        if isinstance(n, ast.Subscript) and isinstance(n.ctx, ast.Load) and id(n) not in cond}
         for text, (name, node) in loads.items():
             arr = env.arrays[name]
             s = f"l{len(slot)}"
@@ -452,7 +488,15 @@ class Lowering:
             off, _ = Emitter(env).offset(_replace_index(node, self.var, "__i0"))
             ld = "appy_ld_cs" if (arr.readonly and self.options.get("_stream_hint", True)) else \
                 ("appy_ld_nc" if arr.readonly else "appy_ld")
-            load_lines.append(f"__rg.{s} = {ld}<{arr.ty.c}, {V}>({name} + ({off}));")
+            line = f"__rg.{s} = {ld}<{arr.ty.c}, {V}>({name} + ({off}));"
+            if text in cond_texts and text not in uncond_texts:
+                # Python would evaluate this element only under a condition, so the array may be
+                # shorter than the iteration range: fetch the pack only when it lies inside the array
+                shape = f"{name}_shape_{arr.ndim - 1}"
+                env.implicit[shape] = (name, "shape", arr.ndim - 1)
+                line = (f"if (__i0 + {V} <= {shape}) {line} else {{ for (int __k = 0; __k < {V}; ++__k) "
+                        f"__rg.{s}.v[__k] = (__i0 + __k < {shape}) ? {name}[({off}) + __k] : {arr.ty.c}(0); }}")
+            load_lines.append(line)
         if V > 1:
             saved_l, saved_s = dict(em.load_override), dict(em.store_override)
             for text, s in slot.items():
@@ -635,9 +679,10 @@ class Lowering:
                 V = max(1, 16 // max(sizes))
         streams = {}
         if V > 1:
+            lazy = conditional_loads([ast.Expr(value=term)])      # evaluated only under a condition: keep scalar
             for n in _subscripts(term):
                 a = self.args.get(n.value.id)
-                if a is None or a.kind != "array":
+                if a is None or a.kind != "array" or id(n) in lazy:
                     continue
                 if _last_index_offset(n, jvar) == 0 and a.unit_last and a.aligned and a.strides_vec_ok.get(V, False):
                     elts = n.slice.elts if isinstance(n.slice, ast.Tuple) else [n.slice]

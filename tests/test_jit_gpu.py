@@ -621,3 +621,30 @@ def test_kernel_cache_is_reused():
     n_entries = len(cg.code_cache)
     k_vec_add(a, b, c)
     assert len(cg.code_cache) == n_entries
+
+
+def test_conditionally_read_array_may_be_shorter_than_the_range():
+    """`a[i] if i < m else 0` must not touch a[] beyond m, also on the 16-byte vector path."""
+    @appy.jit
+    def guarded(a, m, out):
+        #pragma parallel for simd
+        for i in range(out.shape[0]):
+            out[i] = a[i] * 2.0 if i < m else -1.0
+
+    @appy.jit
+    def guarded_sum(a, m, n):
+        s = 0.0
+        #pragma parallel for simd shared(s)
+        for i in range(n):
+            if i < m:
+                s += a[i]
+        return s
+
+    import torch
+    for m in (6, 1023, 4096):
+        a = torch.arange(m, dtype=torch.float32, device="cuda")
+        out = torch.empty(m + 37, dtype=torch.float32, device="cuda")
+        guarded(a, m, out)
+        exp = np.concatenate([np.arange(m, dtype=np.float32) * 2, -np.ones(37, np.float32)])
+        assert np.array_equal(out.cpu().numpy(), exp)
+        assert guarded_sum(a, m, m + 37) == float(np.arange(m, dtype=np.float64).sum())
