@@ -30,6 +30,14 @@ from .emit import ArraySym, Emitter, Env, ScalarSym, cast
 
 OPS = {"+": "appy_add", "*": "appy_mul", "max": "appy_max", "min": "appy_min"}
 
+# Python identifiers that cannot be used as C++ identifiers in the generated kernel
+CXX_RESERVED = frozenset("""alignas alignof asm auto bitand bitor bool case catch char char16_t char32_t compl const
+constexpr const_cast decltype default delete do double dynamic_cast enum explicit export extern float friend goto
+inline int long mutable namespace new noexcept not_eq nullptr operator or_eq private protected public register
+reinterpret_cast short signed sizeof static static_assert static_cast struct switch template this thread_local throw
+typedef typeid typename union unsigned using virtual void volatile wchar_t xor xor_eq and_eq
+i64 u64 u32 u8 threadIdx blockIdx blockDim gridDim warpSize""".split())
+
 
 @dataclass
 class Param:
@@ -206,6 +214,13 @@ class Lowering:
                 self.env.modules.add(a.name)
         self.env.modules |= {"np", "numpy", "math"}
         self.var = self.loop.target.id
+        callees = {id(n.func) for n in ast.walk(self.loop) if isinstance(n, ast.Call)}
+        for n in ast.walk(self.loop):
+            if isinstance(n, ast.Name) and id(n) not in callees \
+                    and (n.id in CXX_RESERVED or n.id.startswith("__")) and not n.id.startswith(("__s", "__r")):
+                raise NotImplementedError(
+                    f"the name `{n.id}` cannot be used inside a parallel loop: it is reserved in the generated "
+                    f"CUDA C (rename the variable)")
         self.env.indices[self.var] = T.WEAK_INT
         self.env.indices["__i0"] = T.I64
         self.env.indices["__j0"] = T.I64

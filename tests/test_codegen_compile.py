@@ -117,3 +117,17 @@ def test_argument_order_follows_first_use():
     plan, _ = build(src, scope)
     names = [p.name for p in plan.params]
     assert names[:6] == ["M", "P", "D", "x", "J", "y"] and names[-2:] == ["__lo", "__hi"]
+
+
+def test_reserved_identifiers_and_builtin_casts():
+    build("#pragma parallel for simd\nfor i in range(n):\n    c[i] = float(int(a[i])) + float('inf') * 0.0 if bool(a[i]) else 1.0",
+          dict(a=A1, c=A1.copy(), n=4))
+    with pytest.raises(NotImplementedError) as e:
+        build("#pragma parallel for simd\nfor i in range(n):\n    register = a[i]\n    c[i] = register", dict(a=A1, c=A1.copy(), n=4))
+    assert "register" in str(e.value)
+
+
+def test_row_max_via_slice_reduction():
+    plan, code = build("#pragma parallel for\nfor i in range(n):\n    y[i] = np.max(A[i, :]) - np.min(A[i, :])",
+                       dict(A=np.ones((8, 8)), y=np.ones(8), n=8))
+    assert plan.kind == "group" and "appy_max" in code and "appy_min" in code
