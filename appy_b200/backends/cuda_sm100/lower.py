@@ -359,14 +359,14 @@ class Lowering:
                 # this GPU's totals, then the exchange with the other ranks inside the same kernel
                 for r, (op, ty, acc, _n) in enumerate(items):
                     out.append(f"  {ty.c} __t{r} = appy_ws_collect<{OPS[op]}, {ty.c}>(__w, {r}, __smem);")
-                out.append("  if (threadIdx.x == 0) {")
-                for r, (op, ty, acc, _n) in enumerate(items):
-                    out.append(f"    appy_p2p_post<{ty.c}>(__mb, __seq, {r}, __t{r});")
-                out.append("    appy_p2p_publish(__mb, __seq);")
-                out.append("    appy_p2p_wait(__mb, __seq);")
+                # first warp: lane r exchanges with rank r, then the warp folds in rank order
+                out.append("  if (threadIdx.x < 32) {")
+                bits = ", ".join(f"appy_to_bits<{ty.c}>(__t{r})" for r, (op, ty, acc, _n) in enumerate(items))
+                out.append(f"    u64 __x[{len(items)}] = {{{bits}}};")
+                out.append(f"    appy_p2p_exchange<{len(items)}>(__mb, __seq, __x);")
                 for r, ((op, ty, acc, _n), addr) in enumerate(zip(items, addrs)):
-                    out.append(f"    __t{r} = appy_p2p_fold<{OPS[op]}, {ty.c}>(__mb, __seq, {r});")
-                    out.append(f"    *{addr} = {OPS[op]}::op<{ty.c}>(*{addr}, __t{r});")
+                    out.append(f"    __t{r} = appy_p2p_fold<{OPS[op]}, {ty.c}>(__mb, __x[{r}]);")
+                    out.append(f"    if (threadIdx.x == 0) *{addr} = {OPS[op]}::op<{ty.c}>(*{addr}, __t{r});")
                 out.append("  }")
             else:
                 for r, ((op, ty, acc, _n), addr) in enumerate(zip(items, addrs)):

@@ -128,37 +128,34 @@ template <class Op, class T> APPY_DEV T appy_ws_collect(const appy_ws& w, int va
 //
 // Every rank (one process per GPU) owns a mailbox in its own HBM and holds peer pointers to
 // the mailboxes of all ranks (CUDA IPC mappings; NVLink/NVSwitch).  After the ordered commit
-// has produced this GPU's totals, one thread of the last CTA
-//   1. writes the totals into its slot of EVERY rank's mailbox with plain stores over NVLink,
-//      then publishes them with a release store of the launch's sequence number;
-//   2. waits (bounded) until the slots of all ranks in its OWN mailbox carry that sequence
-//      number, and folds them in rank order, so every rank obtains the same bits.
-// No kernel reads a peer's memory for data-path operands; only these few words cross GPUs.
-// Slots are double-buffered by sequence parity: a rank can be at most one launch ahead of
-// the slowest rank, because finishing launch s needs every rank's flag s.
-// The wait is limited; on expiry the error word is set and the partial result is used, so
-// a missing rank makes the launch return with a status the host reads, never a hang.
+// has produced this GPU's totals, the first warp of the last CTA runs the exchange, lane r
+// talking to rank r:
+//   1. lane r stores the totals into this rank's slot of rank r's mailbox;
+//   2. lane r polls (bounded) the slot of rank r in this rank's OWN mailbox;
+//   3. the warp folds the world's totals in rank order, so every rank obtains the same bits.
+// A value travels as 8-byte words {32 payload bits, 32-bit tag of the launch}: an aligned
+// 8-byte store is single-copy atomic, payload and tag arrive together, and neither side needs
+// a fence or a separate flag (the scheme of low-latency collective protocols).  A total of up
+// to 8 bytes takes two words.  No kernel reads a peer's memory; only these words cross GPUs.
+// Slots are double-buffered by the parity of the launch sequence number: a rank can be at most
+// one launch ahead of the slowest rank, because finishing launch s needs every rank's words
+// of launch s.  The tag is the low 31 bits of s with bit 31 set, so it differs from the tag
+// two launches earlier and from freshly zeroed memory.
+// The wait is limited; on expiry the error word is set and whatever the slot holds is used,
+// so a missing rank makes the launch return with a status the host reads, never a hang.
 //
-// Mailbox of one rank: [parity 0..1][source rank 0..world-1] x 8 words of 8 bytes:
-// word 0 = sequence flag, words 1..4 = values of up to 4 reduction variables.
+// Mailbox of one rank: [parity 0..1][source rank 0..world-1] x 8 words of 8 bytes;
+// variable v (up to 4 per loop) uses words 2v (low half) and 2v+1 (high half).
 // ---------------------------------------------------------------------------
 struct appy_mailbox {
   int world;
   int rank;
-  unsigned spin_limit;      // polls per source rank before giving up (about 1 us each)
+  unsigned spin_limit;      // polls per source rank before giving up (20 ns, later 1 us apart)
   unsigned reserved;
   unsigned* err;            // set to 1 when a wait ran out
   u64* peer[16];            // peer[r] = mailbox of rank r as mapped into this process
 };
 
-APPY_DEV void appy_st_release_sys(u64* p, u64 v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-APPY_DEV u64 appy_ld_acquire_sys(const u64* p) {
-  u64 v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
 APPY_DEV void appy_st_relaxed_sys(u64* p, u64 v) {
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
@@ -180,42 +177,47 @@ template <class T> APPY_DEV T appy_from_bits(u64 u) {
   return x.t;
 }
 
-// step 1 for variable `var`; call for every variable, then appy_p2p_publish once
-template <class T> APPY_DEV void appy_p2p_post(const appy_mailbox* mb, u64 seq, int var, T v) {
+// Steps 1 and 2, called by the 32 threads of warp 0.  In: x[v] = this rank's total of variable v
+// (raw bits, same in every lane).  Out: in lane r < world, x[v] = rank r's total of variable v.
+template <int NV> APPY_DEV void appy_p2p_exchange(const appy_mailbox* mb, u64 seq, u64 (&x)[NV]) {
   const int world = mb->world, rank = mb->rank;
-  const u64 bits = appy_to_bits<T>(v);
-  for (int p = 0; p < world; ++p)
-    appy_st_relaxed_sys(mb->peer[p] + ((seq & 1) * world + rank) * 8 + 1 + var, bits);
-}
-APPY_DEV void appy_p2p_publish(const appy_mailbox* mb, u64 seq) {
-  const int world = mb->world, rank = mb->rank;
-  __threadfence_system();
-  for (int p = 0; p < world; ++p) appy_st_release_sys(mb->peer[p] + ((seq & 1) * world + rank) * 8, seq);
-}
-// step 2: returns false if some rank's flag did not arrive within the limit
-APPY_DEV bool appy_p2p_wait(const appy_mailbox* mb, u64 seq) {
-  const int world = mb->world, rank = mb->rank;
-  bool ok = true;
-  for (int r = 0; r < world; ++r) {
-    const u64* flag = mb->peer[rank] + ((seq & 1) * world + r) * 8;
-    unsigned spins = 0;
-    while (appy_ld_acquire_sys(flag) < seq) {
-      if (++spins > mb->spin_limit) {
-        ok = false;
-        break;
-      }
-      __nanosleep(spins < 64 ? 20 : 1000);
+  const int lane = threadIdx.x & 31;
+  const u64 tag = (u64)((unsigned)seq | 0x80000000u) << 32;
+  if (lane < world) {
+    u64* dst = mb->peer[lane] + ((seq & 1) * world + rank) * 8;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      appy_st_relaxed_sys(dst + 2 * v, tag | (x[v] & 0xffffffffull));
+      appy_st_relaxed_sys(dst + 2 * v + 1, tag | (x[v] >> 32));
     }
-    if (!ok) break;
+    const u64* src = mb->peer[rank] + ((seq & 1) * world + lane) * 8;
+    const unsigned limit = mb->spin_limit;
+    unsigned spins = 0;
+    bool ok = true;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      u64 lo, hi;
+      for (;;) {
+        lo = appy_ld_relaxed_sys(src + 2 * v);
+        hi = appy_ld_relaxed_sys(src + 2 * v + 1);
+        if (((lo ^ tag) >> 32) == 0 && ((hi ^ tag) >> 32) == 0) break;
+        if (!ok || ++spins > limit) {
+          ok = false;
+          break;
+        }
+        __nanosleep(spins < 256 ? 20 : 1000);
+      }
+      x[v] = (hi << 32) | (lo & 0xffffffffull);
+    }
+    if (!ok) atomicExch(mb->err, 1u);
   }
-  if (!ok) atomicExch(mb->err, 1u);
-  return ok;
+  __syncwarp();
 }
-template <class Op, class T> APPY_DEV T appy_p2p_fold(const appy_mailbox* mb, u64 seq, int var) {
-  const int world = mb->world, rank = mb->rank;
+// Step 3, called by the 32 threads of warp 0 with lane r holding rank r's total.
+template <class Op, class T> APPY_DEV T appy_p2p_fold(const appy_mailbox* mb, u64 bits) {
+  const int world = mb->world;
   T total = Op::template id<T>();
   for (int r = 0; r < world; ++r)
-    total = Op::template op<T>(total, appy_from_bits<T>(appy_ld_relaxed_sys(
-                                          mb->peer[rank] + ((seq & 1) * world + r) * 8 + 1 + var)));
+    total = Op::template op<T>(total, appy_from_bits<T>(__shfl_sync(0xffffffffu, bits, r)));
   return total;
 }

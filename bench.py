@@ -8,7 +8,8 @@ Bernoulli(0.5) bool mask — run through ``@appy_b200.jit``.  A step is one pass
 and one of (b).  ``value`` is effective HBM GB/s: algorithmic bytes (4n + 5n per step
 and GPU) divided by the device time of K steps, inputs resident in HBM, all GPUs
 summed (weak scaling: every rank owns a full-size shard; for N > 1 the two result
-scalars are combined by an NCCL all-reduce inside the timed region).  ``e2e`` is the
+scalars are combined inside the timed region, by default through peer mailboxes
+written by the reduction kernels themselves, with ``--combine nccl`` by an all-reduce).  ``e2e`` is the
 same metric through the public API with NumPy host buffers: host-to-device copies of
 the inputs and the device-to-host read of the result are inside the timed region.
 ``kernels`` adds one line per benchmark configuration (C1..C5) with the kernel's own
@@ -417,9 +418,10 @@ def main():
                     help="run a single configuration's kernel --steps times and exit (for profilers): "
                          "vec_add, sum, masked_sum, gemv, spmv_poisson, spmv_zipf, spmm")
     ap.add_argument("--scale", type=int, default=1, help="with --only: divide the problem size by this factor")
-    ap.add_argument("--combine", default="nccl", choices=["nccl", "p2p"],
-                    help="N > 1: how the two result scalars are combined across GPUs: an NCCL all-reduce "
-                         "per step, or peer mailboxes inside the reduction kernels (no collective call)")
+    ap.add_argument("--combine", default="p2p", choices=["nccl", "p2p"],
+                    help="N > 1: how the two result scalars are combined across GPUs: peer mailboxes inside "
+                         "the reduction kernels (no collective call; falls back to NCCL when peer mappings "
+                         "cannot be made), or an NCCL all-reduce per step")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -460,7 +462,15 @@ def main():
     use_p2p = world > 1 and args.combine == "p2p"
     if use_p2p:
         from appy_b200.backends.cuda_sm100 import multi_gpu as mg
-        combiner = mg.enable_p2p()
+        try:
+            combiner = mg.enable_p2p()
+            mapped = 1
+        except Exception as exc:                  # no peer access between some pair of GPUs
+            sys.stderr.write(f"[bench] rank {rank}: peer mailboxes unavailable ({exc}); using NCCL\n")
+            mapped = 0
+        flag = torch.tensor([mapped], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)       # every rank takes the same path
+        use_p2p = bool(flag.item())
 
     def step():
         out.zero_()

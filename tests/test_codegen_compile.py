@@ -96,6 +96,15 @@ def test_ordered_reduction_uses_the_workspace():
     assert plan.params[-1].kind == "ws"
 
 
+def test_peer_mailbox_combine_compiles_and_is_fused_into_the_reduction_kernel():
+    src = ("#pragma parallel for simd shared(b, c)\nfor i in range(n):\n"
+           "    b[0] += a[i]\n    c[0] = max(c[0], a[i])")
+    plan, code = build(src, dict(a=A1, b=np.array([0.0]), c=np.array([0.0], f32), n=1000), combine="p2p")
+    assert plan.uses_ws and [p.kind for p in plan.params][-2:] == ["mb", "seq"]
+    assert "appy_p2p_exchange<2>" in code and "appy_p2p_fold<appy_add, double>" in code
+    assert "appy_p2p_fold<appy_max, float>" in code
+
+
 def test_unaligned_or_strided_arrays_fall_back_to_scalar_accesses():
     a = np.ones(1001, f32)[1:]          # 4-byte aligned only: host arrays are mirrored, so still aligned
     t = pytest.importorskip("torch")
