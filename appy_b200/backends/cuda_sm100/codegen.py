@@ -372,6 +372,14 @@ class CompiledLoop:
                 if trip >= 8192 * max(1, plan.vec) // 4 and plan.kind == "group":
                     g = 0
                 variant.tun["P_G"] = g
+                if plan.kind == "rowdot" and plan.vec > 1 and trip >= 1024 * plan.vec:
+                    # Long dense rows: one CTA per pair of rows, eight 16-byte chunks per lane and row in
+                    # flight.  Few, deep streams (two resident CTAs per SM) read long contiguous bursts of
+                    # each row, which keeps DRAM pages open; thousands of concurrent warp-per-row streams
+                    # were measured 20 % slower on a 16384 x 16384 matrix.
+                    light = plan.info.get("streams", 9) <= 2
+                    variant.tun.update({"P_G": 0, "P_BLOCK": 256, "P_U": 8 if light else 4, "P_R": 2 if light else 1,
+                                        "P_MINB": 2})
 
     def _csr_overrides(self, variant: Variant, arrays, stream) -> dict:
         """Lanes per row from the row-length histogram of this matrix (cached per indptr buffer)."""

@@ -73,7 +73,8 @@ class KernelPlan:
             return min(grid, 2 ** 31 - 1), block, 0
         if k in ("group", "rowdot"):
             block, g = tun["P_BLOCK"], tun["P_G"]
-            groups = n_iter if g == 0 else (n_iter * g + block - 1) // block
+            units = (n_iter + tun.get("P_R", 1) - 1) // tun.get("P_R", 1)      # R rows per group at once
+            groups = units if g == 0 else (units * g + block - 1) // block
             per_sm = tun.get("P_CTAS", 0)
             grid = groups if per_sm == 0 else min(groups, sm_count * per_sm)
             return max(1, min(grid, 2 ** 31 - 1)), block, 0
@@ -98,6 +99,11 @@ class ArgInfo:
     strides_vec_ok: dict = field(default_factory=dict)   # V -> all leading strides % V == 0
     itemsize: int = 0
     small: bool = False       # every element offset fits in 31 bits
+
+
+# P_MINB > 0 states the resident CTAs per SM a kernel is meant for (second argument of
+# __launch_bounds__); 0 leaves the choice to the compiler
+MINB_MACRO = "#if P_MINB > 0\n#define APPY_MINB_ARG , P_MINB\n#else\n#define APPY_MINB_ARG\n#endif"
 
 
 # --------------------------------------------------------------------------- analysis helpers
@@ -546,10 +552,14 @@ class Lowering:
         src += ["  " + l for l in load_fn + compute + one + finish]
         src += ["};"]
         src += self._kernel_wrapper(params, struct, f"appy_flat<{V}, P_U>(__body, __lo, __hi, __smem);",
-                                    "__shared__ double __smem[33];", self._reduction_init())
-        tun = {"P_BLOCK": [256, 128, 512], "P_U": [1, 2, 4, 8] if V > 1 else [1, 2, 4]}
+                                    "__shared__ double __smem[33];", self._reduction_init(),
+                                    launch_bounds="P_BLOCK APPY_MINB_ARG")
+        src.insert(1, MINB_MACRO)
+        tun = {"P_BLOCK": [256, 128, 512], "P_U": [1, 2, 4, 8] if V > 1 else [1, 2, 4], "P_MINB": [0, 1, 2]}
         if self.reductions:
-            tun = {"P_BLOCK": [256, 512], "P_U": [4, 2, 8], "P_CTAS": [8, 4, 2]}
+            # default: 512-thread CTAs, two per SM, open register budget (measured 4-5 % faster on the
+            # 2^26-element sums than 256-thread CTAs at eight per SM)
+            tun = {"P_BLOCK": [512, 256], "P_U": [4, 2, 8], "P_CTAS": [2, 4, 8], "P_MINB": [1, 0, 2]}
         return KernelPlan("flat", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr,
                           uses_ws=ordered, vec=V,
                           info={"template": "T2 shared-scalar reduction" if self.reductions else "T1 elementwise",
@@ -743,12 +753,17 @@ class Lowering:
                ["    " + l for l in pre_block] + \
                [f"    {acc_ty.c} {acc_name} = {opc}::op<Acc>({init_c}, __total);"] + \
                ["    " + l for l in params_decl_suffix] + ["  }", "};"]
-        src += self._kernel_wrapper(params, struct, f"appy_rowdot<P_G, {V}, P_U>(__body, __lo, __hi, __smem);",
-                                    "__shared__ double __smem[33];")
-        tun = {"P_G": [32, 0, 8, 4, 16], "P_BLOCK": [128, 256, 512], "P_U": [4, 2, 8]}
+        src += self._kernel_wrapper(params, struct, f"appy_rowdot<P_G, {V}, P_U, P_R>(__body, __lo, __hi, __smem);",
+                                    "__shared__ double __smem[33];", launch_bounds="P_BLOCK APPY_MINB_ARG")
+        # P_MINB > 0 states the resident CTAs per SM the kernel is meant for, which opens the register
+        # budget: the compiler then really keeps the U x R loads of a lane in flight instead of
+        # interleaving them with the arithmetic to save registers (0 = no statement, compiler's default)
+        src.insert(1, MINB_MACRO)
+        tun = {"P_G": [32, 0, 8, 4, 16], "P_BLOCK": [128, 256, 512], "P_U": [4, 2, 8], "P_R": [1, 2, 4],
+               "P_MINB": [0, 1, 2]}
         return KernelPlan("rowdot", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr, vec=V,
                           info={"template": "T4 row-dot", "vector_width": V, "inner_lo": loop.iter.args[0],
-                                "inner_hi": loop.iter.args[1]})
+                                "inner_hi": loop.iter.args[1], "streams": len(streams)})
 
     # ------------------------------------------------------------------ T5: CSR x dense
     def try_csrdense(self):

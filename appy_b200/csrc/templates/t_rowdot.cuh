@@ -64,17 +64,84 @@ APPY_DEV void appy_rowdot_row(const Body& body, i64 i, const appy_grp<G>& g) {
   if (g.lane == 0) body.finish(i, total);
 }
 
-template <int G, int V, int U, class Body>
+// R consecutive rows at once: the group walks the same chunk of all R rows before it moves on,
+// so operands that depend on the inner index only (x[j]) are fetched once per chunk (identical
+// read-only loads are merged by the compiler) and every lane keeps R x U chunks in flight.
+// Rows whose inner bounds differ (triangular loops) are processed one after the other.
+template <int G, int V, int U, int R, class Body>
+APPY_DEV void appy_rowdot_rows(const Body& body, i64 i, const appy_grp<G>& g) {
+  typedef typename Body::Acc Acc;
+  typedef typename Body::Op Op;
+  i64 jlo, jhi;
+  body.bounds(i, jlo, jhi);
+  bool same = true;
+#pragma unroll
+  for (int r = 1; r < R; ++r) {
+    i64 a, b;
+    body.bounds(i + r, a, b);
+    same = same && a == jlo && b == jhi;
+  }
+  if (!same) {
+    for (int r = 0; r < R; ++r) appy_rowdot_row<G, V, U, Body>(body, i + r, g);
+    return;
+  }
+  Acc acc[R][U];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc[r][u] = Op::template id<Acc>();
+  const int gs = g.size();
+  i64 c_lo = (jlo + V - 1) / V, c_hi = jhi / V;
+  if (c_hi < c_lo) c_hi = c_lo;
+  const i64 head_end = (c_lo * V < jhi) ? c_lo * V : jhi;
+  for (i64 j = jlo + g.lane; j < head_end; j += gs)
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r][0] = body.one(i + r, j, acc[r][0]);
+  i64 c = c_lo + g.lane;
+  for (; c + (i64)(U - 1) * gs < c_hi; c += (i64)U * gs) {
+    typename Body::Regs rg[R][U];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int u = 0; u < U; ++u) body.load(i + r, (c + (i64)u * gs) * V, rg[r][u]);
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int u = 0; u < U; ++u) acc[r][u] = body.fold(i + r, (c + (i64)u * gs) * V, rg[r][u], acc[r][u]);
+  }
+  for (; c < c_hi; c += gs) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      typename Body::Regs rg;
+      body.load(i + r, c * V, rg);
+      acc[r][0] = body.fold(i + r, c * V, rg, acc[r][0]);
+    }
+  }
+  const i64 tail_begin = (c_hi * V > head_end) ? c_hi * V : head_end;
+  for (i64 j = tail_begin + g.lane; j < jhi; j += gs)
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r][0] = body.one(i + r, j, acc[r][0]);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int u = 1; u < U; ++u) acc[r][0] = Op::template op<Acc>(acc[r][0], acc[r][u]);
+    const Acc total = g.template reduce<Op, Acc>(acc[r][0]);
+    if (g.lane == 0) body.finish(i + r, total);
+  }
+}
+
+template <int G, int V, int U, int R, class Body>
 APPY_DEV void appy_rowdot(const Body& body, i64 lo, i64 hi, void* smem) {
   appy_grp<G> g;
   g.init(smem);
-  if (G == 0) {
-    for (i64 i = lo + blockIdx.x; i < hi; i += gridDim.x) appy_rowdot_row<G, V, U, Body>(body, i, g);
-  } else {
-    const int gg = G ? G : 1;
-    const int gpb = blockDim.x / gg;
-    const i64 gid = (i64)blockIdx.x * gpb + threadIdx.x / gg;
-    const i64 ngroups = (i64)gridDim.x * gpb;
-    for (i64 i = lo + gid; i < hi; i += ngroups) appy_rowdot_row<G, V, U, Body>(body, i, g);
+  const int gg = G ? G : 1;
+  const int gpb = G ? blockDim.x / gg : 1;                       // groups per CTA
+  const i64 gid = G ? (i64)blockIdx.x * gpb + threadIdx.x / gg : (i64)blockIdx.x;
+  const i64 ngroups = (i64)gridDim.x * gpb;
+  const i64 nfull = (hi - lo) / R;                               // units of R rows
+  for (i64 b = gid; b < nfull; b += ngroups) {
+    if (R == 1) appy_rowdot_row<G, V, U, Body>(body, lo + b, g);
+    else appy_rowdot_rows<G, V, U, R, Body>(body, lo + b * R, g);
   }
+  for (i64 i = lo + nfull * R + gid; i < hi; i += ngroups) appy_rowdot_row<G, V, U, Body>(body, i, g);
 }

@@ -208,6 +208,21 @@ def time_kernel(torch, fn, rot: int, iters: int, warm: int = 3):
     return e0.elapsed_time(e1) * 1e3 / iters
 
 
+def _wall(fn):
+    t0 = time.perf_counter()
+    fn()
+    return time.perf_counter() - t0
+
+
+def _scipy_csr(Am):
+    try:
+        import scipy.sparse as sp
+        return sp.csr_matrix((Am.data, Am.indices, Am.indptr), shape=Am.shape)
+    except Exception as e:
+        sys.stderr.write(f"[bench] SciPy unavailable for the host rows: {e!r}\n")
+        return None
+
+
 def _triton_arm():
     """The reference's generated Triton kernels, restated in baseline/triton_kernels.py."""
     try:
@@ -239,6 +254,16 @@ def kernel_table(torch, L, peak, rank, quick=False, with_triton=True, world=1):
             rows[name]["triton_us"] = None
             sys.stderr.write(f"[bench] Triton kernel for {name} failed: {e!r}\n")
 
+    def host(name, fn, reps=2):
+        """The vectorised NumPy/SciPy statement of the same loop on the host cores (one GPU runs only)."""
+        if world > 1:
+            return
+        fn()
+        best = min(_wall(fn) for _ in range(reps))
+        rows[name]["numpy_ms"] = round(best * 1e3, 2)
+        rows[name]["numpy_threads"] = os.cpu_count()
+        rows[name]["speedup_vs_numpy"] = round(best * 1e6 / rows[name]["us"], 1)
+
     def add(name, byts, us, extra=None):
         if world > 1:
             import torch.distributed as dist
@@ -258,6 +283,7 @@ def kernel_table(torch, L, peak, rank, quick=False, with_triton=True, world=1):
         time_kernel(torch, lambda i: L.vec_add(*sets[i]), 4, 40), {"l2": "4 rotating buffer sets"})
     assert np.array_equal(sets[0][2].cpu().numpy(), a + b)
     tri("C1 vec_add f32 n=2^24", W.bytes_vec_add(n), lambda i: TK.vec_add(*sets[i]), 4, 40)
+    host("C1 vec_add f32 n=2^24", lambda: np.add(a, b))
     del sets
     # C4
     al, A, x = W.gemv(16384, seed=rank)
@@ -265,6 +291,7 @@ def kernel_table(torch, L, peak, rank, quick=False, with_triton=True, world=1):
     add("C4 gemv f32 16384x16384", W.bytes_gemv(16384, 16384),
         time_kernel(torch, lambda i: L.gemv(1.0, dA, dx, dy), 1, 20), {"l2": "1 GiB input"})
     tri("C4 gemv f32 16384x16384", W.bytes_gemv(16384, 16384), lambda i: TK.gemv(1.0, dA, dx, dy), 1, 5)
+    host("C4 gemv f32 16384x16384", lambda: A @ x)
     del dA
     if quick:
         return rows
@@ -282,6 +309,9 @@ def kernel_table(torch, L, peak, rank, quick=False, with_triton=True, world=1):
             {"l2": "2 rotating copies"})
         tri(f"C3 spmv {kind} M=2^20 nnz={Am.nnz}", byts,
             lambda i: TK.spmv(sets[i][0], sets[i][1], sets[i][2], sets[i][3], sets[i][4], M), 2, 6)
+        Asp = _scipy_csr(Am)
+        if Asp is not None:
+            host(f"C3 spmv {kind} M=2^20 nnz={Am.nnz}", lambda: Asp @ xv)
         del sets
     # C5
     Am, B = W.spmm(seed=rank)
@@ -293,6 +323,9 @@ def kernel_table(torch, L, peak, rank, quick=False, with_triton=True, world=1):
     add(f"C5 spmm M=2^18 nnz={Am.nnz} B=2^18x128", b1, us,
         {"gather_bytes": int(b2), "gather_gbs": round(b2 / us / 1e3, 1), "l2": "403 MB working set"})
     tri(f"C5 spmm M=2^18 nnz={Am.nnz} B=2^18x128", b1, lambda i: TK.spmm(d[0], d[1], d[2], d[3], Cm, M), 1, 2)
+    Asp = _scipy_csr(Am)
+    if Asp is not None:
+        host(f"C5 spmm M=2^18 nnz={Am.nnz} B=2^18x128", lambda: Asp @ B, reps=1)
     return rows
 
 
@@ -598,6 +631,26 @@ def main():
                 "triton_us": round(tri_msk, 2), "triton_gbs": round(W.bytes_masked_sum(n) / tri_msk / 1e3, 1),
                 "speedup_vs_triton": round(tri_msk / us_msk, 2),
                 "triton_if_form_us": round(tri_if, 2) if tri_if else None})
+        if world == 1:      # the vectorised NumPy statements of the two loops on the host cores
+            for name, us, fn in (("C2a sum f32 n=2^26", us_sum, lambda: np.sum(a_h, dtype=np.float64)),
+                                 ("C2b masked sum f32+bool n=2^26", us_msk,
+                                  lambda: np.sum(a_h, where=m_h, dtype=np.float64))):
+                fn()
+                best = min(_wall(fn) for _ in range(2))
+                table[name].update({"numpy_ms": round(best * 1e3, 2), "numpy_threads": os.cpu_count(),
+                                    "speedup_vs_numpy": round(best * 1e6 / us, 1)})
+
+    # host cost of one call through the whole @jit path (wall clock; the kernel on 4096 elements is
+    # shorter than the call, so the loop is host-bound and wall time per call is the launch path)
+    small, small_out = a[:4096], torch.zeros(1, dtype=torch.float64, device="cuda")
+    for _ in range(20):
+        L.sum_into(small, small_out)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(500):
+        L.sum_into(small, small_out)
+    host_launch_us = (time.perf_counter() - t0) / 500 * 1e6
+    torch.cuda.synchronize()
 
     cpu = None
     if rank == 0 and world == 1:
@@ -626,6 +679,7 @@ def main():
             "e2e": {"value": round(e2e_val, 3), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps},
             "gpu_launches": int(launches),
+            "host_launch_us": round(host_launch_us, 2),
             "clocks": clocks,
             "kernels": table,
         }

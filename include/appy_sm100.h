@@ -162,7 +162,8 @@ int appy_spmv_csr_f32(const float* ddata, const int32_t* dindptr, const int32_t*
                       const float* dx, float* dy, int64_t row_lo, int64_t row_hi, int strategy,
                       void* stream);
 /* y[i] = sum_j alpha * A[i,j] * x[j]          — examples/05-gemv.py:7-17.
- * lda in elements; lanes: 32 = warp per row, 0 = CTA per row. */
+ * lda in elements; lanes: 32 = warp per row, 0 = CTA per pair of rows (the faster choice for
+ * rows of a few thousand elements or more). */
 int appy_gemv_f32(float alpha, const float* dA, int64_t lda, const float* dx, float* dy,
                   int64_t row_lo, int64_t row_hi, int64_t ncols, int lanes, void* stream);
 /* C[i,:] = sum_k data[k] * B[indices[k],:]    — examples/06-spmm.py:4-11.
