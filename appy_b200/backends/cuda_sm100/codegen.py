@@ -157,8 +157,9 @@ class Variant:
     def __init__(self, plan: KernelPlan):
         self.plan = plan
         self.handles: dict = {}       # tunables tuple -> kernel handle
-        self.tun = {k: v[0] for k, v in plan.tunables.items()}
-        self.tuned = False
+        self.tun = {k: v[0] for k, v in plan.tunables.items()}      # defaults: first candidate of each
+        self.choice: dict = {}        # shape class -> tunables settled for it
+        self.last_tun = self.tun
         self.lo_code = compile(ast.Expression(body=plan.lo_expr), "<lo>", "eval")
         self.hi_code = compile(ast.Expression(body=plan.hi_expr), "<hi>", "eval")
 
@@ -352,43 +353,57 @@ class CompiledLoop:
                 vals.append(C.c_uint64(multi_gpu.combiner().next_seq()))
         return rt.ArgPack(vals)
 
-    def _heuristics(self, variant: Variant, scope, arrays):
-        """Pick the lanes-per-row default from the inner trip count when it is known."""
-        plan = variant.plan
-        if plan.kind in ("group", "rowdot") and not variant.tuned:
-            trip = None
-            hi_n, lo_n = plan.info.get("inner_hi"), plan.info.get("inner_lo")
-            try:
-                if hi_n is not None:
-                    trip = int(eval(compile(ast.Expression(body=hi_n), "<t>", "eval"), {}, scope)) - \
-                        int(eval(compile(ast.Expression(body=lo_n), "<t>", "eval"), {}, scope))
-            except Exception:
-                trip = None
-            if trip is not None:
-                per = 4 * max(1, plan.vec)
-                g = 1
-                while g < 32 and g * per < trip:
-                    g *= 2
-                if trip >= 8192 * max(1, plan.vec) // 4 and plan.kind == "group":
-                    g = 0
-                variant.tun["P_G"] = g
-                if plan.kind == "rowdot" and plan.vec > 1 and trip >= 1024 * plan.vec:
-                    # Long dense rows: one CTA per pair of rows, eight 16-byte chunks per lane and row in
-                    # flight.  Few, deep streams (two resident CTAs per SM) read long contiguous bursts of
-                    # each row, which keeps DRAM pages open; thousands of concurrent warp-per-row streams
-                    # were measured 20 % slower on a 16384 x 16384 matrix.
-                    light = plan.info.get("streams", 9) <= 2
-                    variant.tun.update({"P_G": 0, "P_BLOCK": 256, "P_U": 8 if light else 4, "P_R": 2 if light else 1,
-                                        "P_MINB": 2})
+    def _inner_trip(self, plan, scope):
+        """Trip count of the (first) inner simd loop for this call, or None when it is not known on the host."""
+        hi_n, lo_n = plan.info.get("inner_hi"), plan.info.get("inner_lo")
+        if hi_n is None:
+            return None
+        try:
+            return max(0, int(eval(compile(ast.Expression(body=hi_n), "<t>", "eval"), {}, scope)) -
+                       int(eval(compile(ast.Expression(body=lo_n), "<t>", "eval"), {}, scope)))
+        except Exception:
+            return None
 
-    def _csr_overrides(self, variant: Variant, arrays, stream) -> dict:
-        """Lanes per row from the row-length histogram of this matrix (cached per indptr buffer)."""
+    def _shape_class(self, variant: Variant, scope, arrays, n_iter: int, stream):
+        """(class, overrides): launches of one class share their tunables; the overrides are the
+        defaults this class starts from.  The class is what the choice depends on beyond the code
+        itself: the inner trip count for row loops, the row-length profile of the matrix for CSR
+        loops, the size bucket of the outer range."""
         plan = variant.plan
-        if plan.kind != "csr" or not plan.info.get("indptr"):
-            return {}
+        bucket = max(n_iter, 1).bit_length()
+        if plan.kind in ("group", "rowdot"):
+            trip = self._inner_trip(plan, scope)
+            if trip is None:
+                return ("rows", bucket, None), {}
+            ov = {}
+            per = 4 * max(1, plan.vec)
+            g = 1
+            while g < 32 and g * per < trip:
+                g *= 2
+            if plan.kind == "group" and trip >= 2048:
+                g = 0                                   # a CTA per outer iteration
+            ov["P_G"] = g
+            if plan.kind == "rowdot" and plan.vec > 1 and trip >= 1024 * plan.vec:
+                # Long dense rows: one CTA per pair of rows, eight 16-byte chunks per lane and row in
+                # flight.  Few, deep streams (two resident CTAs per SM) read long contiguous bursts of
+                # each row, which keeps DRAM pages open; thousands of concurrent warp-per-row streams
+                # were measured 20 % slower on a 16384 x 16384 matrix.
+                light = plan.info.get("streams", 9) <= 2
+                ov.update({"P_G": 0, "P_BLOCK": 256, "P_U": 8 if light else 4, "P_R": 2 if light else 1,
+                           "P_MINB": 2})
+            return ("rows", bucket, max(trip, 1).bit_length()), ov
+        if plan.kind == "csr" and plan.info.get("indptr"):
+            row_class, ov = self._csr_profile(variant, arrays, stream)
+            return ("csr", bucket, row_class), ov
+        return ("n", bucket), {}
+
+    def _csr_profile(self, variant: Variant, arrays, stream):
+        """(row-length class, lanes per row) from the row-length histogram of this matrix (cached per
+        indptr buffer; runs on the stream the uploads were queued on)."""
+        plan = variant.plan
         ip = next((a for a in arrays if a.name == plan.info["indptr"]), None)
         if ip is None or ip.shape[0] <= 1:
-            return {}
+            return "", {}
         ckey = (ip.dptr, ip.shape[0])
         cache = variant.__dict__.setdefault("csr_choice", {})
         if ckey not in cache:
@@ -405,28 +420,37 @@ class CompiledLoop:
             length = 1 << max(med - 1, 0)
             g = 1 if length <= 1 else 2 if length <= 4 else 4 if length <= 16 else \
                 8 if length <= 64 else 16 if length <= 256 else 32
-            variant.row_class = f"med{med}max{max((b for b, c in enumerate(counts) if c), default=0)}"
-            cache[ckey] = {"P_G": g}
+            row_class = f"med{med}max{max((b for b, c in enumerate(counts) if c), default=0)}"
+            cache[ckey] = (row_class, {"P_G": g})
         return cache[ckey]
-
-    def _settle(self, variant: Variant) -> None:
-        if not self._want_autotune():
-            variant.tuned = True
 
     def _want_autotune(self) -> bool:
         return bool(self.options.get("autotune", os.environ.get("APPY_AUTOTUNE", "0") == "1"))
 
-    def _autotune(self, variant: Variant, args, arrays, lo, hi, stream):
+    def _choose_tunables(self, variant: Variant, args, arrays, scope, lo, hi, stream) -> dict:
+        forced = getattr(variant, "forced_tun", None)        # experiments and sweeps
+        if forced is not None:
+            return forced
+        cls, ov = self._shape_class(variant, scope, arrays, hi - lo, stream)
+        tun = variant.choice.get(cls)
+        if tun is None:
+            tun = dict(variant.tun, **{k: v for k, v in ov.items() if k in variant.tun})
+            if self._want_autotune():
+                tun = self._autotune(variant, args, arrays, lo, hi, stream, tun, cls)
+            if len(variant.choice) > 64:
+                variant.choice.clear()
+            variant.choice[cls] = tun
+        variant.last_tun = tun
+        return tun
+
+    def _autotune(self, variant: Variant, args, arrays, lo, hi, stream, start: dict, cls) -> dict:
         plan = variant.plan
         n_iter = hi - lo
         store = _tune_store()
-        bucket = max(n_iter, 1).bit_length()
         tkey = hashlib.sha1((plan.source + "|".join(map(str, plan.info.get("nvrtc", [])))).encode()).hexdigest() \
-            + f":{bucket}:{getattr(variant, 'row_class', '')}"
+            + ":" + ":".join(str(c) for c in cls)
         if tkey in store:
-            variant.tun.update(store[tkey])
-            variant.tuned = True
-            return
+            return dict(start, **store[tkey])
         # keep the stored arrays intact: run candidates, then restore
         saved = []
         for a in arrays:
@@ -436,12 +460,11 @@ class CompiledLoop:
                     tmp = rt.malloc(ext)
                     rt.check(rt.lib().appy_d2d_async(C.c_void_p(tmp), C.c_void_p(a.dptr), ext, C.c_void_p(stream)))
                     saved.append((a, tmp, ext))
-        best, best_t = dict(variant.tun), float("inf")
-        names = list(plan.tunables)
-        # coordinate descent over the tunables, starting from the defaults
-        cur = dict(variant.tun)
+        best, best_t = dict(start), float("inf")
+        # coordinate descent over the tunables, starting from this class's defaults
+        cur = dict(start)
         pack = self._pack(variant, args, arrays, lo, hi, stream)
-        for name in names:
+        for name in list(plan.tunables):
             for cand in plan.tunables[name]:
                 trial = dict(cur)
                 trial[name] = cand
@@ -459,13 +482,12 @@ class CompiledLoop:
         rt.sync(stream)
         for _a, tmp, _e in saved:
             rt.free(tmp)
-        variant.tun = best
-        variant.tuned = True
         store[tkey] = best
         _tune_save()
         if os.environ.get("APPY_TUNE_LOG") == "1":
-            sys.stderr.write(f"[appy autotune] {plan.name} ({plan.info.get('template')}) n={n_iter}: {best} "
+            sys.stderr.write(f"[appy autotune] {plan.name} ({plan.info.get('template')}) n={n_iter} {cls}: {best} "
                              f"{best_t * 1e3:.1f} us\n")
+        return best
 
     # ------------------------------------------------------------------ distribution over ranks
     def _check_distributable(self):
@@ -596,16 +618,7 @@ class CompiledLoop:
                 cells = self._reduction_cells(args, arrays)
                 self._pre_combine(cells)
         if hi > lo:
-            tun = variant.tun
-            if not variant.tuned:
-                ov = self._csr_overrides(variant, arrays, stream)   # on the stream the uploads were queued on
-                self._heuristics(variant, scope, arrays)
-                self._settle(variant)
-                if self._want_autotune() and not variant.tuned:
-                    self._autotune(variant, args, arrays, lo, hi, stream)
-                elif ov:
-                    variant.tuned = False                      # the choice is per matrix, not per variant
-                    tun = dict(variant.tun, **ov)
+            tun = self._choose_tunables(variant, args, arrays, scope, lo, hi, stream)
             pack = self._pack(variant, args, arrays, lo, hi, stream)
             h = variant.handle(tun)
             grid, block, smem = variant.plan.launch_config(tun, hi - lo, self.sm_count)

@@ -284,6 +284,8 @@ class Lowering:
             a = self.env.arrays[p.name]
             if a.readonly:
                 return f"const {a.ty.c}* __restrict__ {p.name}"
+            if self.options.get("_noalias", True):
+                return f"{a.ty.c}* __restrict__ {p.name}"      # no argument overlaps a stored array
             return f"{a.ty.c}* {p.name}"
         if p.kind == "ws":
             return "void* __ws"
@@ -592,8 +594,11 @@ class Lowering:
         src += self._kernel_wrapper(params, struct, "appy_group_rows<P_G>(__body, __lo, __hi, __smem);",
                                     "__shared__ double __smem[33];")
         tun = {"P_G": [8, 1, 2, 4, 16, 32, 0], "P_BLOCK": [256, 128, 512]}
-        return KernelPlan("group", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr,
-                          info={"template": "generic group lowering"})
+        info = {"template": "generic group lowering"}
+        inner = next((n for st in body for n in ast.walk(st) if isinstance(n, ast.For) and _is_simd(n)), None)
+        if inner is not None and isinstance(inner.iter, ast.Call) and len(inner.iter.args) >= 2:
+            info.update({"inner_lo": inner.iter.args[0], "inner_hi": inner.iter.args[1]})   # lanes per row follow it
+        return KernelPlan("group", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr, info=info)
 
     # ------------------------------------------------------------------ T3 / T4: single inner simd reduction
     def try_rowreduce(self):
@@ -937,6 +942,8 @@ class GroupEmitter(Emitter):
             post.append(f"  {text} = {OPS[op]}::op<{ty.c}>({text}, __g.template reduce<{OPS[op]}, {ty.c}>({p}));")
         self.in_simd = True
         guard, self.store_guard = self.store_guard, None
+        # iterations of a simd loop are independent: unrolled, a lane has several of them in flight
+        out.append("#pragma unroll 4")
         out.append(f"  for (i64 {v} = ({lo}) + __g.lane; {v} < {hi}; {v} += __g.size()) {{")
         out += self.block(st.body, "    ")
         out.append("  }")

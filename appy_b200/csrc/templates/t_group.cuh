@@ -52,7 +52,13 @@ template <> struct appy_grp<0> {
   u32 mask;
   void* smem;
   static const int size_static = 0;
+#ifdef P_BLOCK
+  // generated kernels are compiled for one CTA size: a constant stride lets the compiler prove that
+  // unrolled iterations of a lane touch different elements and overlap their loads
+  APPY_DEV int size() const { return P_BLOCK; }
+#else
   APPY_DEV int size() const { return blockDim.x; }
+#endif
   APPY_DEV void init(void* s) { lane = threadIdx.x; mask = APPY_FULL_MASK; smem = s; }
   APPY_DEV void barrier() const { __syncthreads(); }
   template <class Op, class T> APPY_DEV T reduce(T v) const {
