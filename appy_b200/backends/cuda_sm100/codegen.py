@@ -383,13 +383,21 @@ class CompiledLoop:
             if plan.kind == "group" and trip >= 2048:
                 g = 0                                   # a CTA per outer iteration
             ov["P_G"] = g
+            if g == 0 and plan.info.get("splittable") and n_iter < 4 * self.sm_count:
+                # few long rows of a perfect nest: cut every row into segments until about eight CTAs
+                # per SM have work, keeping at least 2048 iterations per segment
+                seg = 1
+                while seg < 64 and n_iter * seg < 8 * self.sm_count and trip // (seg * 4) >= 2048:
+                    seg *= 4
+                ov["P_SEG"] = seg
             if plan.kind == "rowdot" and plan.vec > 1 and trip >= 1024 * plan.vec:
                 # Long dense rows: one CTA per pair of rows, eight 16-byte chunks per lane and row in
                 # flight.  Few, deep streams (two resident CTAs per SM) read long contiguous bursts of
                 # each row, which keeps DRAM pages open; thousands of concurrent warp-per-row streams
                 # were measured 20 % slower on a 16384 x 16384 matrix.
                 light = plan.info.get("streams", 9) <= 2
-                ov.update({"P_G": 0, "P_BLOCK": 256, "P_U": 8 if light else 4, "P_R": 2 if light else 1,
+                pair = light and n_iter >= 4 * self.sm_count        # with few rows every row gets its own CTA
+                ov.update({"P_G": 0, "P_BLOCK": 256, "P_U": 8 if light else 4, "P_R": 2 if pair else 1,
                            "P_MINB": 2})
             return ("rows", bucket, max(trip, 1).bit_length()), ov
         if plan.kind == "csr" and plan.info.get("indptr"):

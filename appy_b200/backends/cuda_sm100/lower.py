@@ -74,6 +74,7 @@ class KernelPlan:
         if k in ("group", "rowdot"):
             block, g = tun["P_BLOCK"], tun["P_G"]
             units = (n_iter + tun.get("P_R", 1) - 1) // tun.get("P_R", 1)      # R rows per group at once
+            units *= tun.get("P_SEG", 1)                                       # column segments per row
             groups = units if g == 0 else (units * g + block - 1) // block
             per_sm = tun.get("P_CTAS", 0)
             grid = groups if per_sm == 0 else min(groups, sm_count * per_sm)
@@ -582,6 +583,9 @@ class Lowering:
                 "reduce into a loop-local variable and combine it after the inner loop")
         hazards = stored_arrays(body) & loaded_arrays(body)
         ge = self._group_emitter(hazards)
+        # perfect nest: the outer body is one simd loop without reductions -> its range may be cut
+        # into segments worked on by different groups (P_SEG)
+        ge.split = len(body) == 1 and _is_simd(body[0]) and not reductions_of(body[0])
         ge.infer_locals(body)
         decl = ge.declare_locals()
         lines = ge.block(body, "    ")
@@ -591,10 +595,13 @@ class Lowering:
         src += ["  " + m for m in self._members(params)]
         src += [f"  template <class Grp> APPY_DEV void iter(i64 {self.var}, const Grp& __g) {{"]
         src += ["    " + l for l in decl] + lines + ["  }", "};"]
-        src += self._kernel_wrapper(params, struct, "appy_group_rows<P_G>(__body, __lo, __hi, __smem);",
+        src += self._kernel_wrapper(params, struct, "appy_group_rows<P_G, P_SEG>(__body, __lo, __hi, __smem);",
                                     "__shared__ double __smem[33];")
+        src.insert(1, "#ifndef P_SEG\n#define P_SEG 1\n#endif")
         tun = {"P_G": [8, 1, 2, 4, 16, 32, 0], "P_BLOCK": [256, 128, 512]}
-        info = {"template": "generic group lowering"}
+        info = {"template": "generic group lowering", "splittable": ge.split}
+        if ge.split:
+            tun["P_SEG"] = [1, 4, 16, 64]
         inner = next((n for st in body for n in ast.walk(st) if isinstance(n, ast.For) and _is_simd(n)), None)
         if inner is not None and isinstance(inner.iter, ast.Call) and len(inner.iter.args) >= 2:
             info.update({"inner_lo": inner.iter.args[0], "inner_hi": inner.iter.args[1]})   # lanes per row follow it
@@ -942,6 +949,11 @@ class GroupEmitter(Emitter):
             post.append(f"  {text} = {OPS[op]}::op<{ty.c}>({text}, __g.template reduce<{OPS[op]}, {ty.c}>({p}));")
         self.in_simd = True
         guard, self.store_guard = self.store_guard, None
+        if getattr(self, "split", False):          # this group's segment of [lo, hi)
+            out.append(f"  const i64 __l0 = ({lo}), __len = ({hi}) - __l0;")
+            out.append("  const i64 __slo = __l0 + (__len > 0 ? __len * __g.seg / P_SEG : 0);")
+            out.append("  const i64 __shi = __l0 + (__len > 0 ? __len * (__g.seg + 1) / P_SEG : 0);")
+            lo, hi = "__slo", "__shi"
         # iterations of a simd loop are independent: unrolled, a lane has several of them in flight
         out.append("#pragma unroll 4")
         out.append(f"  for (i64 {v} = ({lo}) + __g.lane; {v} < {hi}; {v} += __g.size()) {{")

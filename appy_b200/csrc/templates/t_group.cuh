@@ -18,6 +18,7 @@ template <int G> struct appy_grp {
   int lane;        // 0..G-1 inside the group
   u32 mask;        // warp lanes that form this group
   void* smem;      // unused for sub-warp groups
+  int seg;         // which of the SEG column segments of the outer iteration this group works on
   static const int size_static = G;
   APPY_DEV int size() const { return G; }
   APPY_DEV void init(void* s) {
@@ -25,6 +26,7 @@ template <int G> struct appy_grp {
     lane = wl & (G - 1);
     mask = (G == 32) ? APPY_FULL_MASK : (((1u << G) - 1u) << (wl & ~(G - 1)));
     smem = s;
+    seg = 0;
   }
   APPY_DEV void barrier() const {
     if (G > 1) __syncwarp(mask);
@@ -51,6 +53,7 @@ template <> struct appy_grp<0> {
   int lane;
   u32 mask;
   void* smem;
+  int seg;
   static const int size_static = 0;
 #ifdef P_BLOCK
   // generated kernels are compiled for one CTA size: a constant stride lets the compiler prove that
@@ -59,23 +62,33 @@ template <> struct appy_grp<0> {
 #else
   APPY_DEV int size() const { return blockDim.x; }
 #endif
-  APPY_DEV void init(void* s) { lane = threadIdx.x; mask = APPY_FULL_MASK; smem = s; }
+  APPY_DEV void init(void* s) { lane = threadIdx.x; mask = APPY_FULL_MASK; smem = s; seg = 0; }
   APPY_DEV void barrier() const { __syncthreads(); }
   template <class Op, class T> APPY_DEV T reduce(T v) const {
     return appy_block_reduce<Op, T>(v, reinterpret_cast<T*>(smem));
   }
 };
 
-template <int G, class Body>
+// SEG > 1 (perfect nests only: the outer body is one simd loop without reductions): an outer
+// iteration is cut into SEG column segments worked on by different groups, so that a few long
+// rows still fill the machine.  The generated inner loop takes its bounds from g.seg.
+template <int G, int SEG, class Body>
 APPY_DEV void appy_group_rows(Body& body, i64 lo, i64 hi, void* smem) {
   appy_grp<G> g;
   g.init(smem);
+  const i64 units = (hi - lo) * SEG;
   if (G == 0) {
-    for (i64 i = lo + blockIdx.x; i < hi; i += gridDim.x) body.iter(i, g);
+    for (i64 u = blockIdx.x; u < units; u += gridDim.x) {
+      g.seg = (int)(u % SEG);
+      body.iter(lo + u / SEG, g);
+    }
   } else {
     const int gpb = blockDim.x / (G ? G : 1);                 // groups per CTA
     const i64 gid = (i64)blockIdx.x * gpb + threadIdx.x / (G ? G : 1);
     const i64 ngroups = (i64)gridDim.x * gpb;
-    for (i64 i = lo + gid; i < hi; i += ngroups) body.iter(i, g);
+    for (i64 u = gid; u < units; u += ngroups) {
+      g.seg = (int)(u % SEG);
+      body.iter(lo + u / SEG, g);
+    }
   }
 }

@@ -140,3 +140,36 @@ def test_row_max_via_slice_reduction():
     plan, code = build("#pragma parallel for\nfor i in range(n):\n    y[i] = np.max(A[i, :]) - np.min(A[i, :])",
                        dict(A=np.ones((8, 8)), y=np.ones(8), n=8))
     assert plan.kind == "group" and "appy_max" in code and "appy_min" in code
+
+
+def test_row_loop_tunables_follow_the_inner_trip_count_of_each_call():
+    """One compiled variant serves short and long rows; the lanes per row must not stick to the first call."""
+    A = np.ones((64, 64), f32)
+    src = ("#pragma parallel for\nfor i in range(M):\n    s = 0.0\n    #pragma simd\n    for j in range(N):\n"
+           "        s += A[i, j] * x[j]\n    y[i] = s")
+    scope = dict(A=A, x=np.ones(64, f32), y=np.ones(64, f32), M=64, N=64)
+    vm = dispatcher.build_val_map(src, scope, {"np": np, "math": math})
+    entry = cg.CompiledLoop(src, "kernel_loop_1", list(vm), tuple(cg._kind_of(v) for v in vm.values()), {})
+    entry.source_for(*[v for v in vm.values() if not isinstance(v, types.ModuleType)])
+    variant = list(entry.variants.values())[0]
+    assert variant.plan.kind == "rowdot"
+    short_cls, short = entry._shape_class(variant, dict(scope, N=64), [], 64, 0)
+    long_cls, long_ = entry._shape_class(variant, dict(scope, N=16384), [], 64, 0)
+    assert short_cls != long_cls
+    assert short["P_G"] in (4, 8, 16) and "P_R" not in short
+    assert long_["P_G"] == 0 and long_["P_R"] == 2 and long_["P_MINB"] == 2     # CTA per pair of long rows
+    # the generic group lowering also sizes its groups from the inner trip
+    src2 = "#pragma parallel for\nfor i in range(M):\n    #pragma simd\n    for j in range(N):\n        c[i, j] = A[i, j] + 1.0"
+    scope2 = dict(A=A, c=A.copy(), M=64, N=64)
+    vm2 = dispatcher.build_val_map(src2, scope2, {"np": np, "math": math})
+    e2 = cg.CompiledLoop(src2, "kernel_loop_1", list(vm2), tuple(cg._kind_of(v) for v in vm2.values()), {})
+    e2.source_for(*[v for v in vm2.values() if not isinstance(v, types.ModuleType)])
+    v2 = list(e2.variants.values())[0]
+    assert v2.plan.kind == "group"
+    assert e2._shape_class(v2, dict(scope2, N=16), [], 64, 0)[1]["P_G"] == 4
+    assert e2._shape_class(v2, dict(scope2, N=100000), [], 64, 0)[1]["P_G"] == 0
+    # a few very long rows of a perfect nest are cut into column segments; many rows are not
+    e2.sm_count = 148
+    assert v2.plan.info["splittable"]
+    assert e2._shape_class(v2, dict(scope2, N=1 << 20), [], 64, 0)[1]["P_SEG"] == 64
+    assert e2._shape_class(v2, dict(scope2, N=1 << 20), [], 8192, 0)[1].get("P_SEG", 1) == 1

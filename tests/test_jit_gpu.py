@@ -648,3 +648,29 @@ def test_conditionally_read_array_may_be_shorter_than_the_range():
         exp = np.concatenate([np.arange(m, dtype=np.float32) * 2, -np.ones(37, np.float32)])
         assert np.array_equal(out.cpu().numpy(), exp)
         assert guarded_sum(a, m, m + 37) == float(np.arange(m, dtype=np.float64).sum())
+
+
+@appy.jit
+def few_long_rows_axpy(alpha, x, y):
+    #pragma parallel for
+    for i in range(x.shape[0]):
+        #pragma simd
+        for j in range(1, x.shape[1] - 1):
+            y[i, j] = alpha * x[i, j] + y[i, j]
+
+
+def test_perfect_nest_with_few_long_rows_is_cut_into_segments():
+    """3 rows of 100003 elements: the row range [1, N-1) is split over many CTAs; every element is
+    written exactly once and the two border columns stay untouched."""
+    import torch
+    rng = np.random.default_rng(3)
+    x = rng.uniform(-1, 1, (3, 100003)).astype(np.float32)
+    y = rng.uniform(-1, 1, (3, 100003)).astype(np.float32)
+    ref = y.copy()
+    ref[:, 1:-1] = np.float32(0.5) * x[:, 1:-1] + y[:, 1:-1]
+    dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()
+    few_long_rows_axpy(0.5, dx, dy)
+    assert np.array_equal(dy.cpu().numpy(), ref)
+    from appy_b200.backends.cuda_sm100 import codegen as cg
+    entry = [e for e in cg.code_cache.values() if e.kernel_name.startswith("few_long_rows_axpy_")][0]
+    assert entry.last_variant.last_tun["P_SEG"] > 1 and entry.last_variant.last_tun["P_G"] == 0
