@@ -154,10 +154,12 @@ def test_row_loop_tunables_follow_the_inner_trip_count_of_each_call():
     variant = list(entry.variants.values())[0]
     assert variant.plan.kind == "rowdot"
     short_cls, short = entry._shape_class(variant, dict(scope, N=64), [], 64, 0)
-    long_cls, long_ = entry._shape_class(variant, dict(scope, N=16384), [], 64, 0)
+    long_cls, long_ = entry._shape_class(variant, dict(scope, N=16384), [], 16384, 0)
     assert short_cls != long_cls
     assert short["P_G"] in (4, 8, 16) and "P_R" not in short
     assert long_["P_G"] == 0 and long_["P_R"] == 2 and long_["P_MINB"] == 2     # CTA per pair of long rows
+    few = entry._shape_class(variant, dict(scope, N=16384), [], 64, 0)[1]
+    assert few["P_G"] == 0 and few["P_R"] == 1                                   # few rows: a CTA each
     # the generic group lowering also sizes its groups from the inner trip
     src2 = "#pragma parallel for\nfor i in range(M):\n    #pragma simd\n    for j in range(N):\n        c[i, j] = A[i, j] + 1.0"
     scope2 = dict(A=A, c=A.copy(), M=64, N=64)
