@@ -1,14 +1,16 @@
 """Generates tests/golden/reference_outputs.npz and reference_facts.json by running the
 REFERENCE's own code on CPU.
 
-How: ``/root/reference`` is put on sys.path, the two packages it needs but that are not
+How: the reference checkout (first command-line argument, or the APPY_REFERENCE_TREE
+environment variable) is put on sys.path, the two packages it needs but that are not
 installed here (``ast_comments``, ``astpass``) are provided by the stand-ins under
 tests/golden/standins/, and Triton runs in interpreter mode (TRITON_INTERPRET=1), so the
 reference's decorator, dispatcher, front-end passes, Triton code generator and the generated
 Triton kernels all execute unmodified.  Inputs are seeded; outputs are stored as fixtures.
 
-Run from the repository root in the authoring container:  python tests/golden/make_golden.py
-(The GPU box has no /root/reference; the tests only read the committed fixtures.)
+Run from the repository root where the reference checkout exists:
+    python tests/golden/make_golden.py <path to the reference checkout>
+The tests only read the committed fixtures and never need the checkout.
 """
 import hashlib
 import json
@@ -19,7 +21,10 @@ os.environ["TRITON_INTERPRET"] = "1"
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, os.path.join(HERE, "standins"))
-sys.path.insert(0, "/root/reference")
+REFERENCE_TREE = os.path.abspath(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("APPY_REFERENCE_TREE", ""))
+if not os.path.isdir(os.path.join(REFERENCE_TREE, "appy")):
+    raise SystemExit("usage: python tests/golden/make_golden.py <path to the reference checkout>")
+sys.path.insert(0, REFERENCE_TREE)
 sys.path.insert(0, ROOT)
 
 import numpy as np  # noqa: E402
@@ -27,7 +32,7 @@ import appy  # noqa: E402  (the reference package)
 import appy.backends.triton.passes.block_loop as _bl  # noqa: E402
 from appy_b200 import workloads as W  # noqa: E402
 
-assert appy.__file__.startswith("/root/reference"), appy.__file__
+assert appy.__file__.startswith(REFERENCE_TREE), appy.__file__
 _bl.BlockLoop.__init__ = lambda self: setattr(self, "verbose", 0)   # silence the per-compile print
 
 dumps = {}
@@ -151,7 +156,7 @@ def stencil(A, B):
 
 def main():
     out = {}
-    facts = {"generator": "habanero-lab/APPy at /root/reference, Triton interpreter mode, stand-ins for "
+    facts = {"generator": "habanero-lab/APPy (the reference checkout), Triton interpreter mode, stand-ins for "
                           "ast_comments and astpass (tests/golden/standins)",
              "pinned": [], "not_pinned": ["spmm (its slice lowering comes from the stand-in, not the reference)"]}
     a, b = W.vec_add(1000, seed=0)
