@@ -577,35 +577,54 @@ class Lowering:
 
     def lower_group(self) -> KernelPlan:
         body = self.loop.body
-        if self.reductions:
-            raise NotImplementedError(
-                "a shared(...) reduction on a parallel loop that also has inner simd loops is not supported; "
-                "reduce into a loop-local variable and combine it after the inner loop")
         hazards = stored_arrays(body) & loaded_arrays(body)
         ge = self._group_emitter(hazards)
+        ordered = False
+        if self.reductions:
+            # shared(...) reductions of the parallel loop (reference: one atomic per program,
+            # device_passes/rewrite_par_reduce_to_atomics.py:10-88).  Every lane of a group executes
+            # scalar statements redundantly, so only lane 0 of the group accumulates; the CTA's
+            # accumulators are combined once at the end of the kernel, like in the flat lowering.
+            ordered = bool(self.options.get("ordered_reduction", False) or self.options.get("combine") == "p2p")
+            for text, (op, ty, acc, _node) in self.reductions.items():
+                ge.load_override[text] = (acc, ty)
+                ge.store_override[text] = (lambda code, t, acc=acc, ty=ty:
+                                           [f"if (__g.lane == 0) {acc} = {cast(code, t, ty)};"])
+            ge.outer_reductions = set(self.reductions)
         # perfect nest: the outer body is one simd loop without reductions -> its range may be cut
         # into segments worked on by different groups (P_SEG)
-        ge.split = len(body) == 1 and _is_simd(body[0]) and not reductions_of(body[0])
+        ge.split = len(body) == 1 and _is_simd(body[0]) and not reductions_of(body[0]) and not self.reductions
         ge.infer_locals(body)
         decl = ge.declare_locals()
         lines = ge.block(body, "    ")
-        params = self._params(uses_ws=False)
+        params = self._params(uses_ws=ordered)
         struct = f"{self.name}_body"
         src = ['#include "t_group.cuh"', f"struct {struct} {{"]
+        if self.reductions:
+            src[0] = '#include "t_group.cuh"\n#include "t_flat.cuh"'
         src += ["  " + m for m in self._members(params)]
+        src += ["  " + m for m in self._reduction_members()]
         src += [f"  template <class Grp> APPY_DEV void iter(i64 {self.var}, const Grp& __g) {{"]
-        src += ["    " + l for l in decl] + lines + ["  }", "};"]
-        src += self._kernel_wrapper(params, struct, "appy_group_rows<P_G, P_SEG>(__body, __lo, __hi, __smem);",
-                                    "__shared__ double __smem[33];")
+        src += ["    " + l for l in decl] + lines + ["  }"]
+        call = "appy_group_rows<P_G, P_SEG>(__body, __lo, __hi, __smem);"
+        if self.reductions:
+            src += ["  APPY_DEV void finish(void* __smem) {"] + \
+                   ["    " + l for l in self._reduction_finish(ordered)] + ["  }"]
+            call += " __syncthreads(); __body.finish(__smem);"
+        src += ["};"]
+        src += self._kernel_wrapper(params, struct, call, "__shared__ double __smem[33];", self._reduction_init())
         src.insert(1, "#ifndef P_SEG\n#define P_SEG 1\n#endif")
         tun = {"P_G": [8, 1, 2, 4, 16, 32, 0], "P_BLOCK": [256, 128, 512]}
         info = {"template": "generic group lowering", "splittable": ge.split}
         if ge.split:
             tun["P_SEG"] = [1, 4, 16, 64]
+        if self.reductions:
+            tun["P_CTAS"] = [8, 4, 16]          # persistent grid: one commit per CTA
         inner = next((n for st in body for n in ast.walk(st) if isinstance(n, ast.For) and _is_simd(n)), None)
         if inner is not None and isinstance(inner.iter, ast.Call) and len(inner.iter.args) >= 2:
             info.update({"inner_lo": inner.iter.args[0], "inner_hi": inner.iter.args[1]})   # lanes per row follow it
-        return KernelPlan("group", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr, info=info)
+        return KernelPlan("group", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr,
+                          uses_ws=ordered, info=info)
 
     # ------------------------------------------------------------------ T3 / T4: single inner simd reduction
     def try_rowreduce(self):
@@ -939,14 +958,23 @@ class GroupEmitter(Emitter):
         saved_l, saved_s = dict(self.load_override), dict(self.store_override)
         post = []
         for n, (text, op) in enumerate(reds.items()):
-            if text not in self.env.locals:
+            outer = text in getattr(self, "outer_reductions", ())
+            if text not in self.env.locals and not outer:
                 raise NotImplementedError(f"simd reduction target `{text}` must be a loop-local scalar")
-            ty = self.env.locals[text].strong()
-            p = f"__p{n}_{text}"
+            if outer:        # a shared(...) target of the parallel loop reduced directly inside the simd loop
+                tgt, ty = self.load_override[text]
+                p = f"__p{n}_r"
+            else:
+                tgt, ty = text, self.env.locals[text].strong()
+                p = f"__p{n}_{text}"
             out.append(f"  {ty.c} {p} = {OPS[op]}::id<{ty.c}>();")
             self.load_override[text] = (p, ty)
             self.store_override[text] = (lambda code, t, p=p, ty=ty: [f"{p} = {cast(code, t, ty)};"])
-            post.append(f"  {text} = {OPS[op]}::op<{ty.c}>({text}, __g.template reduce<{OPS[op]}, {ty.c}>({p}));")
+            if outer:
+                post.append(f"  {{ const {ty.c} __r = __g.template reduce<{OPS[op]}, {ty.c}>({p}); "
+                            f"if (__g.lane == 0) {tgt} = {OPS[op]}::op<{ty.c}>({tgt}, __r); }}")
+            else:
+                post.append(f"  {text} = {OPS[op]}::op<{ty.c}>({text}, __g.template reduce<{OPS[op]}, {ty.c}>({p}));")
         self.in_simd = True
         guard, self.store_guard = self.store_guard, None
         if getattr(self, "split", False):          # this group's segment of [lo, hi)

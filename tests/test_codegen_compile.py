@@ -175,3 +175,15 @@ def test_row_loop_tunables_follow_the_inner_trip_count_of_each_call():
     assert v2.plan.info["splittable"]
     assert e2._shape_class(v2, dict(scope2, N=1 << 20), [], 64, 0)[1]["P_SEG"] == 64
     assert e2._shape_class(v2, dict(scope2, N=1 << 20), [], 8192, 0)[1].get("P_SEG", 1) == 1
+
+
+def test_shared_reduction_with_inner_simd_loops_uses_the_group_lowering():
+    A = np.ones((64, 64), f32)
+    src = ("#pragma parallel for shared(s, m)\nfor i in range(M):\n    t = 0.0\n    #pragma simd\n"
+           "    for j in range(N):\n        t += A[i, j]\n        m[0] = max(m[0], A[i, j])\n    s[0] += t * w[i]")
+    scope = dict(A=A, w=np.ones(64, f32), s=np.array([0.0]), m=np.array([0.0], f32), M=64, N=64)
+    plan, code = build(src, scope)
+    assert plan.kind == "group" and "appy_atomic(appy_add()" in code and "appy_atomic(appy_max()" in code
+    assert "if (__g.lane == 0) __acc0" in code            # one lane of the group accumulates
+    plan, code = build(src, scope, ordered_reduction=True)
+    assert plan.uses_ws and "appy_ws_arrive" in code

@@ -674,3 +674,45 @@ def test_perfect_nest_with_few_long_rows_is_cut_into_segments():
     from appy_b200.backends.cuda_sm100 import codegen as cg
     entry = [e for e in cg.code_cache.values() if e.kernel_name.startswith("few_long_rows_axpy_")][0]
     assert entry.last_variant.last_tun["P_SEG"] > 1 and entry.last_variant.last_tun["P_G"] == 0
+
+
+@appy.jit
+def weighted_total_and_max(A, w):
+    s = 0.0
+    m = -1.0e30
+    #pragma parallel for shared(s, m)
+    for i in range(A.shape[0]):
+        t = 0.0
+        #pragma simd
+        for j in range(A.shape[1]):
+            t += A[i, j]
+            m = max(m, A[i, j])
+        s += t * w[i]
+    return s, m
+
+
+@appy.jit(ordered_reduction=True)
+def weighted_total_ordered(A, w):
+    s = 0.0
+    #pragma parallel for shared(s)
+    for i in range(A.shape[0]):
+        t = 0.0
+        #pragma simd
+        for j in range(A.shape[1]):
+            t += A[i, j]
+        s += t * w[i]
+    return s
+
+
+@pytest.mark.parametrize("shape", [(1000, 37), (37, 5000), (513, 256)])
+def test_shared_reduction_on_a_parallel_loop_with_inner_simd_loops(shape):
+    """The reference lowers this to one atomic per program
+    (device_passes/rewrite_par_reduce_to_atomics.py:10-88); rtol 1e-5 against float64."""
+    rng = np.random.default_rng(shape[0])
+    A = rng.uniform(0, 1, shape).astype(np.float32)
+    w = rng.uniform(0, 1, shape[0]).astype(np.float32)
+    ref = float(np.sum(A.astype(np.float64).sum(1) * w.astype(np.float64)))
+    s, m = weighted_total_and_max(A, w)
+    assert np.isclose(s, ref, rtol=1e-5, atol=0) and m == float(A.max())
+    assert np.isclose(weighted_total_ordered(A, w), ref, rtol=1e-5, atol=0)
+    assert weighted_total_ordered(A, w) == weighted_total_ordered(A, w)      # scheduling-independent commit
