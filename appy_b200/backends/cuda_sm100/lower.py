@@ -910,8 +910,14 @@ class Lowering:
                 f"(__body, {indptr}, __lo, __hi, {ncols}, __smem);")
         src += self._kernel_wrapper(params, struct, call, smem, launch_bounds="32 * P_WARPS, P_MINB")
         small = V * Tn <= 4
-        tun = {"P_WARPS": [8, 4], "P_ROWS": [32, 16, 64], "P_D": [8, 4, 2] if small else [2, 4],
-               "P_MINB": [4, 3, 5, 2] if small else [2, 1], "P_ROLL": [1, 0]}
+        # a row that is one 16-byte pack per lane: 16 warps x 3 CTAs per SM, four gathers in flight per
+        # warp, no rolling ring (634 us against 673 us for 8 warps x 4 CTAs with a ring of 8 on the
+        # 2^18-row, 128-column case); wider rows keep 8 warps and fewer, larger gathers
+        one_pack = V == 4 and Tn == 1
+        tun = {"P_WARPS": [16, 8, 4] if one_pack else [8, 4], "P_ROWS": [32, 16, 64],
+               "P_D": ([4, 8, 2] if one_pack else [8, 4, 2]) if small else [2, 4],
+               "P_MINB": ([3, 4, 2] if one_pack else [4, 3, 5, 2]) if small else [2, 1],
+               "P_ROLL": [0, 1] if one_pack else [1, 0]}
         return KernelPlan("csrdense", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr, vec=V,
                           info={"template": "T5 CSR x dense", "ncols": ncols, "vector_width": V, "indptr": indptr})
 
