@@ -449,6 +449,34 @@ class Lowering:
                     del stores[text]
                     for t in [t for t, (nm, _x) in loads.items() if nm == name]:
                         del loads[t]
+        # Neighbour loads (stencils): `a[.., i + d]` with 0 < |d| < V on an array the loop only reads.
+        # The pack of `a[.., i]` plus |d| scalar elements on the side holds every operand, so each
+        # element travels from L1 to registers once instead of once per offset.
+        self.neighbours = {}
+        if self.options.get("_neighbours", True):
+            cond = conditional_loads(body)
+            for st in body:
+                if isinstance(st, (ast.If, ast.For, ast.While)):
+                    continue
+                for n in ast.walk(st):
+                    if not (isinstance(n, ast.Subscript) and isinstance(n.ctx, ast.Load) and isinstance(n.value, ast.Name)):
+                        continue
+                    name = n.value.id
+                    d = _last_index_offset(n, self.var)
+                    if not d or abs(d) >= V or abs(d) > 2 or name in st_arr or not arr_ok(name) or id(n) in cond:
+                        continue
+                    elts = n.slice.elts if isinstance(n.slice, ast.Tuple) else [n.slice]
+                    if any((_names_in(e) - {self.var}) & set(self._assigned_locals()) for e in elts[:-1]):
+                        continue
+                    base = copy.deepcopy(n)
+                    if isinstance(base.slice, ast.Tuple):
+                        base.slice.elts[-1] = ast.Name(id=self.var, ctx=ast.Load())
+                    else:
+                        base.slice = ast.Name(id=self.var, ctx=ast.Load())
+                    base_text = ast.unparse(base)
+                    if base_text not in loads:
+                        loads[base_text] = (name, base)        # the centre pack is fetched for the sides' sake
+                    self.neighbours[ast.unparse(n)] = (base_text, d)
         return loads, stores
 
     def reductions_arrays(self) -> set:
@@ -521,11 +549,29 @@ class Lowering:
                 line = (f"if (__i0 + {V} <= {shape}) {line} else {{ for (int __k = 0; __k < {V}; ++__k) "
                         f"__rg.{s}.v[__k] = (__i0 + __k < {shape}) ? {name}[({off}) + __k] : {arr.ty.c}(0); }}")
             load_lines.append(line)
+        side = {}       # centre text -> (elements needed below, elements needed above)
+        for _t, (base_text, d) in getattr(self, "neighbours", {}).items():
+            lo_n, hi_n = side.get(base_text, (0, 0))
+            side[base_text] = (max(lo_n, -d), max(hi_n, d))
+        for base_text, (lo_n, hi_n) in side.items():
+            name, node = loads[base_text]
+            arr = env.arrays[name]
+            sl = slot[base_text]
+            off, _ = Emitter(env).offset(_replace_index(node, self.var, "__i0"))
+            regs.append(f"{arr.ty.c} {sl}lo[{max(lo_n, 1)}]; {arr.ty.c} {sl}hi[{max(hi_n, 1)}];")
+            for k in range(lo_n):
+                load_lines.append(f"__rg.{sl}lo[{k}] = appy_ldg1({name} + (({off}) - {k + 1}));")
+            for k in range(hi_n):
+                load_lines.append(f"__rg.{sl}hi[{k}] = appy_ldg1({name} + (({off}) + {V + k}));")
         if V > 1:
             saved_l, saved_s = dict(em.load_override), dict(em.store_override)
             for text, s in slot.items():
                 arr = env.arrays[loads[text][0]]
                 em.load_override[text] = (f"__rg.{s}.v[__k]", arr.ty)
+            for text, (base_text, d) in getattr(self, "neighbours", {}).items():
+                arr = env.arrays[loads[base_text][0]]
+                sl = slot[base_text]
+                em.load_override[text] = (f"appy_side(__rg.{sl}, __rg.{sl}lo, __rg.{sl}hi, __k + ({d}))", arr.ty)
             for n_out, (text, (name, node)) in enumerate(stores.items()):
                 arr = env.arrays[name]
                 o = f"o{n_out}"

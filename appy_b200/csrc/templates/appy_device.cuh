@@ -155,6 +155,15 @@ template <class Op, class T> APPY_DEV T appy_block_reduce(T v, T* smem) {
   return r;
 }
 
+// Element `idx` of the run [lo[NL-1] .. lo[0], p.v[0] .. p.v[V-1], hi[0] .. hi[NH-1]] (a pack with the
+// scalar elements below and above it).  `idx` is a constant after unrolling, so this is a register pick.
+template <class T, int V, int NL, int NH>
+APPY_DEV T appy_side(const appy_pack<T, V>& p, const T (&lo)[NL], const T (&hi)[NH], int idx) {
+  if (idx < 0) return lo[-idx - 1];
+  if (idx >= V) return hi[idx - V];
+  return p.v[idx];
+}
+
 // ---------------------------------------------------------------------------
 // atomics on a shared(...) scalar, one per block
 // ---------------------------------------------------------------------------

@@ -716,3 +716,43 @@ def test_shared_reduction_on_a_parallel_loop_with_inner_simd_loops(shape):
     assert np.isclose(s, ref, rtol=1e-5, atol=0) and m == float(A.max())
     assert np.isclose(weighted_total_ordered(A, w), ref, rtol=1e-5, atol=0)
     assert weighted_total_ordered(A, w) == weighted_total_ordered(A, w)      # scheduling-independent commit
+
+
+@appy.jit
+def five_point_1d(a, b, lo, hi):
+    #pragma parallel for simd
+    for i in range(lo, hi):
+        b[i] = a[i - 2] - 2.0 * a[i - 1] + 4.0 * a[i] - 2.0 * a[i + 1] + a[i + 2]
+
+
+@appy.jit
+def row_of_matrix_stencil(A, b, r):
+    #pragma parallel for simd
+    for i in range(1, A.shape[1] - 1):
+        b[i] = A[r, i + 1] - A[r, i - 1]
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("lo,hi", [(2, 100001), (3, 4099), (5, 9)])
+def test_neighbour_loads_equal_numpy_bit_for_bit(dtype, lo, hi):
+    """Offsets of one and two elements around the vectorised centre pack (float64 packs hold two
+    elements, so there only the +-1 offsets ride on the pack); one rounding per operation, so the
+    result equals the same NumPy expression exactly."""
+    import torch
+    rng = np.random.default_rng(lo + hi)
+    a = rng.uniform(-1, 1, hi + 2).astype(dtype)
+    b = np.full(hi + 2, 7, dtype)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    five_point_1d(da, db, lo, hi)
+    ref = b.copy()
+    c = np.arange(lo, hi)
+    two, four = dtype(2.0), dtype(4.0)
+    ref[c] = a[c - 2] - two * a[c - 1] + four * a[c] - two * a[c + 1] + a[c + 2]
+    assert np.array_equal(db.cpu().numpy(), ref)
+    A = rng.uniform(-1, 1, (3, 1001)).astype(dtype)
+    out = np.zeros(1001, dtype)
+    dA, dout = torch.from_numpy(A).cuda(), torch.from_numpy(out).cuda()
+    row_of_matrix_stencil(dA, dout, 2)
+    ref2 = out.copy()
+    ref2[1:-1] = A[2, 2:] - A[2, :-2]
+    assert np.array_equal(dout.cpu().numpy(), ref2)
