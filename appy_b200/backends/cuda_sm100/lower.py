@@ -372,9 +372,10 @@ class Lowering:
                 out.append("  if (threadIdx.x < 32) {")
                 bits = ", ".join(f"appy_to_bits<{ty.c}>(__t{r})" for r, (op, ty, acc, _n) in enumerate(items))
                 out.append(f"    u64 __x[{len(items)}] = {{{bits}}};")
-                out.append(f"    appy_p2p_exchange<{len(items)}>(__mb, __seq, __x);")
+                out.append(f"    const bool __ok = appy_p2p_exchange<{len(items)}>(__mb, __seq, __x);")
                 for r, ((op, ty, acc, _n), addr) in enumerate(zip(items, addrs)):
                     out.append(f"    __t{r} = appy_p2p_fold<{OPS[op]}, {ty.c}>(__mb, __x[{r}]);")
+                    out.append(f"    if (!__ok) __t{r} = appy_p2p_poison<{ty.c}>(__t{r});")
                     out.append(f"    if (threadIdx.x == 0) *{addr} = {OPS[op]}::op<{ty.c}>(*{addr}, __t{r});")
                 out.append("  }")
             else:

@@ -141,7 +141,7 @@ template <class Op, class T> APPY_DEV T appy_ws_collect(const appy_ws& w, int va
 // one launch ahead of the slowest rank, because finishing launch s needs every rank's words
 // of launch s.  The tag is the low 31 bits of s with bit 31 set, so it differs from the tag
 // two launches earlier and from freshly zeroed memory.
-// The wait is limited; on expiry the error word is set and whatever the slot holds is used,
+// The wait is limited; on expiry the error word is set and floating-point results are set to NaN,
 // so a missing rank makes the launch return with a status the host reads, never a hang.
 //
 // Mailbox of one rank: [parity 0..1][source rank 0..world-1] x 8 words of 8 bytes;
@@ -179,10 +179,12 @@ template <class T> APPY_DEV T appy_from_bits(u64 u) {
 
 // Steps 1 and 2, called by the 32 threads of warp 0.  In: x[v] = this rank's total of variable v
 // (raw bits, same in every lane).  Out: in lane r < world, x[v] = rank r's total of variable v.
-template <int NV> APPY_DEV void appy_p2p_exchange(const appy_mailbox* mb, u64 seq, u64 (&x)[NV]) {
+// Returns false (to every lane) when some rank's words did not arrive within the limit.
+template <int NV> APPY_DEV bool appy_p2p_exchange(const appy_mailbox* mb, u64 seq, u64 (&x)[NV]) {
   const int world = mb->world, rank = mb->rank;
   const int lane = threadIdx.x & 31;
   const u64 tag = (u64)((unsigned)seq | 0x80000000u) << 32;
+  bool ok = true;
   if (lane < world) {
     u64* dst = mb->peer[lane] + ((seq & 1) * world + rank) * 8;
 #pragma unroll
@@ -193,7 +195,6 @@ template <int NV> APPY_DEV void appy_p2p_exchange(const appy_mailbox* mb, u64 se
     const u64* src = mb->peer[rank] + ((seq & 1) * world + lane) * 8;
     const unsigned limit = mb->spin_limit;
     unsigned spins = 0;
-    bool ok = true;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       u64 lo, hi;
@@ -211,8 +212,13 @@ template <int NV> APPY_DEV void appy_p2p_exchange(const appy_mailbox* mb, u64 se
     }
     if (!ok) atomicExch(mb->err, 1u);
   }
-  __syncwarp();
+  return __all_sync(0xffffffffu, ok) != 0;
 }
+// A combine that timed out must not look like a result: floating-point totals become NaN (integer
+// totals cannot be marked; the status word is the only sign there).
+template <class T> APPY_DEV T appy_p2p_poison(T v) { return v; }
+template <> APPY_DEV float appy_p2p_poison<float>(float) { return __int_as_float(0x7fc00000); }
+template <> APPY_DEV double appy_p2p_poison<double>(double) { return __longlong_as_double(0x7ff8000000000000ll); }
 // Step 3, called by the 32 threads of warp 0 with lane r holding rank r's total.
 template <class Op, class T> APPY_DEV T appy_p2p_fold(const appy_mailbox* mb, u64 bits) {
   const int world = mb->world;

@@ -54,6 +54,7 @@ def test_missing_rank_times_out_with_a_status_not_a_hang(rt):
         da = torch.from_numpy(a).cuda()
         s, m = sum_and_max(da)                  # returns: the wait for rank 1 runs out
         torch.cuda.synchronize()
+        assert np.isnan(s) and np.isnan(m)      # a combine that timed out does not look like a result
         assert c.timed_out()
         assert not c.timed_out()                # reading the status clears it
         out = torch.ones(8, device="cuda") * 2  # the context is still usable
