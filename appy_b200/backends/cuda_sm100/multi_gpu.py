@@ -102,6 +102,25 @@ class P2PCombiner:
         self._seq += 1
         return self._seq
 
+    _OPS = {"+": 0, "*": 1, "max": 2, "min": 3}
+    _DTYPES = {"float32": 0, "float64": 1, "int32": 2, "int64": 3}
+
+    def combine(self, values, op: str = "+", stream: int | None = None) -> None:
+        """Fold a 1-D CUDA tensor of one to four scalars over all ranks, in place (every rank ends with
+        the same bits).  For results of kernels that do not combine in their own tail, e.g. the prebuilt
+        C-ABI kernels; collective like a `combine="p2p"` loop: every rank calls it at the same point."""
+        import ctypes as C
+        import torch
+        if values.dim() != 1 or not 1 <= values.numel() <= 4 or not values.is_contiguous():
+            raise ValueError("combine() takes a contiguous 1-D tensor of one to four elements")
+        dt = self._DTYPES.get(str(values.dtype).replace("torch.", ""))
+        if dt is None or op not in self._OPS:
+            raise ValueError(f"combine(): unsupported dtype {values.dtype} or operator {op!r}")
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream
+        rt.check(rt.lib().appy_p2p_combine(self._ctx, self.next_seq(), self._OPS[op], dt,
+                                           C.c_void_p(values.data_ptr()), values.numel(), C.c_void_p(stream)))
+
     def timed_out(self) -> bool:
         import ctypes as C
         flag = C.c_int()

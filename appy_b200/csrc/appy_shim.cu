@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "../../include/appy_sm100.h"
+#include "templates/t_flat.cuh"      // peer-mailbox exchange used by appy_p2p_combine
 
 namespace {
 
@@ -666,14 +667,10 @@ struct P2PContext {
   void* d_desc = nullptr;       // device copy of the descriptor the kernels read
   unsigned* d_err = nullptr;
   bool loopback = false;
+  bool opened = false;
 };
 
-struct MailboxDesc {            // must match `appy_mailbox` in templates/t_flat.cuh
-  int world, rank;
-  unsigned spin_limit, reserved;
-  unsigned* err;
-  unsigned long long* peer[16];
-};
+typedef appy_mailbox MailboxDesc;   // the descriptor the kernels read (templates/t_flat.cuh)
 
 int appy_p2p_create(int world, int rank, void** ctx, void* ipc_handle_out) {
   if (!ctx || !ipc_handle_out || world < 1 || world > 16 || rank < 0 || rank >= world)
@@ -723,7 +720,61 @@ int appy_p2p_open(void* ctx, const void* all_handles, unsigned spin_limit, void*
   d.err = c->d_err;
   for (int r = 0; r < c->world; ++r) d.peer[r] = static_cast<unsigned long long*>(c->peers[r]);
   CK(cudaMemcpy(c->d_desc, &d, sizeof d, cudaMemcpyHostToDevice));
+  c->opened = true;
   *device_descriptor = c->d_desc;
+  return APPY_OK;
+}
+
+}  // extern "C"
+
+namespace {
+// One warp: exchange up to four device scalars with all ranks and fold them in rank order, in place.
+template <class Op, class T>
+__global__ void __launch_bounds__(32) k_p2p_combine(const appy_mailbox* mb, u64 seq, T* values, int count) {
+  u64 x[4];
+#pragma unroll
+  for (int v = 0; v < 4; ++v) x[v] = v < count ? appy_to_bits<T>(values[v]) : 0ull;
+  const bool ok = appy_p2p_exchange<4>(mb, seq, x);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    T t = appy_p2p_fold<Op, T>(mb, x[v]);
+    if (!ok) t = appy_p2p_poison<T>(t);
+    if (threadIdx.x == 0 && v < count) values[v] = t;
+  }
+}
+template <class T>
+cudaError_t launch_p2p_combine(int op, const appy_mailbox* mb, u64 seq, void* values, int count, cudaStream_t s) {
+  T* v = static_cast<T*>(values);
+  switch (op) {
+    case APPY_OP_ADD: k_p2p_combine<appy_add, T><<<1, 32, 0, s>>>(mb, seq, v, count); break;
+    case APPY_OP_MUL: k_p2p_combine<appy_mul, T><<<1, 32, 0, s>>>(mb, seq, v, count); break;
+    case APPY_OP_MAX: k_p2p_combine<appy_max, T><<<1, 32, 0, s>>>(mb, seq, v, count); break;
+    default:          k_p2p_combine<appy_min, T><<<1, 32, 0, s>>>(mb, seq, v, count); break;
+  }
+  return cudaGetLastError();
+}
+}  // namespace
+
+extern "C" {
+
+int appy_p2p_combine(void* ctx, uint64_t seq, int op, int dtype, void* dvalues, int count, void* stream) {
+  if (!ctx || !dvalues) return fail(APPY_ERR_ARG, "appy_p2p_combine: NULL argument");
+  if (count < 1 || count > 4) return fail(APPY_ERR_ARG, "appy_p2p_combine: count must be 1..4");
+  if (op < APPY_OP_ADD || op > APPY_OP_MIN) return fail(APPY_ERR_ARG, "appy_p2p_combine: unknown operator %d", op);
+  P2PContext* c = static_cast<P2PContext*>(ctx);
+  if (!c->opened) return fail(APPY_ERR_ARG, "appy_p2p_combine: appy_p2p_open has not been called");
+  const appy_mailbox* mb = static_cast<const appy_mailbox*>(c->d_desc);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  switch (dtype) {
+    case APPY_F32: e = launch_p2p_combine<float>(op, mb, seq, dvalues, count, s); break;
+    case APPY_F64: e = launch_p2p_combine<double>(op, mb, seq, dvalues, count, s); break;
+    case APPY_I32: e = launch_p2p_combine<int>(op, mb, seq, dvalues, count, s); break;
+    case APPY_I64: e = launch_p2p_combine<i64>(op, mb, seq, dvalues, count, s); break;
+    default: return fail(APPY_ERR_ARG, "appy_p2p_combine: unknown dtype %d", dtype);
+  }
+  if (e != cudaSuccess) return fail(APPY_ERR_CUDA, "appy_p2p_combine launch failed: %s", cudaGetErrorString(e));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   return APPY_OK;
 }
 

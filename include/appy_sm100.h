@@ -141,6 +141,14 @@ int appy_p2p_open(void* ctx, const void* all_handles /* world x 64 bytes */, uns
                   void** device_descriptor);
 int appy_p2p_status(void* ctx, int* timed_out);
 int appy_p2p_destroy(void* ctx);
+/* Combine `count` (1..4) device scalars of one type across all ranks, in place: every rank ends with
+ * the fold, in rank order, of all ranks' values.  For callers of the prebuilt kernels, whose results
+ * are per-GPU (the generated kernels do this exchange in their own tail).  `seq` numbers the
+ * combining launches of this context: it starts at 1 and grows by one per launch that uses the
+ * mailboxes (this call or a `combine="p2p"` kernel), identically on all ranks. */
+enum { APPY_OP_ADD = 0, APPY_OP_MUL = 1, APPY_OP_MAX = 2, APPY_OP_MIN = 3 };
+enum { APPY_F32 = 0, APPY_F64 = 1, APPY_I32 = 2, APPY_I64 = 3 };
+int appy_p2p_combine(void* ctx, uint64_t seq, int op, int dtype, void* dvalues, int count, void* stream);
 
 /* ---- prebuilt instantiations of the five templates (float32 / int32) ----
  * Device pointers; asynchronous on `stream`.  Each is the canonical

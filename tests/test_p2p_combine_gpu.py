@@ -64,6 +64,29 @@ def test_missing_rank_times_out_with_a_status_not_a_hang(rt):
         mg.set_combiner(None)
 
 
+def test_standalone_combine_of_prebuilt_kernel_results_one_rank(rt):
+    """appy_p2p_combine on one rank is the identity fold; the sequence numbers interleave with a
+    combine="p2p" loop on the same context."""
+    mg.set_combiner(None)
+    c = mg.enable_p2p()
+    try:
+        v = torch.tensor([1.5, -2.0, 7.25], dtype=torch.float64, device="cuda")
+        c.combine(v, "+")
+        a = W.vec_sum(1 << 16, seed=6)
+        s, _m = sum_and_max(torch.from_numpy(a).cuda())
+        w = torch.tensor([3, 9], dtype=torch.int32, device="cuda")
+        c.combine(w, "max")
+        torch.cuda.synchronize()
+        assert v.tolist() == [1.5, -2.0, 7.25] and w.tolist() == [3, 9]
+        assert np.isclose(s, float(np.sum(a, dtype=np.float64)), rtol=1e-5, atol=0)
+        assert not c.timed_out()
+        with pytest.raises(ValueError):
+            c.combine(torch.zeros(5, device="cuda"))
+    finally:
+        c.close()
+        mg.set_combiner(None)
+
+
 @appy.jit(distribute=True)
 def d_vec_add(a, b, c):
     #pragma parallel for simd
@@ -143,6 +166,14 @@ def _rank_main(rank, world, port, out_dir):
             s, m = sum_and_max(da)
             assert np.isclose(s, total, rtol=1e-5, atol=0), (rank, s, total)
             assert m == big
+        # ---- a per-GPU result of a prebuilt C-ABI kernel combined with the standalone call
+        part = torch.zeros(2, dtype=torch.float64, device="cuda")
+        rt.check(rt.lib().appy_sum_f32(da.data_ptr(), da.numel(), part.data_ptr(), 1, None))
+        part[1] = float(rank + 1)
+        comb.combine(part[0:1], "+")
+        comb.combine(part[1:2], "max")
+        torch.cuda.synchronize()
+        assert np.isclose(part[0].item(), total, rtol=1e-5, atol=0) and part[1].item() == float(world)
         assert not comb.timed_out()
         # ---- the iteration space split over the ranks (`distribute=True`), replicated inputs
         x, y = W.vec_add(100003, seed=7)
