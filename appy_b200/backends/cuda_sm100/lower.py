@@ -84,7 +84,8 @@ class KernelPlan:
             return max(1, min((n_iter + rows - 1) // rows, 2 ** 31 - 1)), tun["P_BLOCK"], 0
         if k == "csrdense":
             rows = tun["P_ROWS"]
-            return max(1, min((n_iter + rows - 1) // rows, 2 ** 31 - 1)), 32 * tun["P_WARPS"], 0
+            dyn = tun["P_WARPS"] * tun["P_S"] * (self.info["row_bytes"] + 8) if "P_S" in tun else 0   # ring + barriers
+            return max(1, min((n_iter + rows - 1) // rows, 2 ** 31 - 1)), 32 * tun["P_WARPS"], dyn
         raise AssertionError(k)
 
 
@@ -941,7 +942,8 @@ class Lowering:
         nc = ncols if ncols == 32 * V * Tn else 0
         init_c = cast(*em.expr(z.body[0].value), elt)
         struct = f"{self.name}_body"
-        params = self._params(uses_ws=False)
+        bulk = bool(self.options.get("_bulk_rows")) and nc > 0 and V > 1
+        params = self._params(uses_ws=bulk)           # the bulk variant reports a wait that ran out at ws+8
         ptr = env.arrays[indptr]
         src = ['#include "t_csr_dense.cuh"', f"struct {struct} {{",
                f"  typedef {elt.c} Elt; typedef {off_ty} Off;"]
@@ -955,7 +957,20 @@ class Lowering:
                 f"{elt.c}>::bytes];")
         call = (f"appy_csr_dense<{V}, {Tn}, P_D, P_WARPS, P_ROWS, {nc}, P_ROLL, {ptr.ty.c}>"
                 f"(__body, {indptr}, __lo, __hi, {ncols}, __smem);")
+        if bulk:
+            # B rows travel by asynchronous bulk copies into a per-warp ring in shared memory
+            # (t_csr_dense_bulk.cuh); measured slower than register gathers for 512-byte rows, kept as an option
+            src[0] = '#include "t_csr_dense_bulk.cuh"'
+            smem += "\n  extern __shared__ __align__(128) unsigned char __dyn[];"
+            call = (f"appy_csr_dense_bulk<{V}, {Tn}, P_S, P_WARPS, P_ROWS, {nc}, {ptr.ty.c}>(__body, {indptr}, __lo, "
+                    f"__hi, __smem, __dyn, reinterpret_cast<unsigned*>(reinterpret_cast<char*>(__ws) + 8), 1u << 22);")
         src += self._kernel_wrapper(params, struct, call, smem, launch_bounds="32 * P_WARPS, P_MINB")
+        if bulk:
+            tun = {"P_WARPS": [8, 4, 16], "P_ROWS": [32, 16, 64], "P_S": [4, 8, 16], "P_MINB": [2, 1]}
+            return KernelPlan("csrdense", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr,
+                              uses_ws=True, vec=V,
+                              info={"template": "T5 CSR x dense (bulk-copy rows)", "ncols": ncols, "vector_width": V,
+                                    "indptr": indptr, "row_bytes": ncols * (elt.bits // 8)})
         small = V * Tn <= 4
         # a row that is one 16-byte pack per lane: 16 warps x 3 CTAs per SM, four gathers in flight per
         # warp, no rolling ring (634 us against 673 us for 8 warps x 4 CTAs with a ring of 8 on the

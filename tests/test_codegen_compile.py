@@ -187,3 +187,14 @@ def test_shared_reduction_with_inner_simd_loops_uses_the_group_lowering():
     assert "if (__g.lane == 0) __acc0" in code            # one lane of the group accumulates
     plan, code = build(src, scope, ordered_reduction=True)
     assert plan.uses_ws and "appy_ws_arrive" in code
+
+
+def test_bulk_copy_variant_of_the_csr_dense_template_compiles():
+    spmm = CASES["spmm"] if "spmm" in CASES else None
+    assert spmm is not None
+    src, scope = spmm[0], spmm[1]
+    plan, code = build(src, scope, _bulk_rows=True)
+    assert plan.info["template"].endswith("(bulk-copy rows)")
+    assert "appy_csr_dense_bulk<" in code and plan.uses_ws and "P_S" in plan.tunables
+    grid, block, dyn = plan.launch_config({k: v[0] for k, v in plan.tunables.items()}, 1000, 148)
+    assert dyn == 8 * 4 * (plan.info["row_bytes"] + 8) and block == 256
