@@ -191,6 +191,7 @@ class CompiledLoop:
         self.last_variant: Variant | None = None
         self.last_source: str | None = None
         self.memo: dict = {}
+        self.has_device_args = any(sg[0] == "A" and sg[1] == "cuda" for sg in self.arg_sigs)
         self.device = None
         self.sm_count = 148
 
@@ -563,18 +564,41 @@ class CompiledLoop:
         return cells
 
     def _memo_key(self, args):
+        """Key of the launch record.  Device tensors enter with their address and layout, host arrays
+        with their layout only (their device mirror is looked up on every call), scalars by value.
+        None: this call cannot use a record (a host array that is not C-contiguous)."""
         key = []
         for sig, v in zip(self.arg_sigs, args):
             if sig[0] == "A":
                 if sig[1] == "cuda":
                     key.append((v.data_ptr(), v.shape, v.stride()))
                 elif sig[1] == "np":
-                    key.append((v.__array_interface__["data"][0], v.shape, v.strides))
+                    if not v.flags.c_contiguous:
+                        return None
+                    key.append(v.shape)
                 else:
-                    key.append((v.data_ptr(), v.shape, v.stride()))
+                    if not v.is_contiguous():
+                        return None
+                    key.append(tuple(v.shape))
             else:
                 key.append(v)
         return tuple(key)
+
+    def _host_args(self, args, slots):
+        """(arrays, disjoint): the host arrays of a memoised call resolved again, and whether the
+        stored ones still overlap no other host array (the record was made under that assumption)."""
+        arrays = []
+        for argi, name, _slot in slots:
+            v = args[argi]
+            a = _Array()
+            a.name, a.tmp = name, None
+            a.pinnable = type(v) is np.ndarray or isinstance(v, np.ndarray)
+            h = v if a.pinnable else v.numpy()
+            a.obj, a.host, a.hptr, a.nbytes, a.dptr = h, True, h.ctypes.data, h.nbytes, 0
+            arrays.append(a)
+        spans = sorted((a.hptr, a.hptr + a.nbytes) for a in arrays if a.nbytes)
+        disjoint = all(spans[i][1] <= spans[i + 1][0] for i in range(len(spans) - 1))
+        return arrays, disjoint
 
     def __call__(self, *args):
         if len(args) != len(self.arg_names):
@@ -587,13 +611,21 @@ class CompiledLoop:
             rt.init(self.device)
             self.sm_count = rt.device_info(self.device)["sm_count"]
         mkey = self._memo_key(args)
-        memo = self.memo.get(mkey)
+        memo = self.memo.get(mkey) if mkey is not None else None
         if memo is not None:
-            # everything lives on the device and this exact call was seen before: launch straight away
-            handle, grid, block, smem, pack, seq_slot, memo_stream, cells = memo
+            # this exact call was seen before: launch straight away
+            handle, grid, block, smem, pack, seq_slot, memo_stream, cells, host_slots = memo
             torch = sys.modules.get("torch")
-            stream = _torch_stream(torch, self.device) if torch is not None else rt.stream(0)
-            if memo_stream is None or memo_stream == stream:     # a workspace belongs to one stream
+            if torch is not None and (self.has_device_args or not host_slots):
+                stream = _torch_stream(torch, self.device)      # orders with the producers of the device tensors
+            else:
+                stream = rt.stream(0)
+            harr, disjoint = self._host_args(args, host_slots) if host_slots else ((), True)
+            if disjoint and (memo_stream is None or memo_stream == stream):     # a workspace belongs to one stream
+                if host_slots:        # mirrors of the host arrays: look up, upload, patch into the arguments
+                    self._acquire_device(harr, stream)
+                    for a, (_argi, _name, slot) in zip(harr, host_slots):
+                        pack.values[slot].value = a.dptr
                 if cells:
                     self._pre_combine(cells)
                 if grid:
@@ -603,6 +635,11 @@ class CompiledLoop:
                     rt.launch(handle, grid, block, pack, smem, stream)
                 if cells:
                     self._post_combine(cells)
+                if host_slots:
+                    for a in harr:
+                        if a.name in self.stored and a.nbytes:
+                            rt.d2h(a.hptr, a.dptr, a.nbytes, stream)
+                    rt.sync(stream)
                 return
         arrays = self._resolve_arrays(args)
         any_host = any(a.host for a in arrays)
@@ -631,15 +668,28 @@ class CompiledLoop:
             h = variant.handle(tun)
             grid, block, smem = variant.plan.launch_config(tun, hi - lo, self.sm_count)
             rt.launch(h, grid, block, pack, smem, stream)
-            if not any_host:
+            # Launch record.  With host arrays it is kept when they are contiguous, none of them had to
+            # be copied to become so, the stored ones overlap nothing, and the loop does not distribute
+            # or combine (those paths look at the arrays again).
+            recordable = mkey is not None and (not any_host or (
+                key[1] and not cells and not self.options.get("distribute")
+                and variant.plan.kind != "csr"          # lanes per row follow the matrix, not only its shape
+                and all(a.tmp is None for a in arrays)))
+            if recordable:
                 if len(self.memo) > 256:
                     self.memo.clear()
                 kinds = [p.kind for p in variant.plan.params]
                 seq_slot = kinds.index("seq") if "seq" in kinds else None
+                host_slots = []
+                if any_host:
+                    pnames = [p.name if p.kind == "array" else None for p in variant.plan.params]
+                    for argi, (name, sig) in enumerate(zip(self.arg_names, self.arg_sigs)):
+                        if sig[0] == "A" and sig[1] != "cuda":
+                            host_slots.append((argi, name, pnames.index(name)))
                 self.memo[mkey] = (h, grid, block, smem, pack, seq_slot,
-                                   stream if variant.plan.uses_ws else None, cells)
-        elif not any_host:
-            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells)
+                                   stream if (variant.plan.uses_ws or any_host) else None, cells, tuple(host_slots))
+        elif not any_host and mkey is not None:
+            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells, ())
         if cells:
             self._post_combine(cells)
         if any_host:

@@ -787,3 +787,47 @@ def test_spmm_with_rows_fetched_by_bulk_copies(rt):
     rt.d2h(status.ctypes.data, rt.workspace(stream) + 8, 4, stream)
     rt.sync(stream)
     assert status[0] == 0
+
+
+@appy.jit
+def host_axpy(alpha, x, y):
+    #pragma parallel for simd
+    for i in range(x.shape[0]):
+        y[i] = alpha * x[i] + y[i]
+
+
+@appy.jit
+def host_shift(src, dst):
+    #pragma parallel for simd
+    for i in range(dst.shape[0]):
+        dst[i] = src[i] + 1.0
+
+
+def test_repeated_calls_with_host_arrays_reuse_the_launch_record_safely():
+    """Calls with NumPy arguments are memoised by layout; what the record assumed is checked again on
+    every call: other arrays of the same shape, the same array passed twice (overlap), a strided view."""
+    rng = np.random.default_rng(21)
+    for trial in range(4):                                   # same shapes, different buffers and values
+        x = rng.uniform(-1, 1, 5001).astype(np.float32)
+        y = rng.uniform(-1, 1, 5001).astype(np.float32)
+        ref = np.float32(0.5) * x + y
+        host_axpy(0.5, x, y)
+        assert np.array_equal(y, ref)
+    z = rng.uniform(-1, 1, 5001).astype(np.float32)
+    ref = np.float32(0.5) * z + z
+    host_axpy(0.5, z, z)                                     # x and y are the same buffer
+    assert np.array_equal(z, ref)
+    big = rng.uniform(-1, 1, 10002).astype(np.float32)
+    xv, yv = big[0::2], big[1::2].copy()                     # a strided host view takes the copying path
+    ref = np.float32(0.5) * xv + yv
+    host_axpy(0.5, xv, yv)
+    assert np.array_equal(yv, ref)
+    buf = rng.uniform(-1, 1, 6000).astype(np.float32)        # overlapping, shifted views of one buffer
+    a, b = buf[:5001].copy(), np.empty(5001, np.float32)
+    host_shift(a, b)
+    host_shift(a, b)
+    assert np.array_equal(b, a + np.float32(1.0))
+    src, dst = buf[0:5001], buf[500:5501]
+    expect = src.copy() + np.float32(1.0)
+    host_shift(src, dst)                                     # a record exists for this layout; the overlap is seen
+    assert np.array_equal(dst, expect)
