@@ -354,18 +354,23 @@ class CompiledLoop:
                 vals.append(C.c_uint64(multi_gpu.combiner().next_seq()))
         return rt.ArgPack(vals)
 
-    def _inner_trip(self, plan, scope):
-        """Trip count of the (first) inner simd loop for this call, or None when it is not known on the host."""
+    def _inner_trip(self, plan, scope, lo=0, hi=0):
+        """Trip count of the (first) inner simd loop for this call, or None when it is not known on the
+        host.  Bounds that depend on the outer index (triangular loops) are taken at the middle of the
+        outer range, which is the mean row length for a linear dependence."""
         hi_n, lo_n = plan.info.get("inner_hi"), plan.info.get("inner_lo")
         if hi_n is None:
             return None
-        try:
-            return max(0, int(eval(compile(ast.Expression(body=hi_n), "<t>", "eval"), {}, scope)) -
-                       int(eval(compile(ast.Expression(body=lo_n), "<t>", "eval"), {}, scope)))
-        except Exception:
-            return None
+        for extra in ({}, {plan.info.get("outer_var", "_"): (lo + hi) // 2}):
+            try:
+                sc = dict(scope, **extra) if extra else scope
+                return max(0, int(eval(compile(ast.Expression(body=hi_n), "<t>", "eval"), {}, sc)) -
+                           int(eval(compile(ast.Expression(body=lo_n), "<t>", "eval"), {}, sc)))
+            except Exception:
+                continue
+        return None
 
-    def _shape_class(self, variant: Variant, scope, arrays, n_iter: int, stream):
+    def _shape_class(self, variant: Variant, scope, arrays, n_iter: int, stream, lo: int = 0):
         """(class, overrides): launches of one class share their tunables; the overrides are the
         defaults this class starts from.  The class is what the choice depends on beyond the code
         itself: the inner trip count for row loops, the row-length profile of the matrix for CSR
@@ -373,7 +378,7 @@ class CompiledLoop:
         plan = variant.plan
         bucket = max(n_iter, 1).bit_length()
         if plan.kind in ("group", "rowdot"):
-            trip = self._inner_trip(plan, scope)
+            trip = self._inner_trip(plan, scope, lo, lo + n_iter)
             if trip is None:
                 return ("rows", bucket, None), {}
             ov = {}
@@ -440,7 +445,7 @@ class CompiledLoop:
         forced = getattr(variant, "forced_tun", None)        # experiments and sweeps
         if forced is not None:
             return forced
-        cls, ov = self._shape_class(variant, scope, arrays, hi - lo, stream)
+        cls, ov = self._shape_class(variant, scope, arrays, hi - lo, stream, lo)
         tun = variant.choice.get(cls)
         if tun is None:
             tun = dict(variant.tun, **{k: v for k, v in ov.items() if k in variant.tun})

@@ -670,7 +670,8 @@ class Lowering:
             tun["P_CTAS"] = [8, 4, 16]          # persistent grid: one commit per CTA
         inner = next((n for st in body for n in ast.walk(st) if isinstance(n, ast.For) and _is_simd(n)), None)
         if inner is not None and isinstance(inner.iter, ast.Call) and len(inner.iter.args) >= 2:
-            info.update({"inner_lo": inner.iter.args[0], "inner_hi": inner.iter.args[1]})   # lanes per row follow it
+            info.update({"inner_lo": inner.iter.args[0], "inner_hi": inner.iter.args[1],    # lanes per row follow it
+                         "outer_var": self.var})
         return KernelPlan("group", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr,
                           uses_ws=ordered, info=info)
 
@@ -842,7 +843,7 @@ class Lowering:
                "P_MINB": [0, 1, 2]}
         return KernelPlan("rowdot", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr, vec=V,
                           info={"template": "T4 row-dot", "vector_width": V, "inner_lo": loop.iter.args[0],
-                                "inner_hi": loop.iter.args[1], "streams": len(streams)})
+                                "inner_hi": loop.iter.args[1], "streams": len(streams), "outer_var": self.var})
 
     # ------------------------------------------------------------------ T5: CSR x dense
     def try_csrdense(self):

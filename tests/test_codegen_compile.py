@@ -198,3 +198,16 @@ def test_bulk_copy_variant_of_the_csr_dense_template_compiles():
     assert "appy_csr_dense_bulk<" in code and plan.uses_ws and "P_S" in plan.tunables
     grid, block, dyn = plan.launch_config({k: v[0] for k, v in plan.tunables.items()}, 1000, 148)
     assert dyn == 8 * 4 * (plan.info["row_bytes"] + 8) and block == 256
+
+
+def test_triangular_inner_ranges_are_sized_by_their_mean_length():
+    A = np.ones((64, 64), f32)
+    src = "#pragma parallel for\nfor i in range(n):\n    #pragma simd\n    for j in range(0, i + 1):\n        C[i, j] = C[i, j] * 2.0"
+    scope = dict(C=A, n=64)
+    vm = dispatcher.build_val_map(src, scope, {"np": np, "math": math})
+    e = cg.CompiledLoop(src, "kernel_loop_1", list(vm), tuple(cg._kind_of(v) for v in vm.values()), {})
+    e.source_for(*[v for v in vm.values() if not isinstance(v, types.ModuleType)])
+    v = list(e.variants.values())[0]
+    assert e._inner_trip(v.plan, dict(n=8192), 0, 8192) == 4097          # taken at the middle row
+    assert e._shape_class(v, dict(n=8192), [], 8192, 0)[1]["P_G"] == 0   # long rows on average: a CTA each
+    assert e._shape_class(v, dict(n=40), [], 40, 0)[1]["P_G"] in (4, 8)
