@@ -757,7 +757,7 @@ def _register_finalizer(obj, hptr: int) -> None:
 
 
 _OPTION_KEYS = ("ordered_reduction", "combine", "distribute", "fp_contract", "autotune", "pin_host", "_generic_only", "_vectorize",
-                "_stream_hint", "_hoist_safe", "_shape_spec", "_neighbours", "_bulk_rows")
+                "_stream_hint", "_hoist_safe", "_shape_spec", "_neighbours", "_bulk_rows", "_group_vectorize")
 
 
 def codegen(loop_source: str, loop_name: str, val_map: dict, options: dict):

@@ -387,17 +387,20 @@ class Lowering:
         return out
 
     # ------------------------------------------------------------------ FLAT (T1 / T2)
-    def _stream_accesses(self, V: int):
+    def _stream_accesses(self, V: int, body=None, var=None):
         """Classify subscripts for the vector path.  Returns (loads, stores):
         loads  : {text: (array, node)} hoistable 16-byte loads at index exactly `i`
         stores : {text: (array, node)} unconditional top-level stores at index exactly `i`."""
-        body = self.loop.body
+        inner = body is not None          # an inner simd loop of the group lowering: (body, var) given
+        body = self.loop.body if body is None else body
+        var = self.var if var is None else var
         if V == 1:
             return {}, {}
-        st_arr = stored_arrays(body)
+        st_arr = stored_arrays(self.loop.body)        # stored anywhere in the kernel
         ld_arr = loaded_arrays(body)
         loads, stores = {}, {}
-        hoist_cond_ok = self.options.get("_hoist_safe", True)
+        hoist_cond_ok = self.options.get("_hoist_safe", True) and not inner
+        never = conditional_loads(body) if inner else set()
 
         def arr_ok(name):
             a = self.args.get(name)
@@ -409,12 +412,15 @@ class Lowering:
         for k, st in enumerate(body):
             if isinstance(st, ast.Assign) and isinstance(st.targets[0], ast.Subscript):
                 tgt = st.targets[0]
-                if isinstance(tgt.value, ast.Name) and arr_ok(tgt.value.id) and _last_index_offset(tgt, self.var) == 0:
+                if isinstance(tgt.value, ast.Name) and arr_ok(tgt.value.id) and _last_index_offset(tgt, var) == 0:
                     name = tgt.value.id
                     # every other store to this array must be this same element
                     others = [n for s2 in body for n in ast.walk(s2)
                               if isinstance(n, ast.Subscript) and isinstance(n.ctx, ast.Store)
                               and isinstance(n.value, ast.Name) and n.value.id == name]
+                    telts = tgt.slice.elts if isinstance(tgt.slice, ast.Tuple) else [tgt.slice]
+                    if any((_names_in(e) - {self.var, var}) & set(self._assigned_locals()) for e in telts[:-1]):
+                        continue
                     if len(others) == 1:
                         stores[ast.unparse(tgt)] = (name, tgt)
                         store_stmt_index[name] = k
@@ -425,7 +431,7 @@ class Lowering:
                 if not (isinstance(n, ast.Subscript) and isinstance(n.ctx, ast.Load) and isinstance(n.value, ast.Name)):
                     continue
                 name = n.value.id
-                if not arr_ok(name) or _last_index_offset(n, self.var) != 0:
+                if not arr_ok(name) or _last_index_offset(n, var) != 0 or id(n) in never:
                     continue
                 if name in st_arr:
                     # read-modify-write of the same element: only loads at or before the single store
@@ -438,7 +444,7 @@ class Lowering:
                     continue
                 # indices other than the last must not depend on loop-local values
                 elts = n.slice.elts if isinstance(n.slice, ast.Tuple) else [n.slice]
-                if any((_names_in(e) - {self.var}) & set(self._assigned_locals()) for e in elts[:-1]):
+                if any((_names_in(e) - {self.var, var}) & set(self._assigned_locals()) for e in elts[:-1]):
                     continue
                 loads[ast.unparse(n)] = (name, n)
         # a stored array that is also loaded somewhere not covered above cannot use a deferred vector store
@@ -455,7 +461,7 @@ class Lowering:
         # The pack of `a[.., i]` plus |d| scalar elements on the side holds every operand, so each
         # element travels from L1 to registers once instead of once per offset.
         self.neighbours = {}
-        if self.options.get("_neighbours", True):
+        if self.options.get("_neighbours", True) and not inner:
             cond = conditional_loads(body)
             for st in body:
                 if isinstance(st, (ast.If, ast.For, ast.While)):
@@ -621,6 +627,7 @@ class Lowering:
         ge = GroupEmitter(self.env, hazard_arrays)
         ge.load_override = self.em.load_override
         ge.store_override = self.em.store_override
+        ge.lowering = self
         return ge
 
     def lower_group(self) -> KernelPlan:
@@ -1016,6 +1023,63 @@ class GroupEmitter(Emitter):
             lines = lines + ["__g.barrier();"]
         return lines
 
+    def _vector_plan(self, st, v):
+        """(V, loads, stores) when the simd loop `st` over `v` can move 16-byte packs, else None."""
+        low = getattr(self, "lowering", None)
+        if low is None or not low.options.get("_vectorize", True) or not low.options.get("_group_vectorize", True):
+            return None
+        sizes = [low.args[n.value.id].itemsize for b in st.body for n in _subscripts(b)
+                 if n.value.id in low.args and low.args[n.value.id].kind == "array" and _last_index_offset(n, v) == 0]
+        if not sizes:
+            return None
+        V0 = max(1, 16 // max(sizes))
+        for V in (V0, V0 // 2):
+            if V >= 2:
+                loads, stores = low._stream_accesses(V, st.body, v)
+                if loads or stores:
+                    return V, loads, stores
+        return None
+
+    def _vector_loop(self, st, v, lo, hi, V, loads, stores):
+        """The simd loop as a loop over chunks of V consecutive iterations, aligned to multiples of V in
+        absolute index space: chunks wholly inside [lo, hi) move packs, the ragged ones run element-wise."""
+        env = self.env
+        out = [f"  const i64 __vlo = ({lo}), __vhi = ({hi});",
+               f"  const i64 __c_lo = appy_floor_div_i64(__vlo, {V}), __c_hi = (__vhi > __vlo) ? appy_floor_div_i64(__vhi - 1, {V}) + 1 : __c_lo;",
+               f"  const i64 __cf_lo = appy_floor_div_i64(__vlo + {V - 1}, {V}), __cf_hi = appy_floor_div_i64(__vhi, {V});",
+               "#pragma unroll 2",
+               "  for (i64 __c = __c_lo + __g.lane; __c < __c_hi; __c += __g.size()) {",
+               f"    const i64 __j0 = __c * {V};",
+               "    if (__c >= __cf_lo && __c < __cf_hi) {"]
+        saved_l, saved_s = dict(self.load_override), dict(self.store_override)
+        tail = []
+        for n_l, (text, (name, node)) in enumerate(loads.items()):
+            arr = env.arrays[name]
+            off, _ = Emitter(env).offset(_replace_index(node, v, "__j0"))
+            ld = "appy_ld_nc" if arr.readonly else "appy_ld"
+            out.append(f"      const appy_pack<{arr.ty.c}, {V}> __v{n_l} = {ld}<{arr.ty.c}, {V}>({name} + ({off}));")
+            self.load_override[text] = (f"__v{n_l}.v[__k]", arr.ty)
+        for n_o, (text, (name, node)) in enumerate(stores.items()):
+            arr = env.arrays[name]
+            off, _ = Emitter(env).offset(_replace_index(node, v, "__j0"))
+            out.append(f"      appy_pack<{arr.ty.c}, {V}> __o{n_o};")
+            self.store_override[text] = (lambda code, t, o=f"__o{n_o}", ty=arr.ty: [f"{o}.v[__k] = {cast(code, t, ty)};"])
+            tail.append(f"      appy_st<{arr.ty.c}, {V}>({name} + ({off}), __o{n_o});")
+        out += ["#pragma unroll", f"      for (int __k = 0; __k < {V}; ++__k) {{", f"        const i64 {v} = __j0 + __k;"]
+        out += self.block(st.body, "        ")
+        out += ["      }"] + tail + ["    } else {"]
+        for text in list(loads) + list(stores):          # the ragged chunks use plain element accesses
+            for table, saved in ((self.load_override, saved_l), (self.store_override, saved_s)):
+                if text in saved:
+                    table[text] = saved[text]
+                else:
+                    table.pop(text, None)
+        out += [f"      for (int __k = 0; __k < {V}; ++__k) {{", f"        const i64 {v} = __j0 + __k;",
+                f"        if ({v} >= __vlo && {v} < __vhi) {{"]
+        out += self.block(st.body, "          ")
+        out += ["        }", "      }", "    }", "  }"]
+        return out
+
     def s_For(self, st):
         if self.in_simd or not _is_simd(st):
             return super().s_For(st)
@@ -1051,11 +1115,15 @@ class GroupEmitter(Emitter):
             out.append("  const i64 __slo = __l0 + (__len > 0 ? __len * __g.seg / P_SEG : 0);")
             out.append("  const i64 __shi = __l0 + (__len > 0 ? __len * (__g.seg + 1) / P_SEG : 0);")
             lo, hi = "__slo", "__shi"
-        # iterations of a simd loop are independent: unrolled, a lane has several of them in flight
-        out.append("#pragma unroll 4")
-        out.append(f"  for (i64 {v} = ({lo}) + __g.lane; {v} < {hi}; {v} += __g.size()) {{")
-        out += self.block(st.body, "    ")
-        out.append("  }")
+        vec = self._vector_plan(st, v)
+        if vec is not None:
+            out += self._vector_loop(st, v, lo, hi, *vec)
+        else:
+            # iterations of a simd loop are independent: unrolled, a lane has several of them in flight
+            out.append("#pragma unroll 4")
+            out.append(f"  for (i64 {v} = ({lo}) + __g.lane; {v} < {hi}; {v} += __g.size()) {{")
+            out += self.block(st.body, "    ")
+            out.append("  }")
         self.store_guard = guard
         self.in_simd = False
         self.load_override, self.store_override = saved_l, saved_s

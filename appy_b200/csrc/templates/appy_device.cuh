@@ -155,6 +155,12 @@ template <class Op, class T> APPY_DEV T appy_block_reduce(T v, T* smem) {
   return r;
 }
 
+// floor(a / b) for chunk arithmetic on signed iteration ranges
+APPY_DEV i64 appy_floor_div_i64(i64 a, i64 b) {
+  i64 q = a / b;
+  return (a % b != 0 && ((a < 0) != (b < 0))) ? q - 1 : q;
+}
+
 // Element `idx` of the run [lo[NL-1] .. lo[0], p.v[0] .. p.v[V-1], hi[0] .. hi[NH-1]] (a pack with the
 // scalar elements below and above it).  `idx` is a constant after unrolling, so this is a register pick.
 template <class T, int V, int NL, int NH>

@@ -23,11 +23,6 @@
 #pragma once
 #include "appy_device.cuh"
 
-APPY_DEV i64 appy_floor_div_i64(i64 a, i64 b) {
-  i64 q = a / b;
-  return (a % b != 0 && ((a < 0) != (b < 0))) ? q - 1 : q;
-}
-
 template <int V, int U, class Body>
 APPY_DEV void appy_flat(Body& body, i64 lo, i64 hi, void* smem) {
   if (hi > lo) {
