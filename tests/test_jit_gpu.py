@@ -831,3 +831,31 @@ def test_repeated_calls_with_host_arrays_reuse_the_launch_record_safely():
     expect = src.copy() + np.float32(1.0)
     host_shift(src, dst)                                     # a record exists for this layout; the overlap is seen
     assert np.array_equal(dst, expect)
+
+
+@appy.jit
+def rows_window_update(a, b, c, lo, hi):
+    #pragma parallel for
+    for i in range(a.shape[0]):
+        #pragma simd
+        for j in range(lo, hi):
+            c[i, j] = 2.0 * a[i, j] - b[i, j] + c[i, j]
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("shape,lo,hi", [((7, 40), 0, 40), ((7, 40), 1, 39), ((5, 64), 3, 10), ((5, 64), 9, 9),
+                                         ((3, 100004), 1, 100003), ((300, 36), 2, 35), ((4, 37), 0, 37)])
+def test_inner_simd_loops_with_packs_and_ragged_ends(dtype, shape, lo, hi):
+    """Inner simd loops of the group lowering move 16-byte packs where whole aligned chunks lie inside
+    [lo, hi) and run element-wise at the ragged ends (and everywhere when rows are not 16-byte
+    aligned, as for 37 columns); elements outside the window stay untouched.  Bit-exact vs NumPy."""
+    import torch
+    rng = np.random.default_rng(shape[1] + lo)
+    a = rng.uniform(-1, 1, shape).astype(dtype)
+    b = rng.uniform(-1, 1, shape).astype(dtype)
+    c = rng.uniform(-1, 1, shape).astype(dtype)
+    ref = c.copy()
+    ref[:, lo:hi] = dtype(2.0) * a[:, lo:hi] - b[:, lo:hi] + c[:, lo:hi]
+    da, db, dc = (torch.from_numpy(v).cuda() for v in (a, b, c))
+    rows_window_update(da, db, dc, lo, hi)
+    assert np.array_equal(dc.cpu().numpy(), ref)
