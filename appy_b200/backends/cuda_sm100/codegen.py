@@ -228,7 +228,9 @@ class CompiledLoop:
             arrays.append(a)
         return arrays
 
-    def _acquire_device(self, arrays, stream):
+    def _acquire_device(self, arrays, stream, slices=None):
+        """Device mirrors of the host arrays, filled from the host.  `slices` (distributed loops):
+        {array name: (first byte, one past last byte)} for arrays of which this rank touches only a part."""
         for a in arrays:
             if not a.host:
                 continue
@@ -236,6 +238,8 @@ class CompiledLoop:
                 a.dptr = 0
                 continue
             a.dptr, _created = rt.mirror(a.hptr, a.nbytes)
+            b0, b1 = slices.get(a.name, (0, a.nbytes)) if slices else (0, a.nbytes)
+            transfer_stats["h2d"] += max(0, b1 - b0)
             pinned = a.hptr in _finalizers
             if a.nbytes >= _PIN_MIN_BYTES and a.tmp is None and a.pinnable and self.options.get("pin_host", True) \
                     and not pinned:
@@ -250,10 +254,12 @@ class CompiledLoop:
                         pinned = a.hptr in _finalizers
                     except rt.AppyRuntimeError:
                         pass
+            if b1 <= b0:
+                continue
             if pinned or a.nbytes < _PIN_MIN_BYTES:
-                rt.h2d(a.dptr, a.hptr, a.nbytes, stream)          # true DMA, or too small to matter
+                rt.h2d(a.dptr + b0, a.hptr + b0, b1 - b0, stream)          # true DMA, or too small to matter
             else:
-                rt.h2d_staged(a.dptr, a.hptr, a.nbytes, stream)   # pageable: pinned staging buffers
+                rt.h2d_staged(a.dptr + b0, a.hptr + b0, b1 - b0, stream)   # pageable: pinned staging buffers
 
     def _spec_key(self, arrays):
         key = []
@@ -525,6 +531,74 @@ class CompiledLoop:
                         f"parallel index `{var}` in its leading dimension")
         self._dist_checked = True
 
+    def _shard_classes(self, variant) -> dict:
+        """Which arrays a rank touches only in part when the outer range is split:
+        "rows"  every subscript has the parallel index itself as its leading index;
+        "nnz"   (CSR loops) every subscript is the index of an inner loop that runs from
+                indptr[i] to indptr[i+1].  Everything else (gathered or shifted operands) is whole."""
+        cached = getattr(variant, "shard_classes", None)
+        if cached is not None:
+            return cached
+        loop = self.ir.loop
+        var = loop.target.id
+        indptr = variant.plan.info.get("indptr")
+        nnz_vars = set()
+        if indptr:
+            bound = {}      # local name -> "lo" / "hi" when assigned from indptr[i] / indptr[i + 1]
+            for n in ast.walk(loop):
+                if isinstance(n, ast.Assign) and isinstance(n.targets[0], ast.Name) and isinstance(n.value, ast.Subscript) \
+                        and isinstance(n.value.value, ast.Name) and n.value.value.id == indptr:
+                    txt = ast.unparse(n.value.slice).replace(" ", "")
+                    if txt == var:
+                        bound[n.targets[0].id] = "lo"
+                    elif txt in (f"{var}+1", f"1+{var}"):
+                        bound[n.targets[0].id] = "hi"
+            for n in ast.walk(loop):
+                if isinstance(n, ast.For) and n is not loop and isinstance(n.iter, ast.Call) and len(n.iter.args) >= 2:
+                    a0, a1 = n.iter.args[0], n.iter.args[1]
+                    if isinstance(a0, ast.Name) and isinstance(a1, ast.Name) and bound.get(a0.id) == "lo" \
+                            and bound.get(a1.id) == "hi":
+                        nnz_vars.add(n.target.id)
+        seen = {}
+        for n in ast.walk(loop):
+            if not (isinstance(n, ast.Subscript) and isinstance(n.value, ast.Name)):
+                continue
+            name = n.value.id
+            elts = n.slice.elts if isinstance(n.slice, ast.Tuple) else [n.slice]
+            first = elts[0]
+            if isinstance(first, ast.Name) and first.id == var:
+                kind = "rows"
+            elif len(elts) == 1 and isinstance(first, ast.Name) and first.id in nnz_vars:
+                kind = "nnz"
+            else:
+                kind = None
+            seen[name] = kind if seen.get(name, kind) == kind else None
+        variant.shard_classes = {k: v for k, v in seen.items() if v and k != indptr}
+        return variant.shard_classes
+
+    def _rank_slices(self, variant, arrays, lo, hi) -> dict:
+        """Byte ranges of the host arrays this rank needs for its sub-range [lo, hi) (see _shard_classes)."""
+        out = {}
+        classes = self._shard_classes(variant)
+        by_name = {a.name: a for a in arrays}
+        ip = by_name.get(variant.plan.info.get("indptr")) if variant.plan.info.get("indptr") else None
+        for a in arrays:
+            kind = classes.get(a.name)
+            if not a.host or kind is None or not a.shape:
+                continue
+            if hi <= lo:
+                out[a.name] = (0, 0)
+            elif kind == "rows":
+                row = (a.nbytes // a.shape[0]) if a.shape[0] else 0
+                out[a.name] = (max(0, lo) * row, min(hi, a.shape[0]) * row)
+            elif ip is not None:
+                host = ip.obj if ip.host else None
+                if host is None:
+                    continue
+                k0, k1 = int(host[lo]), int(host[hi])
+                out[a.name] = (k0 * a.itemsize, min(k1 * a.itemsize, a.nbytes))
+        return out
+
     def _rank_range(self, variant, arrays, lo, hi):
         from . import multi_gpu
         rank, world_size = multi_gpu.world()
@@ -653,17 +727,23 @@ class CompiledLoop:
             stream = _torch_stream(torch, self.device)     # orders with torch ops and with collectives
         else:
             stream = rt.stream(0)
-        self._acquire_device(arrays, stream)
-        key = self._spec_key(arrays)
+        from . import multi_gpu
+        sharded = bool(self.options.get("distribute")) and any_host and multi_gpu.world()[1] > 1
+        if not sharded:
+            self._acquire_device(arrays, stream)
+        key = self._spec_key(arrays)       # mirrors are 16-byte aligned whether or not they exist yet
         variant = self._variant(arrays, key)
         self.last_variant = variant
         scope = self._scope(args, arrays)
         lo = int(eval(variant.lo_code, {}, scope))
         hi = int(eval(variant.hi_code, {}, scope))
         cells = []
+        slices = None
         if self.options.get("distribute"):
             lo, hi = self._rank_range(variant, arrays, lo, hi)
-            from . import multi_gpu
+            if sharded:      # every rank uploads only the part of the row- and nnz-indexed arrays it works on
+                slices = self._rank_slices(variant, arrays, lo, hi)
+                self._acquire_device(arrays, stream, slices)
             if multi_gpu.world()[1] > 1 and self.options.get("combine") != "p2p":
                 cells = self._reduction_cells(args, arrays)
                 self._pre_combine(cells)
@@ -700,7 +780,10 @@ class CompiledLoop:
         if any_host:
             for a in arrays:
                 if a.host and a.name in self.stored and a.nbytes:
-                    rt.d2h(a.hptr, a.dptr, a.nbytes, stream)
+                    b0, b1 = slices.get(a.name, (0, a.nbytes)) if slices else (0, a.nbytes)
+                    if b1 > b0:
+                        rt.d2h(a.hptr + b0, a.dptr + b0, b1 - b0, stream)
+                        transfer_stats["d2h"] += b1 - b0
             rt.sync(stream)
             for a in arrays:
                 if a.host and a.tmp is not None:
@@ -730,6 +813,7 @@ class CompiledLoop:
 
 
 _finalizers: dict = {}
+transfer_stats = {"h2d": 0, "d2h": 0}      # bytes moved for host arrays (tests read this)
 
 
 def _register_finalizer(obj, hptr: int) -> None:

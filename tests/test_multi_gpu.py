@@ -71,3 +71,43 @@ def test_split_range_is_aligned_and_exact():
         assert cuts[0][0] == 0 and cuts[-1][1] == n
         assert all(a[1] == b[0] for a, b in zip(cuts, cuts[1:]))
         assert all(c[0] % 32 == 0 for c in cuts[1:] if c[0] < n)
+
+
+def test_arrays_a_rank_touches_only_in_part():
+    """Host transfers of a distributed loop: arrays indexed by the parallel index (rows) or by the inner
+    index of a CSR row loop (non-zeros) travel in slices, gathered and shifted operands travel whole."""
+    import math
+    import types
+    from appy_b200 import dispatcher
+    from appy_b200.backends.cuda_sm100 import codegen as cg
+
+    def compiled(src, scope):
+        vm = dispatcher.build_val_map(src, scope, {"np": np, "math": math})
+        e = cg.CompiledLoop(src, "kernel_loop_1", list(vm), tuple(cg._kind_of(v) for v in vm.values()),
+                            {"distribute": True})
+        args = [v for v in vm.values() if not isinstance(v, types.ModuleType)]
+        e.source_for(*args)
+        return e, list(e.variants.values())[0], e._resolve_arrays(args)
+
+    f32 = np.float32
+    a = np.ones(1000, f32)
+    e, v, arrs = compiled("#pragma parallel for simd\nfor i in range(1, n - 1):\n    c[i] = a[i] + b[i - 1]",
+                          dict(a=a, b=a.copy(), c=a.copy(), n=1000))
+    assert e._shard_classes(v) == {"c": "rows", "a": "rows"}            # b is read at a shifted index: whole
+    assert e._rank_slices(v, arrs, 250, 500) == {"c": (1000, 2000), "a": (1000, 2000)}
+    assert e._rank_slices(v, arrs, 7, 7) == {"c": (0, 0), "a": (0, 0)}
+
+    A = np.ones((64, 32), f32)
+    e, v, arrs = compiled("#pragma parallel for\nfor i in range(M):\n    s = 0.0\n    #pragma simd\n"
+                          "    for j in range(N):\n        s += A[i, j] * x[j]\n    y[i] = s",
+                          dict(A=A, x=np.ones(32, f32), y=np.ones(64, f32), M=64, N=32))
+    assert e._shard_classes(v) == {"A": "rows", "y": "rows"}
+    assert e._rank_slices(v, arrs, 16, 32) == {"A": (16 * 128, 32 * 128), "y": (64, 128)}
+
+    P = np.array([0, 2, 2, 5, 9], np.int32)
+    e, v, arrs = compiled("#pragma parallel for\nfor i in range(M):\n    start, end = P[i], P[i+1]\n    s = 0.0\n"
+                          "    #pragma simd\n    for j in range(start, end):\n        s += D[j] * x[J[j]]\n    y[i] = s",
+                          dict(P=P, D=np.ones(9, f32), J=np.zeros(9, np.int32), x=np.ones(4, f32),
+                               y=np.ones(4, f32), M=4))
+    assert e._shard_classes(v) == {"D": "nnz", "J": "nnz", "y": "rows"}
+    assert e._rank_slices(v, arrs, 2, 4) == {"D": (8, 36), "J": (8, 36), "y": (8, 16)}

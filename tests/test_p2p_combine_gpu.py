@@ -178,17 +178,25 @@ def _rank_main(rank, world, port, out_dir):
         # ---- the iteration space split over the ranks (`distribute=True`), replicated inputs
         x, y = W.vec_add(100003, seed=7)
         z = np.full_like(x, np.nan)
+        from appy_b200.backends.cuda_sm100 import codegen as cg
+        cg.transfer_stats.update(h2d=0, d2h=0)
         d_vec_add(x, y, z)                                   # every rank fills only its range
         lo, hi = mg.split_range(0, x.size, world, rank)
         assert np.array_equal(z[lo:hi], (x + y)[lo:hi]) and np.all(np.isnan(np.delete(z, np.s_[lo:hi])))
+        # ... and moves only its range of the three row-indexed host arrays
+        assert cg.transfer_stats == {"h2d": 3 * 4 * (hi - lo), "d2h": 4 * (hi - lo)}
         ref = 1.5 + float(np.sum(x, dtype=np.float64))
         assert np.isclose(d_sum(x), ref, rtol=1e-6)          # NCCL/gloo combine of the shared scalar
         assert np.isclose(d_sum(torch.from_numpy(x).cuda()), ref, rtol=1e-6)
         assert np.isclose(d_sum_p2p(torch.from_numpy(x).cuda()), ref, rtol=1e-6)   # mailbox combine
         A, xv = W.spmv(20000, 16, kind="zipf", cap=2048, seed=8)
         yv = np.full(A.shape[0], np.nan, np.float32)
+        cg.transfer_stats.update(h2d=0, d2h=0)
         d_spmv(A.data, A.indptr, A.indices, xv, yv, A.shape[0])
         r0, r1 = mg.split_rows(A.indptr, world, rank)        # rows balanced by non-zeros
+        nnz_r = int(A.indptr[r1] - A.indptr[r0])             # data and indices in part, indptr and x whole
+        assert cg.transfer_stats["h2d"] == 8 * nnz_r + A.indptr.nbytes + xv.nbytes + 4 * (r1 - r0)
+        assert cg.transfer_stats["d2h"] == 4 * (r1 - r0)
         from oracle import numpy_oracle as O
         full = O.spmv(A.data, A.indptr, A.indices, xv)
         scale = O.spmv_abs(A.data, A.indptr, A.indices, xv)
