@@ -103,6 +103,7 @@ struct Kernel {
   cudaLibrary_t lib = nullptr;
   cudaKernel_t kern = nullptr;
   std::string name;
+  std::atomic<size_t> dyn_smem_allowed{48 * 1024};   // raised on demand, once per size
 };
 std::unordered_map<std::string, Kernel*> g_kernels;  // key: hash + name
 
@@ -580,9 +581,11 @@ int appy_launch(void* handle, unsigned grid, unsigned block, size_t dyn_smem, vo
   if (!handle) return fail(APPY_ERR_ARG, "NULL kernel handle");
   if (grid == 0) return APPY_OK;
   Kernel* k = static_cast<Kernel*>(handle);
-  if (dyn_smem > 48 * 1024)
+  if (dyn_smem > k->dyn_smem_allowed.load(std::memory_order_relaxed)) {
     CK(cudaFuncSetAttribute((const void*)k->kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                             (int)dyn_smem));
+    k->dyn_smem_allowed.store(dyn_smem, std::memory_order_relaxed);
+  }
   CK(cudaLaunchKernel((const void*)k->kern, dim3(grid), dim3(block), args, dyn_smem,
                       static_cast<cudaStream_t>(stream)));
   g_launches.fetch_add(1, std::memory_order_relaxed);
