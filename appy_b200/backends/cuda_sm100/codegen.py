@@ -402,15 +402,20 @@ class CompiledLoop:
                 while seg < 64 and n_iter * seg < 8 * self.sm_count and trip // (seg * 4) >= 2048:
                     seg *= 4
                 ov["P_SEG"] = seg
-            if plan.kind == "rowdot" and plan.vec > 1 and trip >= 1024 * plan.vec:
-                # Long dense rows: one CTA per pair of rows, eight 16-byte chunks per lane and row in
-                # flight.  Few, deep streams (two resident CTAs per SM) read long contiguous bursts of
-                # each row, which keeps DRAM pages open; thousands of concurrent warp-per-row streams
-                # were measured 20 % slower on a 16384 x 16384 matrix.
+            if plan.kind == "rowdot" and plan.vec > 1 and trip >= 256 * plan.vec:
+                # Long dense rows: few, deep, contiguous streams keep DRAM pages open (thousands of
+                # concurrent warp-per-row streams of two chunks each were measured 20 % slower on
+                # 16384 x 16384 and 262144 x 1024 matrices).  Eight 16-byte chunks per lane and row in
+                # flight, two rows at once when the body streams at most two arrays, register budget
+                # open.  Rows of at least 256 x 8 chunks get a 256-thread CTA per row pair (two CTAs per
+                # SM); shorter ones a warp per row pair, so that the unrolled loop still runs.
                 light = plan.info.get("streams", 9) <= 2
-                pair = light and n_iter >= 4 * self.sm_count        # with few rows every row gets its own CTA
-                ov.update({"P_G": 0, "P_BLOCK": 256, "P_U": 8 if light else 4, "P_R": 2 if pair else 1,
-                           "P_MINB": 2})
+                u = 8 if light else 4
+                if trip >= 256 * u * plan.vec:
+                    pair = light and n_iter >= 4 * self.sm_count        # with few rows every row gets its own CTA
+                    ov.update({"P_G": 0, "P_BLOCK": 256, "P_U": u, "P_R": 2 if pair else 1, "P_MINB": 2})
+                else:
+                    ov.update({"P_G": 32, "P_BLOCK": 128, "P_U": u, "P_R": 2 if light else 1, "P_MINB": 1})
             return ("rows", bucket, max(trip, 1).bit_length()), ov
         if plan.kind == "csr" and plan.info.get("indptr"):
             row_class, ov = self._csr_profile(variant, arrays, stream)

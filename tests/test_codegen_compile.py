@@ -160,6 +160,8 @@ def test_row_loop_tunables_follow_the_inner_trip_count_of_each_call():
     assert long_["P_G"] == 0 and long_["P_R"] == 2 and long_["P_MINB"] == 2     # CTA per pair of long rows
     few = entry._shape_class(variant, dict(scope, N=16384), [], 64, 0)[1]
     assert few["P_G"] == 0 and few["P_R"] == 1                                   # few rows: a CTA each
+    mid = entry._shape_class(variant, dict(scope, N=2048), [], 100000, 0)[1]
+    assert (mid["P_G"], mid["P_BLOCK"], mid["P_U"], mid["P_R"], mid["P_MINB"]) == (32, 128, 8, 2, 1)   # warp per row pair
     # the generic group lowering also sizes its groups from the inner trip
     src2 = "#pragma parallel for\nfor i in range(M):\n    #pragma simd\n    for j in range(N):\n        c[i, j] = A[i, j] + 1.0"
     scope2 = dict(A=A, c=A.copy(), M=64, N=64)
