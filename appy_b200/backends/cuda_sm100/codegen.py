@@ -388,12 +388,22 @@ class CompiledLoop:
             if trip is None:
                 return ("rows", bucket, None), {}
             ov = {}
-            per = 4 * max(1, plan.vec)
-            g = 1
-            while g < 32 and g * per < trip:
-                g *= 2
-            if plan.kind == "group" and trip >= 2048:
-                g = 0                                   # a CTA per outer iteration
+            if plan.kind == "group":
+                # a lane takes about four packs (or four elements) of the row; at least two lanes, so
+                # that neighbouring rows still coalesce; from 2048 iterations on, a CTA per row
+                # (512 threads once a thread would otherwise walk more than 16 packs)
+                per = 4 * max(1, plan.info.get("inner_vec", 1))
+                g = 2
+                while g < 32 and g * per < trip:
+                    g *= 2
+                if trip >= 2048:
+                    g = 0
+                    ov["P_BLOCK"] = 512 if trip >= 16384 else 256
+            else:
+                per = 4 * max(1, plan.vec)
+                g = 1
+                while g < 32 and g * per < trip:
+                    g *= 2
             ov["P_G"] = g
             if g == 0 and plan.info.get("splittable") and n_iter < 4 * self.sm_count:
                 # few long rows of a perfect nest: cut every row into segments until about eight CTAs

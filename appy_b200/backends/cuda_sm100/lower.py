@@ -670,7 +670,8 @@ class Lowering:
         src += self._kernel_wrapper(params, struct, call, "__shared__ double __smem[33];", self._reduction_init())
         src.insert(1, "#ifndef P_SEG\n#define P_SEG 1\n#endif")
         tun = {"P_G": [8, 1, 2, 4, 16, 32, 0], "P_BLOCK": [256, 128, 512]}
-        info = {"template": "generic group lowering", "splittable": ge.split}
+        info = {"template": "generic group lowering", "splittable": ge.split,
+                "inner_vec": getattr(ge, "widest_pack", 1)}
         if ge.split:
             tun["P_SEG"] = [1, 4, 16, 64]
         if self.reductions:
@@ -1117,6 +1118,7 @@ class GroupEmitter(Emitter):
             lo, hi = "__slo", "__shi"
         vec = self._vector_plan(st, v)
         if vec is not None:
+            self.widest_pack = max(getattr(self, "widest_pack", 1), vec[0])
             out += self._vector_loop(st, v, lo, hi, *vec)
         else:
             # iterations of a simd loop are independent: unrolled, a lane has several of them in flight

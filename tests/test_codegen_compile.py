@@ -170,7 +170,8 @@ def test_row_loop_tunables_follow_the_inner_trip_count_of_each_call():
     e2.source_for(*[v for v in vm2.values() if not isinstance(v, types.ModuleType)])
     v2 = list(e2.variants.values())[0]
     assert v2.plan.kind == "group"
-    assert e2._shape_class(v2, dict(scope2, N=16), [], 64, 0)[1]["P_G"] == 4
+    assert e2._shape_class(v2, dict(scope2, N=16), [], 64, 0)[1]["P_G"] == 2      # four packs: two lanes
+    assert e2._shape_class(v2, dict(scope2, N=256), [], 64, 0)[1]["P_G"] == 16
     assert e2._shape_class(v2, dict(scope2, N=100000), [], 64, 0)[1]["P_G"] == 0
     # a few very long rows of a perfect nest are cut into column segments; many rows are not
     e2.sm_count = 148
@@ -212,4 +213,4 @@ def test_triangular_inner_ranges_are_sized_by_their_mean_length():
     v = list(e.variants.values())[0]
     assert e._inner_trip(v.plan, dict(n=8192), 0, 8192) == 4097          # taken at the middle row
     assert e._shape_class(v, dict(n=8192), [], 8192, 0)[1]["P_G"] == 0   # long rows on average: a CTA each
-    assert e._shape_class(v, dict(n=40), [], 40, 0)[1]["P_G"] in (4, 8)
+    assert e._shape_class(v, dict(n=40), [], 40, 0)[1]["P_G"] in (2, 4)
