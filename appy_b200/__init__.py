@@ -108,7 +108,8 @@ def _to_gpu(a):
     import numpy as np
     import torch
     if isinstance(a, np.ndarray):
-        return torch.from_numpy(a).to("cuda")
+        from .backends.cuda_sm100.codegen import to_device
+        return to_device(a)
     if isinstance(a, torch.Tensor):
         return a.to("cuda")
     if isinstance(a, list):

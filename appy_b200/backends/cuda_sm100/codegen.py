@@ -240,26 +240,8 @@ class CompiledLoop:
             a.dptr, _created = rt.mirror(a.hptr, a.nbytes)
             b0, b1 = slices.get(a.name, (0, a.nbytes)) if slices else (0, a.nbytes)
             transfer_stats["h2d"] += max(0, b1 - b0)
-            pinned = a.hptr in _finalizers
-            if a.nbytes >= _PIN_MIN_BYTES and a.tmp is None and a.pinnable and self.options.get("pin_host", True) \
-                    and not pinned:
-                if len(_seen_host) > 4096:
-                    _seen_host.clear()
-                seen = _seen_host.get(a.hptr, 0) + 1
-                _seen_host[a.hptr] = seen
-                if seen == 2:      # a buffer that comes back is worth pinning in place
-                    try:
-                        rt.check(rt.lib().appy_register_host(C.c_void_p(a.hptr), a.nbytes))
-                        _register_finalizer(a.obj, a.hptr)
-                        pinned = a.hptr in _finalizers
-                    except rt.AppyRuntimeError:
-                        pass
-            if b1 <= b0:
-                continue
-            if pinned or a.nbytes < _PIN_MIN_BYTES:
-                rt.h2d(a.dptr + b0, a.hptr + b0, b1 - b0, stream)          # true DMA, or too small to matter
-            else:
-                rt.h2d_staged(a.dptr + b0, a.hptr + b0, b1 - b0, stream)   # pageable: pinned staging buffers
+            _upload(a.dptr + b0, a.hptr + b0, b1 - b0, a.hptr, a.nbytes, a.obj,
+                    a.tmp is None and a.pinnable and self.options.get("pin_host", True), stream)
 
     def _spec_key(self, arrays):
         key = []
@@ -825,6 +807,49 @@ class CompiledLoop:
     def source_for(self, *args) -> str:
         arrays = self._resolve_arrays(args)    # host arrays: dptr 0, mirrors are always aligned
         return self._variant(arrays, self._spec_key(arrays)).plan.source
+
+
+def _upload(dst: int, src: int, nbytes: int, base: int, base_bytes: int, owner, may_pin: bool, stream: int) -> None:
+    """Host-to-device copy of [src, src + nbytes), a part of the host buffer [base, base + base_bytes)
+    owned by `owner`.  A buffer of at least 1 MiB that comes back a second time is pinned in place, after
+    which its copies are true DMA; until then large pageable buffers go through the pinned staging
+    buffers of the runtime."""
+    if nbytes <= 0:
+        return
+    pinned = base in _finalizers
+    if base_bytes >= _PIN_MIN_BYTES and may_pin and not pinned:
+        if len(_seen_host) > 4096:
+            _seen_host.clear()
+        seen = _seen_host.get(base, 0) + 1
+        _seen_host[base] = seen
+        if seen == 2:      # a buffer that comes back is worth pinning in place
+            try:
+                rt.check(rt.lib().appy_register_host(C.c_void_p(base), base_bytes))
+                _register_finalizer(owner, base)
+                pinned = base in _finalizers
+            except rt.AppyRuntimeError:
+                pass
+    if pinned or base_bytes < _PIN_MIN_BYTES:
+        rt.h2d(dst, src, nbytes, stream)          # true DMA, or too small to matter
+    else:
+        rt.h2d_staged(dst, src, nbytes, stream)   # pageable: pinned staging buffers
+
+
+def to_device(array):
+    """A NumPy array as a new torch CUDA tensor, uploaded with the copy path of the loops (pinned in
+    place from the second time on).  Returns after the copy has completed, so the host array may be
+    modified at once.  This is what `appy.to_gpu` uses for NumPy arguments."""
+    import torch
+    h = np.ascontiguousarray(array)
+    t = torch.empty(h.shape, dtype=torch.from_numpy(h[:0] if h.ndim else h.reshape(1)[:0]).dtype, device="cuda")
+    if h.nbytes:
+        dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
+        rt.init(dev)
+        stream = _torch_stream(torch, dev)
+        _upload(t.data_ptr(), h.ctypes.data, h.nbytes, h.ctypes.data, h.nbytes, h, h is array, stream)
+        transfer_stats["h2d"] += h.nbytes
+        rt.sync(stream)
+    return t
 
 
 _finalizers: dict = {}

@@ -859,3 +859,24 @@ def test_inner_simd_loops_with_packs_and_ragged_ends(dtype, shape, lo, hi):
     da, db, dc = (torch.from_numpy(v).cuda() for v in (a, b, c))
     rows_window_update(da, db, dc, lo, hi)
     assert np.array_equal(dc.cpu().numpy(), ref)
+
+
+def test_to_gpu_uploads_numpy_arrays_with_the_runtime_copy_path():
+    """appy.to_gpu (appy/__init__.py: to_gpu) returns torch CUDA tensors; NumPy inputs go through the
+    runtime's pinned path and the host array may be changed right after the call returns."""
+    import torch
+    rng = np.random.default_rng(9)
+    for trial in range(3):                            # the third upload of the same buffer is pinned DMA
+        a = rng.standard_normal(1 << 19).astype(np.float32) if trial == 0 else a
+        expect = a.copy()
+        d = appy.to_gpu(a)
+        a += 1.0                                      # the copy has completed
+        assert d.is_cuda and d.dtype == torch.float32 and np.array_equal(d.cpu().numpy(), expect)
+    m = rng.random((7, 5)) < 0.5
+    strided = rng.standard_normal((64, 10))[:, ::2]
+    dm, ds, k = appy.to_gpu(m, strided, 3)
+    assert dm.dtype == torch.bool and np.array_equal(dm.cpu().numpy(), m)
+    assert np.array_equal(ds.cpu().numpy(), strided) and k == 3
+    assert appy.to_gpu(np.zeros((0, 4), np.float64)).shape == (0, 4)
+    back = appy.to_cpu(ds)
+    assert isinstance(back, np.ndarray) and np.array_equal(back, strided)
