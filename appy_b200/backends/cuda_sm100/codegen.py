@@ -42,10 +42,6 @@ _seen_host: dict = {}          # host ptr -> times seen (for the pin-on-second-u
 _tune_cache: dict | None = None
 
 
-def _is_numpy(v) -> bool:
-    return isinstance(v, np.ndarray)
-
-
 def _is_torch(v) -> bool:
     t = sys.modules.get("torch")
     return t is not None and isinstance(v, t.Tensor)

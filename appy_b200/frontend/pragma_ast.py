@@ -48,10 +48,6 @@ def pragma_text(node) -> str | None:
     return None
 
 
-def make_pragma_stmt(text: str) -> ast.Expr:
-    return ast.Expr(value=ast.Constant(value=text))
-
-
 def unparse(tree) -> str:
     """``ast.unparse`` with pragma markers written back as comment lines."""
     out = []
