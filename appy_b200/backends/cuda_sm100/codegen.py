@@ -51,15 +51,25 @@ _SIMPLE_KINDS = {bool: ("S", "bool"), int: ("S", "pyint"), float: ("S", "pyfloat
                  _types.ModuleType: ("M",)}
 
 
+_TORCH_TENSOR = None      # torch.Tensor once torch has been imported
+
+
 def _kind_of(v) -> tuple:
     """Signature entry of one argument: decides which kernel source is generated.
     Arrays: ("A", where, dtype object, rank); scalars: ("S", kind); modules: ("M",)."""
+    global _TORCH_TENSOR
     t = type(v)
     k = _SIMPLE_KINDS.get(t)
     if k is not None:
         return k
+    if t is _TORCH_TENSOR:
+        return ("A", v.device.type, v.dtype, v.ndim)
     if t is np.ndarray:
         return ("A", "np", v.dtype, v.ndim)
+    if _TORCH_TENSOR is None and "torch" in sys.modules:
+        _TORCH_TENSOR = sys.modules["torch"].Tensor
+        if t is _TORCH_TENSOR:
+            return ("A", v.device.type, v.dtype, v.ndim)
     if _is_torch(v):
         return ("A", v.device.type, v.dtype, v.ndim)
     if isinstance(v, np.ndarray):
@@ -188,6 +198,15 @@ class CompiledLoop:
         self.last_source: str | None = None
         self.memo: dict = {}
         self.has_device_args = any(sg[0] == "A" and sg[1] == "cuda" for sg in self.arg_sigs)
+        # Scalars whose value only flows into the arithmetic (not into any range bound) do not shape the
+        # launch: records are shared across their values and the value is patched into the arguments.
+        in_ranges = set()
+        for n in ast.walk(self.ir.loop):
+            if isinstance(n, ast.For) and isinstance(n.iter, ast.Call):
+                for arg in n.iter.args:
+                    in_ranges |= {x.id for x in ast.walk(arg) if isinstance(x, ast.Name)}
+        self.data_scalars = frozenset(i for i, (nm, sg) in enumerate(zip(self.arg_names, self.arg_sigs))
+                                      if sg[0] == "S" and nm not in in_ranges)
         self.device = None
         self.sm_count = 148
 
@@ -636,24 +655,35 @@ class CompiledLoop:
         return cells
 
     def _memo_key(self, args):
-        """Key of the launch record.  Device tensors enter with their address and layout, host arrays
-        with their layout only (their device mirror is looked up on every call), scalars by value.
-        None: this call cannot use a record (a host array that is not C-contiguous)."""
+        """Key of the launch record, computed from the values alone.  Device tensors enter with their
+        address, layout and dtype, host arrays with their layout and dtype only (their device mirror is
+        looked up on every call), scalars with their type and value.  None: this call cannot use a
+        record (a host array that is not C-contiguous, or an argument of an unexpected kind)."""
         key = []
-        for sig, v in zip(self.arg_sigs, args):
-            if sig[0] == "A":
-                if sig[1] == "cuda":
-                    key.append((v.data_ptr(), v.shape, v.stride()))
-                elif sig[1] == "np":
-                    if not v.flags.c_contiguous:
-                        return None
-                    key.append(v.shape)
+        tt = _TORCH_TENSOR
+        data = self.data_scalars
+        for i, v in enumerate(args):
+            t = type(v)
+            if i in data:
+                if t in _SIMPLE_KINDS or isinstance(v, np.generic):
+                    key.append(t)             # value patched into the record's arguments at launch
+                    continue
+                return None
+            if t is tt or (tt is not None and isinstance(v, tt)):
+                if v.is_cuda:
+                    key.append((v.data_ptr(), v.shape, v.stride(), v.dtype))
+                elif v.is_contiguous():
+                    key.append((v.shape, v.dtype))
                 else:
-                    if not v.is_contiguous():
-                        return None
-                    key.append(tuple(v.shape))
+                    return None
+            elif t is np.ndarray or isinstance(v, np.ndarray):
+                if not v.flags.c_contiguous:
+                    return None
+                key.append((v.shape, v.dtype))
+            elif tt is None and _is_torch(v):
+                return None                       # first sight of a tensor: the slow path registers the class
             else:
-                key.append(v)
+                key.append((t, v))
         return tuple(key)
 
     def _host_args(self, args, slots):
@@ -672,6 +702,51 @@ class CompiledLoop:
         disjoint = all(spans[i][1] <= spans[i + 1][0] for i in range(len(spans) - 1))
         return arrays, disjoint
 
+    def fast_call(self, args) -> bool:
+        """Launch from a record if this exact call (addresses, layouts, dtypes, scalar values) was seen
+        before; False sends the caller down the full path."""
+        if self.device is None or len(args) != len(self.arg_names):
+            return False
+        try:
+            mkey = self._memo_key(args)
+            memo = self.memo.get(mkey) if mkey is not None else None
+        except TypeError:                 # an unhashable argument
+            return False
+        return memo is not None and self._replay(memo, args)
+
+    def _replay(self, memo, args) -> bool:
+        handle, grid, block, smem, pack, seq_slot, memo_stream, cells, host_slots, scalar_slots = memo
+        torch = sys.modules.get("torch")
+        if torch is not None and (self.has_device_args or not host_slots):
+            stream = _torch_stream(torch, self.device)      # orders with the producers of the device tensors
+        else:
+            stream = rt.stream(0)
+        harr, disjoint = self._host_args(args, host_slots) if host_slots else ((), True)
+        if not disjoint or not (memo_stream is None or memo_stream == stream):     # a workspace belongs to one stream
+            return False
+        if host_slots:        # mirrors of the host arrays: look up, upload, patch into the arguments
+            self._acquire_device(harr, stream)
+            for a, (_argi, _name, slot) in zip(harr, host_slots):
+                pack.values[slot].value = a.dptr
+        for argi, slot in scalar_slots:
+            v = args[argi]
+            pack.values[slot].value = v.item() if isinstance(v, np.generic) else v
+        if cells:
+            self._pre_combine(cells)
+        if grid:
+            if seq_slot is not None:
+                from . import multi_gpu
+                pack.values[seq_slot].value = multi_gpu.combiner().next_seq()
+            rt.launch(handle, grid, block, pack, smem, stream)
+        if cells:
+            self._post_combine(cells)
+        if host_slots:
+            for a in harr:
+                if a.name in self.stored and a.nbytes:
+                    rt.d2h(a.hptr, a.dptr, a.nbytes, stream)
+            rt.sync(stream)
+        return True
+
     def __call__(self, *args):
         if len(args) != len(self.arg_names):
             raise TypeError(f"{self.loop_name} expects {len(self.arg_names)} arguments, got {len(args)}")
@@ -684,35 +759,8 @@ class CompiledLoop:
             self.sm_count = rt.device_info(self.device)["sm_count"]
         mkey = self._memo_key(args)
         memo = self.memo.get(mkey) if mkey is not None else None
-        if memo is not None:
-            # this exact call was seen before: launch straight away
-            handle, grid, block, smem, pack, seq_slot, memo_stream, cells, host_slots = memo
-            torch = sys.modules.get("torch")
-            if torch is not None and (self.has_device_args or not host_slots):
-                stream = _torch_stream(torch, self.device)      # orders with the producers of the device tensors
-            else:
-                stream = rt.stream(0)
-            harr, disjoint = self._host_args(args, host_slots) if host_slots else ((), True)
-            if disjoint and (memo_stream is None or memo_stream == stream):     # a workspace belongs to one stream
-                if host_slots:        # mirrors of the host arrays: look up, upload, patch into the arguments
-                    self._acquire_device(harr, stream)
-                    for a, (_argi, _name, slot) in zip(harr, host_slots):
-                        pack.values[slot].value = a.dptr
-                if cells:
-                    self._pre_combine(cells)
-                if grid:
-                    if seq_slot is not None:
-                        from . import multi_gpu
-                        pack.values[seq_slot].value = multi_gpu.combiner().next_seq()
-                    rt.launch(handle, grid, block, pack, smem, stream)
-                if cells:
-                    self._post_combine(cells)
-                if host_slots:
-                    for a in harr:
-                        if a.name in self.stored and a.nbytes:
-                            rt.d2h(a.hptr, a.dptr, a.nbytes, stream)
-                    rt.sync(stream)
-                return
+        if memo is not None and self._replay(memo, args):
+            return
         arrays = self._resolve_arrays(args)
         any_host = any(a.host for a in arrays)
         torch = sys.modules.get("torch")
@@ -764,10 +812,14 @@ class CompiledLoop:
                     for argi, (name, sig) in enumerate(zip(self.arg_names, self.arg_sigs)):
                         if sig[0] == "A" and sig[1] != "cuda":
                             host_slots.append((argi, name, pnames.index(name)))
+                pslot = {p.name: k for k, p in enumerate(variant.plan.params) if p.kind == "scalar"}
+                scalar_slots = tuple((i, pslot[self.arg_names[i]]) for i in sorted(self.data_scalars)
+                                     if self.arg_names[i] in pslot)
                 self.memo[mkey] = (h, grid, block, smem, pack, seq_slot,
-                                   stream if (variant.plan.uses_ws or any_host) else None, cells, tuple(host_slots))
+                                   stream if (variant.plan.uses_ws or any_host) else None, cells, tuple(host_slots),
+                                   scalar_slots)
         elif not any_host and mkey is not None:
-            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells, ())
+            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells, (), ())
         if cells:
             self._post_combine(cells)
         if any_host:
@@ -880,12 +932,23 @@ _OPTION_KEYS = ("ordered_reduction", "combine", "distribute", "fp_contract", "au
                 "_stream_hint", "_hoist_safe", "_shape_spec", "_neighbours", "_bulk_rows", "_group_vectorize")
 
 
+_site_options: dict = {}       # site number -> option key; the loops of one rewritten function always pass the same options
+
+
 def codegen(loop_source: str, loop_name: str, val_map: dict, options: dict):
     """Backend plugin entry (see module docstring)."""
     names = tuple(val_map)
     signature = tuple([_kind_of(v) for v in val_map.values()])
-    opt_key = tuple([options.get(k) for k in _OPTION_KEYS])
-    cache_key = (loop_source, loop_name, names, signature, opt_key, options.get("_fn"))
+    fn = options.get("_fn")
+    site = options.get("_site")             # set by the decoration-time rewrite, one per rewritten function
+    opt_key = _site_options.get(site) if site is not None else None
+    if opt_key is None:
+        opt_key = tuple([options.get(k) for k in _OPTION_KEYS])
+        if site is not None:
+            if len(_site_options) > 4096:
+                _site_options.clear()
+            _site_options[site] = opt_key
+    cache_key = (loop_source, loop_name, names, signature, opt_key, fn)
     entry = code_cache.get(cache_key)
     fresh = entry is None
     if fresh:

@@ -251,7 +251,9 @@ class ArgPack:
 
 
 def launch(handle: int, grid: int, block: int, args: ArgPack, dyn_smem: int = 0, stream_: int = 0) -> None:
-    check(lib().appy_launch(C.c_void_p(handle), grid, block, dyn_smem, args.ptrs, C.c_void_p(stream_)))
+    # argtypes are declared, so plain ints convert without building ctypes objects first
+    if (_LIB or lib()).appy_launch(handle, grid, block, dyn_smem, args.ptrs, stream_ or None) != 0:
+        check(-1)
 
 
 def time_launches(handle: int, grid: int, block: int, args: ArgPack, dyn_smem: int = 0,

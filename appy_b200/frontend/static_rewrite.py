@@ -92,9 +92,15 @@ def _shared_names(pragma: str) -> list[str]:
     return names
 
 
+import itertools as _itertools
+
+_site_ids = _itertools.count(1)
+
+
 class _Rewriter:
     def __init__(self, options: dict, fn_name: str = ""):
         self.options = dict(options)
+        self.options["_site"] = next(_site_ids)  # one number per rewritten function: its loops' options never change
         if fn_name:
             self.options["_fn"] = fn_name      # names the CUDA kernel after the function (profilers)
         self.counter = 0

@@ -880,3 +880,49 @@ def test_to_gpu_uploads_numpy_arrays_with_the_runtime_copy_path():
     assert appy.to_gpu(np.zeros((0, 4), np.float64)).shape == (0, 4)
     back = appy.to_cpu(ds)
     assert isinstance(back, np.ndarray) and np.array_equal(back, strided)
+
+
+@appy.jit
+def relax_through(path, k):
+    #pragma parallel for
+    for i in range(path.shape[0]):
+        #pragma simd
+        for j in range(path.shape[1]):
+            path[i, j] = min(path[i, j], path[i, k] + path[k, j])
+
+
+@appy.jit
+def scale_prefix(x, alpha, m):
+    #pragma parallel for simd
+    for i in range(m):
+        x[i] = alpha * x[i]
+
+
+def test_scalars_that_only_feed_the_arithmetic_share_one_launch_record():
+    """`k` changes on every call of a Floyd-Warshall sweep and `alpha` on every scaling, but neither
+    shapes the launch: one record serves all values (the value is patched into the arguments); `m`
+    bounds the range, so every value of `m` has its own record."""
+    import torch
+    from appy_b200.backends.cuda_sm100 import codegen as cg
+    rng = np.random.default_rng(17)
+    n = 48
+    d = rng.uniform(1, 10, (n, n))
+    np.fill_diagonal(d, 0.0)
+    ref = d.copy()
+    for k in range(n):
+        ref = np.minimum(ref, ref[:, k:k + 1] + ref[k:k + 1, :])
+    dp = torch.from_numpy(d).cuda()
+    for k in range(n):
+        relax_through(dp, k)
+    assert np.allclose(dp.cpu().numpy(), ref, rtol=1e-12, atol=0)
+    entry = [e for e in cg.code_cache.values() if e.kernel_name.startswith("relax_through_")][0]
+    assert len(entry.memo) == 1
+
+    x = torch.ones(1000, dtype=torch.float64, device="cuda")
+    expect = np.ones(1000)
+    for alpha, m in ((2.0, 1000), (0.5, 1000), (3.0, 10), (1.5, 10), (-1.0, 1000)):
+        scale_prefix(x, alpha, m)
+        expect[:m] *= alpha
+    assert np.array_equal(x.cpu().numpy(), expect)
+    entry = [e for e in cg.code_cache.values() if e.kernel_name.startswith("scale_prefix_")][0]
+    assert len(entry.memo) == 2                      # m = 1000 and m = 10

@@ -55,7 +55,9 @@ def reference_view(monkeypatch):
         real_defaults(options)
         options["dry_run"] = True
 
+    from appy_b200 import dispatcher
     monkeypatch.setattr(cg, "codegen", codegen_and_compile)
+    monkeypatch.setattr(dispatcher, "_sm100_codegen", codegen_and_compile)     # the dispatcher keeps its own reference
     monkeypatch.setattr(appy_b200, "set_default_options", defaults_with_dry_run)
     monkeypatch.setitem(sys.modules, "appy", appy_b200)
     return compiled
