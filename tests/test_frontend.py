@@ -193,3 +193,49 @@ def test_offset_slice_update_is_refused():
     # docs/metal_simd_memory_hazards.md: `A[i, 1:] = A[i, :-1]` would need a temporary
     with pytest.raises(NotImplementedError):
         normalize("#pragma parallel for\nfor i in range(n):\n    A[i, 1:] = A[i, :-1] + 1", {"A": 2}.get)
+
+
+SLICE_CASES = {
+    "row_times_gathered_rows": (
+        "#pragma parallel for\nfor i in range(M):\n    start, end = P[i], P[i+1]\n    y[i, :] = 0\n"
+        "    for k in range(start, end):\n        y[i, :] += D[k] * B[J[k], :]", ["y"]),
+    "sums_dots_and_extrema": (
+        "#pragma parallel for\nfor i in range(M):\n    y1[i] = np.sum(alpha * A[i, :] * x[:])\n    y2[i] = A[i, :] @ x\n"
+        "    y3[i] = np.max(A[i, 1:N-1]) - np.min(A[i, :])", ["y1", "y2", "y3"]),
+    "triangular_rank_k_update": (
+        "#pragma parallel for\nfor i in range(M):\n    S[i, :i + 1] *= beta\n    for k in range(N):\n"
+        "        S[i, :i + 1] += alpha * A[i, k] * A[:i + 1, k]", ["S"]),
+    "windows_with_negative_bounds": (
+        "#pragma parallel for\nfor i in range(M):\n    W[i, 1:-1] = 2.0 * A[i, 1:-1] - A[i, 2:] + A[i, :-2]\n"
+        "    W[i, 0:1] = A[i, 0:1]", ["W"]),
+}
+
+
+@pytest.mark.parametrize("name", sorted(SLICE_CASES))
+def test_slice_lowering_preserves_numpy_semantics(name):
+    """P1/P2: the slice front end (the role of the absent astpass.vector_op_to_loop).  The loop with
+    its slice statements runs in NumPy as written; the normalised loop (explicit inner loops, hoisted
+    shapes) runs as plain Python; stored arrays must agree (sums to 1e-12: NumPy adds pairwise)."""
+    src, stored = SLICE_CASES[name]
+    rng = np.random.default_rng(5)
+    M, N = 7, 9
+
+    def fresh():
+        r = np.random.default_rng(6)
+        P = np.array([0, 2, 2, 5, 9, 9, 12, 14])
+        return dict(M=M, N=N, alpha=1.5, beta=0.25, np=np, P=P, D=r.standard_normal(14),
+                    J=r.integers(0, M, 14), B=r.standard_normal((M, N)), A=r.standard_normal((M, N)),
+                    x=r.standard_normal(N), y=np.ones((M, N)), y1=np.zeros(M), y2=np.zeros(M), y3=np.zeros(M),
+                    S=r.standard_normal((M, M)), W=np.ones((M, N)))
+
+    ndims = {k: v.ndim for k, v in fresh().items() if isinstance(v, np.ndarray)}
+    ir = normalize(src, ndims.get)
+    direct, lowered = fresh(), fresh()
+    exec(compile(src.split("\n", 1)[1], "<direct>", "exec"), direct)
+    for nm in ir.extra_names:
+        arr, _shape, dim = nm.rpartition("_shape_")
+        lowered[nm] = lowered[arr].shape[int(dim)]
+    exec(compile(ast.unparse(ir.loop), "<lowered>", "exec"), lowered)
+    for nm in stored:
+        assert np.allclose(lowered[nm], direct[nm], rtol=1e-12, atol=1e-13), nm
+        assert not np.array_equal(direct[nm], fresh()[nm]), "the case must change the array"
