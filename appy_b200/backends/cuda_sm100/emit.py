@@ -320,6 +320,15 @@ class Emitter:
         return None, None
 
     def e_Call(self, node):
+        code, ty = self._call(node)
+        _name, mod = self._fname(node.func)
+        if mod in ("np", "numpy") and ty.weak:
+            # NumPy functions return NumPy scalars: np.sqrt(3.25) is a float64, no longer a weak Python
+            # float, so `f32 * np.sqrt(3.25)` is computed in float64 (math.sqrt(3.25) stays weak)
+            ty = ty.strong()
+        return code, ty
+
+    def _call(self, node):
         name, mod = self._fname(node.func)
         if name is None or node.keywords:
             raise ValueError(f"Unknown function: {ast.unparse(node.func)}")
