@@ -1,6 +1,6 @@
 """Seeded random element-wise expressions: the generated kernel against NumPy, bit for bit.
 
-Every loop is ``out[i] = <expr>`` over arrays of mixed dtypes (float32, float64, int32, int64, bool)
+Every loop is ``[t = <expr>; [u = <expr>;]] out[i] = <expr>`` over arrays of mixed dtypes (float32, float64, int32, int64, bool)
 and Python scalars.  The expression text is evaluated twice: by NumPy on whole arrays (``a[i]``
 replaced by the array ``a``), which is the oracle, and by the CUDA kernel generated for the loop.
 Operators are those with one correctly rounded result per operation (+ - * / // % abs min max sqrt,
@@ -21,6 +21,9 @@ pytestmark = pytest.mark.gpu
 
 N = 2053
 ARRAYS = {"f": np.float32, "d": np.float64, "k": np.int32, "l": np.int64, "m": np.bool_}
+
+
+_LOCALS: list = []      # names of the loop-local scalars an expression may use (set by the test)
 
 
 def _rand_expr(rng, depth, want):
@@ -44,7 +47,7 @@ def _rand_expr(rng, depth, want):
             return repr(float(rng.choice([0.5, 2.0, 3.25, -1.75, 10.0])))
         if r == 5:
             return repr(int(rng.integers(-7, 8)))
-        return rng.choice(["alpha", "n2"])
+        return rng.choice(["alpha", "n2"] + list(_LOCALS))
     r = rng.integers(0, 12)
     a = _rand_expr(rng, depth - 1, "num")
     b = _rand_expr(rng, depth - 1, "num")
@@ -61,6 +64,10 @@ def _rand_expr(rng, depth, want):
     if r == 9:
         return f"np.sqrt(abs({a}))"
     if r == 10:
+        if "[i]" not in a and "[i]" not in b:
+            # two Python scalars: the scalar loop yields a weak Python value chosen per element, which
+            # whole-array NumPy cannot express; give one branch an array operand
+            b = f"({b} * d[i])"
         return f"({a} if {_rand_expr(rng, depth - 1, 'bool')} else {b})"
     return f"(-{a})"
 
@@ -138,11 +145,21 @@ def test_random_elementwise_expressions(seed):
         "m": rng.random(N) < 0.5,
     }
     alpha, n2 = 1.5, 3
-    exprs = [_rand_expr(rng, int(rng.integers(1, 4)), "num") for _ in range(10)]
+    # every loop: up to two loop-local scalars, each assigned once, then the stored expression
+    loops = []
+    for _ in range(10):
+        del _LOCALS[:]
+        pre = []
+        for name in ("t", "u")[:int(rng.integers(0, 3))]:
+            pre.append((name, _rand_expr(rng, int(rng.integers(0, 3)), "num")))
+            _LOCALS.append(name)
+        loops.append((pre, _rand_expr(rng, int(rng.integers(1, 4)), "num")))
+    del _LOCALS[:]
+    exprs = [e for _pre, e in loops]
     src = ["import math", "import numpy as np", "import appy_b200 as appy", ""]
-    for j, e in enumerate(exprs):
+    for j, (pre, e) in enumerate(loops):
         src += ["@appy.jit", f"def loop{j}(f, d, k, l, m, alpha, n2, out):", "    #pragma parallel for simd",
-                "    for i in range(out.shape[0]):", f"        out[i] = {e}", ""]
+                "    for i in range(out.shape[0]):"] + [f"        {nm} = {ex}" for nm, ex in pre] + [f"        out[i] = {e}", ""]
     path = os.path.join(tempfile.gettempdir(), f"appy_random_expr_{os.getpid()}_{seed}.py")
     with open(path, "w") as fh:
         fh.write("\n".join(src))
@@ -153,8 +170,11 @@ def test_random_elementwise_expressions(seed):
     env = dict(data, alpha=alpha, n2=n2, np=np, math=math, abs=_py_abs, _where=_promote_like_python,
                _and=np.logical_and, _or=np.logical_or, _not=np.logical_not,
                _min=_py_minmax("min"), _max=_py_minmax("max"))
-    for j, e in enumerate(exprs):
+    for j, (pre, e) in enumerate(loops):
+        env.pop("t", None), env.pop("u", None)
         with np.errstate(all="ignore"):
+            for nm, ex in pre:
+                env[nm] = eval(_vectorised(ex), env)
             ref = np.asarray(eval(_vectorised(e), env))
         ref = np.broadcast_to(ref, (N,)).copy()
         if ref.dtype == np.bool_:
@@ -163,4 +183,4 @@ def test_random_elementwise_expressions(seed):
         getattr(mod, f"loop{j}")(dev["f"], dev["d"], dev["k"], dev["l"], dev["m"], alpha, n2, out)
         got = out.cpu().numpy()
         same = (got == ref) | (np.isnan(got.astype(np.float64)) & np.isnan(ref.astype(np.float64)))
-        assert same.all(), (e, ref.dtype, got[~same][:4], ref[~same][:4])
+        assert same.all(), (pre, e, ref.dtype, got[~same][:4], ref[~same][:4])
