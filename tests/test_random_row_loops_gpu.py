@@ -128,3 +128,68 @@ def test_random_row_reductions(seed, shape, lo, hi):
             v2 = np.broadcast_to(eval(_vec(t2), env), (M, hi - lo))
             ref2, scale2 = v2.sum(1) * data["w"], np.abs(v2).sum(1) * np.abs(data["w"])
             assert np.all(np.abs(out2.cpu().numpy() - ref2) <= 2e-5 * scale2 + 1e-6), (t2,)
+
+
+FLAT_LEAVES = ["a[i]", "b[i]", "d[i]", "alpha", "2.0", "0.5", "-1.25"]
+
+
+def _flat_term(rng, depth):
+    if depth == 0:
+        return FLAT_LEAVES[int(rng.integers(0, len(FLAT_LEAVES)))]
+    r = int(rng.integers(0, 8))
+    a, b = _flat_term(rng, depth - 1), _flat_term(rng, depth - 1)
+    if r < 4:
+        return f"({a} {'+-**'[r]} {b})"
+    if r == 4:
+        return f"abs({a})"
+    if r == 5:
+        return f"{'min' if rng.integers(0, 2) else 'max'}({a}, {b})"
+    if r == 6:
+        return f"({a} if mask[i] else {b})"
+    return f"(-{a})"
+
+
+@pytest.mark.parametrize("seed", range(int(os.environ.get("APPY_RANDOM_ROW_SEEDS", "8"))))
+def test_random_shared_scalar_reductions(seed):
+    """One to three shared(...) scalars per loop (+, max, min), written the way the reference's examples
+    are (`s = 0.0 ... shared(s) ... return s`): rtol 1e-5 of sum|term| for sums (float64 accumulation of
+    float32 terms), exact up to term rounding for the extrema."""
+    rng = np.random.default_rng(900 + seed)
+    n = int(rng.choice([1, 31, 4099, 262147]))
+    data = {"a": rng.uniform(-1, 1, n).astype(np.float32), "b": rng.uniform(-1, 1, n).astype(np.float32),
+            "d": rng.uniform(-1, 1, n), "mask": rng.random(n) < 0.5}
+    alpha = 0.75
+    src = ["import numpy as np", "import appy_b200 as appy", ""]
+    cases = []
+    for c in range(5):
+        k = int(rng.integers(1, 4))
+        ops = [["+", "max", "min"][int(rng.integers(0, 3))] for _ in range(k)]
+        terms = [_flat_term(rng, int(rng.integers(1, 3))) for _ in range(k)]
+        terms = [t if "[i]" in t else f"({t} * a[i])" for t in terms]
+        names = ["r0", "r1", "r2"][:k]
+        init = {"+": "0.0", "max": "-1.0e30", "min": "1.0e30"}
+        body = ["@appy.jit", f"def red{c}(a, b, d, mask, alpha):"] + [f"    {nm} = {init[op]}" for nm, op in zip(names, ops)]
+        body += [f"    #pragma parallel for simd shared({', '.join(names)})", "    for i in range(a.shape[0]):"]
+        for nm, op, t in zip(names, ops, terms):
+            body.append(f"        {nm} = {nm} + {t}" if op == "+" else f"        {nm} = {op}({nm}, {t})")
+        body.append(f"    return {', '.join(names)}" + ("," if k == 1 else ""))
+        src += body + [""]
+        cases.append((ops, terms))
+    path = os.path.join(tempfile.gettempdir(), f"appy_random_red_{os.getpid()}_{seed}.py")
+    with open(path, "w") as fh:
+        fh.write("\n".join(src))
+    spec = importlib.util.spec_from_file_location(f"appy_random_red_{seed}", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    dev = {k: torch.from_numpy(v).cuda() for k, v in data.items()}
+    env = {"_a": data["a"].astype(np.float64), "_b": data["b"].astype(np.float64), "_d": data["d"], "_mask": data["mask"],
+           "alpha": alpha, "_where": _where, "_min": _pymin, "_max": _pymax, "_abs": np.abs}
+    for c, (ops, terms) in enumerate(cases):
+        got = getattr(mod, f"red{c}")(dev["a"], dev["b"], dev["d"], dev["mask"], alpha)
+        for op, t, g in zip(ops, terms, got):
+            v = np.broadcast_to(eval(_vec(t), env), (n,))
+            if op == "+":
+                assert abs(g - v.sum()) <= 1e-5 * np.abs(v).sum() + 1e-6, (op, t, g, v.sum())
+            else:
+                ref = v.max() if op == "max" else v.min()
+                assert abs(g - ref) <= 1e-5 * abs(ref) + 1e-6, (op, t, g, ref)
