@@ -314,7 +314,30 @@ class Lowering:
         return lines
 
     # ------------------------------------------------------------------ dispatch
+    def _check_carried_scalars(self) -> None:
+        """Iterations of the parallel loop and of every simd loop run concurrently.  A scalar that is
+        read before it is written in an iteration carries a value from another iteration; that is only
+        meaningful for the recognised reductions (+, *, max, min).  Anything else would silently give a
+        lane-dependent result, so it is refused."""
+        loops = [self.loop] + [n for n in ast.walk(self.loop) if isinstance(n, ast.For) and n is not self.loop and _is_simd(n)]
+        for lp in loops:
+            declared = set(reductions_of(lp))
+            written = set()
+            for st in lp.body:
+                if isinstance(st, ast.Assign) and isinstance(st.targets[0], ast.Name):
+                    name = st.targets[0].id
+                    if name in _names_in(st.value) and name not in written and name not in declared \
+                            and getattr(st, "reduce", None) is None and lp is not self.loop:
+                        raise NotImplementedError(
+                            f"`{ast.unparse(st)}`: `{name}` carries a value between iterations of a simd loop; "
+                            "only +, *, max and min reductions of the form `x = x op (...)` can do that")
+                    written.add(name)
+                elif isinstance(st, (ast.If, ast.For, ast.While)):
+                    written |= {n.targets[0].id for n in ast.walk(st)
+                                if isinstance(n, ast.Assign) and isinstance(n.targets[0], ast.Name)}
+
     def lower(self) -> KernelPlan:
+        self._check_carried_scalars()
         body = self.loop.body
         if not _has_inner_simd(body):
             return self.lower_flat()
@@ -748,6 +771,8 @@ class Lowering:
                 others = [p for p in prefix if p.targets[0].id not in (lo_n.id, hi_n.id, acc_name)]
                 if not others and not ({lo_n.id, hi_n.id} & _names_in(ast.Module(body=suffix, type_ignores=[]))):
                     csr_ptr = a.value.id
+        if self.var in _names_in(term):
+            csr_ptr = None       # the CSR template evaluates term(k) without the row; the row-dot template passes it
         term_c, term_t = em.expr(term)
         # finish(i, total): the suffix statements with acc bound to the total
         fin_em = Emitter(env)

@@ -384,6 +384,42 @@ def _reduction_op(node: ast.Assign):
     return None
 
 
+def _chain_reduction(node: ast.Assign):
+    """`t = t + a - b + c` or `t = t * a * b` written as one left-associated chain whose leftmost
+    operand is the target: returns (op, value in the canonical form `t op (rest)`), else None.
+    (`t -= e` arrives here as `t = t - e` and becomes `t = t + (-e)`.)  The rewrite re-associates, which
+    a reduction does anyway; it is applied only to statements that then qualify as reductions."""
+    target, value = node.targets[0], node.value
+    if not _is_name_or_const_index(target) or not isinstance(value, ast.BinOp):
+        return None
+    t = _s(target)
+    spine = []          # (operator, right operand) from the outermost to the innermost
+    cur = value
+    while isinstance(cur, ast.BinOp) and isinstance(cur.op, (ast.Add, ast.Sub, ast.Mult)):
+        spine.append((cur.op, cur.right))
+        cur = cur.left
+    if not (_is_name_or_const_index(cur) and _s(cur) == t) or not spine:
+        return None
+    spine.reverse()
+    if all(isinstance(op, ast.Mult) for op, _ in spine):
+        kind = "*"
+    elif all(isinstance(op, (ast.Add, ast.Sub)) for op, _ in spine):
+        kind = "+"
+    else:
+        return None
+    if len(spine) == 1 and not isinstance(spine[0][0], ast.Sub):
+        return None     # already canonical
+    if any(t in {_s(x) for x in ast.walk(operand) if _is_name_or_const_index(x)} for _, operand in spine):
+        return None     # the target also appears inside an operand
+    op0, rest = spine[0]
+    if isinstance(op0, ast.Sub):
+        rest = ast.UnaryOp(op=ast.USub(), operand=rest)
+    for op, operand in spine[1:]:
+        rest = ast.BinOp(left=rest, op=op, right=operand)
+    new_value = ast.BinOp(left=cur, op=ast.Mult() if kind == "*" else ast.Add(), right=rest)
+    return kind, ast.fix_missing_locations(ast.copy_location(new_value, value))
+
+
 def detect_reductions(loop: ast.For) -> None:
     """Innermost loops first; marks ``Assign.reduce`` and extends ``For.pragma['reduction']``."""
     for child in ast.walk(loop):
@@ -395,9 +431,20 @@ def detect_reductions(loop: ast.For) -> None:
         return
     ops: dict[str, set] = {}
     assigns = [n for n in ast.walk(loop) if isinstance(n, ast.Assign)]
+    chains = {}
     for a in assigns:
         if _is_name_or_const_index(a.targets[0]):
-            ops.setdefault(_s(a.targets[0]), set()).add(_reduction_op(a))
+            kind = _reduction_op(a)
+            if kind is None:
+                ch = _chain_reduction(a)
+                if ch is not None:
+                    kind, chains[id(a)] = ch[0], ch[1]
+            ops.setdefault(_s(a.targets[0]), set()).add(kind)
+    for a in assigns:       # chains become `t = t op (rest)` where that makes the variable a reduction
+        if id(a) in chains:
+            kinds = ops.get(_s(a.targets[0]), set())
+            if len(kinds) == 1 and None not in kinds:
+                a.value = chains[id(a)]
     found: dict[str, str] = {}
     for a in assigns:
         key = _s(a.targets[0])

@@ -214,3 +214,27 @@ def test_triangular_inner_ranges_are_sized_by_their_mean_length():
     assert e._inner_trip(v.plan, dict(n=8192), 0, 8192) == 4097          # taken at the middle row
     assert e._shape_class(v, dict(n=8192), [], 8192, 0)[1]["P_G"] == 0   # long rows on average: a CTA each
     assert e._shape_class(v, dict(n=40), [], 40, 0)[1]["P_G"] in (2, 4)
+
+
+def test_csr_row_loop_whose_term_uses_the_row_index():
+    """`s += D[j] * x[J[j]] * w[i]`: the CSR template has no row in term(k); the loop takes the row-dot
+    template with the row bounds read from indptr."""
+    src = ("#pragma parallel for\nfor i in range(M):\n    start, end = P[i], P[i+1]\n    s = 0.0\n    #pragma simd\n"
+           "    for j in range(start, end):\n        s = s + D[j] * x[J[j]] * w[i]\n    y[i] = s")
+    scope = dict(D=np.ones(9, f32), P=np.array([0, 2, 2, 5, 9], np.int32), J=np.zeros(9, np.int32), x=np.ones(4, f32),
+                 w=np.ones(4, f32), y=np.ones(4), M=4)
+    plan, code = build(src, scope)
+    assert plan.kind == "rowdot" and "w + (i)" in code
+
+
+def test_scalar_carried_through_a_simd_loop_without_a_reduction_is_refused():
+    A = np.ones((8, 8), f32)
+    src = ("#pragma parallel for\nfor i in range(M):\n    t = 1.0\n    #pragma simd\n    for j in range(N):\n"
+           "        t = t * 0.5 + A[i, j]\n    y[i] = t")          # a recurrence, not a reduction
+    with pytest.raises(NotImplementedError) as e:
+        build(src, dict(A=A, y=np.ones(8, f32), M=8, N=8))
+    assert "carries a value between iterations" in str(e.value)
+    ok = ("#pragma parallel for\nfor i in range(M):\n    #pragma simd\n    for j in range(N):\n"
+          "        t = A[i, j]\n        t = t * 2.0\n        B[i, j] = t")     # written first in every iteration
+    plan, _code = build(ok, dict(A=A, B=A.copy(), M=8, N=8))
+    assert plan.kind == "group"

@@ -239,3 +239,20 @@ def test_slice_lowering_preserves_numpy_semantics(name):
     for nm in stored:
         assert np.allclose(lowered[nm], direct[nm], rtol=1e-12, atol=1e-13), nm
         assert not np.array_equal(direct[nm], fresh()[nm]), "the case must change the array"
+
+
+def test_chained_and_subtractive_updates_are_reductions():
+    """`s = s + a - b + c`, `s -= a` and `p = p * a * b` are sums / products of a re-associated rest; an
+    element update `c[i] = c[i] + a[i] + b[i]` is left exactly as written."""
+    ir = normalize("#pragma parallel for simd shared(s)\nfor i in range(n):\n    s[0] = s[0] + a[i] - b[i] + 2.0")
+    assert reductions_of(ir.loop) == {"s[0]": "+"} and "s[0] = s[0] + (a[i] - b[i] + 2.0)" in ast.unparse(ir.loop)
+    ir = normalize("#pragma parallel for simd shared(s)\nfor i in range(n):\n    s[0] -= a[i]")
+    assert reductions_of(ir.loop) == {"s[0]": "+"} and "s[0] = s[0] + -a[i]" in ast.unparse(ir.loop)
+    ir = normalize("#pragma parallel for simd shared(p)\nfor i in range(n):\n    p[0] = p[0] * a[i] * b[i]")
+    assert reductions_of(ir.loop) == {"p[0]": "*"}
+    ir = normalize("#pragma parallel for simd\nfor i in range(n):\n    c[i] = c[i] + a[i] + b[i]")
+    assert reductions_of(ir.loop) == {} and "c[i] = c[i] + a[i] + b[i]" in ast.unparse(ir.loop)
+    ir = normalize("#pragma parallel for\nfor i in range(n):\n    t = 0.0\n    #pragma simd\n    for j in range(m):\n"
+                   "        t = t + abs(A[i, j]) + x[j]\n    y[i] = t", {"A": 2}.get)
+    inner = [n for n in ast.walk(ir.loop) if isinstance(n, ast.For) and n is not ir.loop][0]
+    assert reductions_of(inner) == {"t": "+"}

@@ -6,6 +6,7 @@ indexed by the row, Python scalars, ternaries and abs/min/max.  The oracle is th
 NumPy on whole arrays and reduced along the row in float64; sums within 1e-5 of sum|term| per row
 (float32 accumulation in a different order), maxima and minima exactly.
 """
+import ast as ast_mod
 import importlib.util
 import os
 import tempfile
@@ -193,3 +194,73 @@ def test_random_shared_scalar_reductions(seed):
             else:
                 ref = v.max() if op == "max" else v.min()
                 assert abs(g - ref) <= 1e-5 * abs(ref) + 1e-6, (op, t, g, ref)
+
+
+CSR_TERMS = ["D[j] * x[J[j]]", "D[j] * x[J[j]] * w[i]", "abs(D[j]) + x[J[j]]", "D[j] * (x[J[j]] - z[J[j]])",
+             "(D[j] if x[J[j]] > 0.0 else -D[j])", "D[j] * D[j]", "x[J[j]] * z[J[j]] + alpha",
+             "min(D[j], x[J[j]]) * 2.0"]
+
+
+@pytest.mark.parametrize("idx_dtype", [np.int32, np.int64])
+@pytest.mark.parametrize("val_dtype", [np.float32, np.float64])
+def test_csr_row_loops_with_varied_terms(idx_dtype, val_dtype):
+    """CSR row loops whose inner term is not the plain SpMV product: per-row factors, two gathered
+    vectors, ternaries, max/min reductions; int32 and int64 index arrays, float32 and float64 values."""
+    from appy_b200 import workloads as W
+    A, x = W.spmv(2500, 12, kind="zipf", cap=700, seed=31)
+    rng = np.random.default_rng(32)
+    D = A.data.astype(val_dtype)
+    P, J = A.indptr.astype(idx_dtype), A.indices.astype(idx_dtype)
+    xv = x.astype(val_dtype)
+    zv = rng.uniform(-1, 1, x.size).astype(val_dtype)
+    wv = rng.uniform(-1, 1, A.shape[0]).astype(val_dtype)
+    alpha = 0.25
+    src = ["import numpy as np", "import appy_b200 as appy", ""]
+    cases = [(t, op) for t in CSR_TERMS for op in ("+",)] + [(CSR_TERMS[0], "max"), (CSR_TERMS[3], "min")]
+    for c, (t, op) in enumerate(cases):
+        init = {"+": "0.0", "max": "-1.0e30", "min": "1.0e30"}[op]
+        upd = f"s = s + {t}" if op == "+" else f"s = {op}(s, {t})"
+        src += ["@appy.jit", f"def csr{c}(D, P, J, x, z, w, alpha, y, M):", "    #pragma parallel for",
+                "    for i in range(M):", "        start, end = P[i], P[i+1]", f"        s = {init}", "        #pragma simd",
+                "        for j in range(start, end):", f"            {upd}", "        y[i] = s", ""]
+    path = os.path.join(tempfile.gettempdir(), f"appy_random_csr_{os.getpid()}_{np.dtype(idx_dtype).name}_{np.dtype(val_dtype).name}.py")
+    with open(path, "w") as fh:
+        fh.write("\n".join(src))
+    spec = importlib.util.spec_from_file_location("appy_random_csr_" + np.dtype(idx_dtype).name + np.dtype(val_dtype).name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    dev = [torch.from_numpy(v).cuda() for v in (D, P, J, xv, zv, wv)]
+    M = A.shape[0]
+    rows = np.repeat(np.arange(M), np.diff(A.indptr))
+    env = {"_D": D.astype(np.float64), "_x": xv.astype(np.float64)[A.indices], "_z": zv.astype(np.float64)[A.indices],
+           "_w": wv.astype(np.float64)[rows], "_J": None, "alpha": alpha, "_where": _where, "_min": _pymin, "_max": _pymax,
+           "_abs": np.abs}
+
+    class GatherVec(ast_mod.NodeTransformer):
+        def visit_Subscript(self, node):      # x[J[j]] -> _x (already gathered), D[j] -> _D, w[i] -> _w
+            return ast_mod.Name(id="_" + node.value.id, ctx=ast_mod.Load())
+
+        def visit_IfExp(self, node):
+            self.generic_visit(node)
+            return ast_mod.Call(func=ast_mod.Name(id="_where", ctx=ast_mod.Load()), args=[node.test, node.body, node.orelse], keywords=[])
+
+        def visit_Call(self, node):
+            self.generic_visit(node)
+            if isinstance(node.func, ast_mod.Name) and node.func.id in ("min", "max", "abs"):
+                node.func = ast_mod.Name(id="_" + node.func.id, ctx=ast_mod.Load())
+            return node
+
+    for c, (t, op) in enumerate(cases):
+        tree = GatherVec().visit(ast_mod.parse(t, mode="eval"))
+        v = np.broadcast_to(eval(compile(ast_mod.fix_missing_locations(tree), "<csr>", "eval"), env), (A.nnz,))
+        y = torch.full((M,), 7.0, dtype=torch.float64, device="cuda")
+        getattr(mod, f"csr{c}")(*dev, alpha, y, M)
+        got = y.cpu().numpy()
+        if op == "+":
+            ref = np.zeros(M); np.add.at(ref, rows, v)
+            scale = np.zeros(M); np.add.at(scale, rows, np.abs(v))
+            assert np.all(np.abs(got - ref) <= 2e-5 * scale + 1e-6), (t, np.abs(got - ref).max())
+        else:
+            ref = np.full(M, -1.0e30 if op == "max" else 1.0e30)
+            (np.maximum if op == "max" else np.minimum).at(ref, rows, v)
+            assert np.all(np.abs(got - ref) <= 1e-5 * np.abs(ref) + 1e-6), (t, op)
