@@ -467,7 +467,10 @@ class CompiledLoop:
         tun = variant.choice.get(cls)
         if tun is None:
             tun = dict(variant.tun, **{k: v for k, v in ov.items() if k in variant.tun})
-            if self._want_autotune():
+            # A kernel that exchanges its totals with other ranks in its tail is not timed: every trial
+            # launch would need its own sequence number on every rank at once.  It keeps the defaults.
+            fused_exchange = any(p.kind == "seq" for p in variant.plan.params)
+            if self._want_autotune() and not fused_exchange and hi > lo:
                 tun = self._autotune(variant, args, arrays, lo, hi, stream, tun, cls)
             if len(variant.choice) > 64:
                 variant.choice.clear()
@@ -780,15 +783,25 @@ class CompiledLoop:
         hi = int(eval(variant.hi_code, {}, scope))
         cells = []
         slices = None
+        exchange_only = False
         if self.options.get("distribute"):
+            full_lo, full_hi = lo, hi
             lo, hi = self._rank_range(variant, arrays, lo, hi)
+            # A rank whose share of the range is empty still has to take part in an exchange fused into
+            # the kernel's tail: it launches one CTA on the empty range [hi, hi), whose accumulators are
+            # the identities, so that it posts its words, draws its sequence number and leaves with
+            # the world's totals like every other rank.
+            exchange_only = (hi <= lo and full_hi > full_lo and multi_gpu.world()[1] > 1
+                             and any(p.kind == "seq" for p in variant.plan.params))
+            if exchange_only:
+                lo = hi = max(lo, hi)
             if sharded:      # every rank uploads only the part of the row- and nnz-indexed arrays it works on
                 slices = self._rank_slices(variant, arrays, lo, hi)
                 self._acquire_device(arrays, stream, slices)
             if multi_gpu.world()[1] > 1 and self.options.get("combine") != "p2p":
                 cells = self._reduction_cells(args, arrays)
                 self._pre_combine(cells)
-        if hi > lo:
+        if hi > lo or exchange_only:
             tun = self._choose_tunables(variant, args, arrays, scope, lo, hi, stream)
             pack = self._pack(variant, args, arrays, lo, hi, stream)
             h = variant.handle(tun)

@@ -554,6 +554,30 @@ def test_c5_spmm(fn, nrows, ncols):
     assert np.all(np.abs(y - ref) <= 1e-5 * scale + 1e-30)
 
 
+@pytest.mark.parametrize("density", [0.0001, 0.001, 0.01, 0.1])
+def test_c5_spmm_as_the_reference_example_checks_it(density):
+    """The one check the reference holds for this loop (examples/06-spmm.py:30-48): float64
+    values, the parts of a torch CSR tensor as arguments (``values()``, ``crow_indices()``,
+    ``col_indices()``: int64 indices on the device), a dense operand with 200 columns,
+    densities 1e-4 .. 1e-1, ``assert_close(rtol=1e-6, atol=1e-6)`` against ``A @ B``.  The
+    matrix side is 2000 here instead of 10000 so that the four cases run in seconds."""
+    import torch
+    n = 2000
+    g = torch.Generator(device="cuda").manual_seed(int(density * 1e6))
+    A = torch.randn(n, n, device="cuda", dtype=torch.float64, generator=g)
+    mask = torch.rand(n, n, device="cuda", generator=g) < density
+    A = (A * mask).to_sparse_csr()
+    B = torch.randn(n, 200, device="cuda", dtype=torch.float64, generator=g)
+    y_ref = A @ B
+    y = torch.full((n, 200), float("nan"), device="cuda", dtype=torch.float64)
+    assert A.crow_indices().dtype == torch.int64 and A.col_indices().dtype == torch.int64
+    k_spmm(A.values(), A.crow_indices(), A.col_indices(), B, y, n)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(y, y_ref, rtol=1e-6, atol=1e-6)
+    # and against the dense product, so that the check does not rest on one library routine
+    torch.testing.assert_close(y, A.to_dense() @ B, rtol=1e-6, atol=1e-6)
+
+
 def test_small_loops_match_the_plain_python_loops():
     """The reference's CPU execution of the same functions (decorator removed)."""
     A, x = W.spmv(200, 8, seed=1)

@@ -54,6 +54,20 @@ def _worker(rank, world, port, out_dir):
         assert np.array_equal(y, c_loops.spmv(A.data, A.indptr, A.indices, x))
         nnz = [int(A.indptr[p[1]] - A.indptr[p[0]]) for p in pieces]
         assert max(nnz) - min(nnz) <= 2 * 1024
+        # --- CSR x dense: the same row split, the dense operand whole on every rank, each rank
+        # computes its rows of the result with the rebased row pointers of its shard
+        As, Bs = W.spmm(3000, 24, cap=1500, ncols_b=64, seed=7)
+        d_r, p_r, i_r, s0, s1 = mg.shard_csr(As.data, As.indptr, As.indices, world, rank)
+        C_r = c_loops.spmm(np.ascontiguousarray(d_r), np.ascontiguousarray(p_r), np.ascontiguousarray(i_r), Bs)
+        assert C_r.shape == (s1 - s0, 64)
+        parts = [None] * world
+        dist.all_gather_object(parts, (s0, s1, C_r))
+        parts.sort(key=lambda p: p[0])
+        assert parts[0][0] == 0 and parts[-1][1] == As.shape[0]
+        assert all(p[1] == q[0] for p, q in zip(parts, parts[1:]))
+        assert np.array_equal(np.concatenate([p[2] for p in parts]), c_loops.spmm(As.data, As.indptr, As.indices, Bs))
+        share = [int(As.indptr[p[1]] - As.indptr[p[0]]) for p in parts]
+        assert max(share) - min(share) <= 2 * 1500
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
@@ -111,3 +125,11 @@ def test_arrays_a_rank_touches_only_in_part():
                                y=np.ones(4, f32), M=4))
     assert e._shard_classes(v) == {"D": "nnz", "J": "nnz", "y": "rows"}
     assert e._rank_slices(v, arrs, 2, 4) == {"D": (8, 36), "J": (8, 36), "y": (8, 16)}
+
+    Bd = np.ones((4, 8), f32)
+    e, v, arrs = compiled("#pragma parallel for\nfor i in range(M):\n    start, end = P[i], P[i+1]\n    y2[i, :] = 0\n"
+                          "    for k in range(start, end):\n        y2[i, :] += D[k] * Bd[J[k], :]",
+                          dict(P=P, y2=np.ones((4, 8), f32), D=np.ones(9, f32), Bd=Bd, J=np.zeros(9, np.int32), M=4))
+    assert v.plan.kind == "csrdense"
+    assert e._shard_classes(v) == {"y2": "rows", "D": "nnz", "J": "nnz"}        # the dense operand travels whole
+    assert e._rank_slices(v, arrs, 2, 4) == {"y2": (64, 128), "D": (8, 36), "J": (8, 36)}

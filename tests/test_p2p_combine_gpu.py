@@ -125,6 +125,16 @@ def d_spmv(A_data, A_indptr, A_indices, x, y, M):
 
 
 @appy.jit(distribute=True)
+def d_spmm(A_data, A_indptr, A_indices, B, y, M):
+    #pragma parallel for
+    for i in range(M):
+        start, end = A_indptr[i], A_indptr[i+1]
+        y[i, :] = 0
+        for k in range(start, end):
+            y[i, :] += A_data[k] * B[A_indices[k], :]
+
+
+@appy.jit(distribute=True)
 def d_scatter(idx, out):
     #pragma parallel for simd
     for i in range(idx.shape[0]):
@@ -205,6 +215,36 @@ def _rank_main(rank, world, port, out_dir):
         pieces = [None] * world
         dist.all_gather_object(pieces, (r0, r1))
         assert sorted(pieces)[0][0] == 0 and sorted(pieces)[-1][1] == A.shape[0]
+        # ---- distributed SpMM: rows split by non-zeros, the dense operand whole on every rank,
+        # rows of the result outside this rank's range untouched
+        As, Bs = W.spmm(6000, 24, cap=3000, ncols_b=128, seed=9)
+        ys = np.full((As.shape[0], 128), np.nan, np.float32)
+        cg.transfer_stats.update(h2d=0, d2h=0)
+        d_spmm(As.data, As.indptr, As.indices, Bs, ys, As.shape[0])
+        r0, r1 = mg.split_rows(As.indptr, world, rank)
+        nnz_r = int(As.indptr[r1] - As.indptr[r0])
+        assert cg.transfer_stats["h2d"] == 8 * nnz_r + As.indptr.nbytes + Bs.nbytes + 4 * 128 * (r1 - r0)
+        assert cg.transfer_stats["d2h"] == 4 * 128 * (r1 - r0)
+        full, scale = O.spmm(As.data, As.indptr, As.indices, Bs), O.spmm_abs(As.data, As.indptr, As.indices, Bs)
+        assert np.all(np.abs(ys[r0:r1] - full[r0:r1]) <= 1e-5 * scale[r0:r1] + 1e-30)
+        assert np.all(np.isnan(ys[:r0])) and np.all(np.isnan(ys[r1:]))
+        # ... and on device tensors held in full by every rank
+        dev = [torch.from_numpy(v).cuda() for v in (As.data, As.indptr, As.indices, Bs)]
+        yd = torch.full((As.shape[0], 128), float("nan"), device="cuda")
+        d_spmm(dev[0], dev[1], dev[2], dev[3], yd, As.shape[0])
+        yh = yd.cpu().numpy()
+        assert np.all(np.abs(yh[r0:r1] - full[r0:r1]) <= 1e-5 * scale[r0:r1] + 1e-30)
+        assert np.all(np.isnan(yh[:r0])) and np.all(np.isnan(yh[r1:]))
+        # ---- ranks whose share of a short range is empty still take part in the fused exchange:
+        # 20 iterations cut at multiples of 32 leave one rank without work
+        tiny = W.vec_sum(20, seed=3)
+        dt = torch.from_numpy(tiny).cuda()
+        shares = [mg.split_range(0, 20, world, r) for r in range(world)]
+        assert any(hi_ <= lo_ for lo_, hi_ in shares)
+        for _ in range(3):
+            assert np.isclose(d_sum_p2p(dt), 1.5 + float(np.sum(tiny, dtype=np.float64)), rtol=1e-6)
+        assert np.isclose(d_sum_p2p(torch.from_numpy(x).cuda()), ref, rtol=1e-6)     # sequence numbers still agree
+        assert not comb.timed_out()
         try:
             d_scatter(np.arange(10, dtype=np.int64), np.zeros(10))
             raise AssertionError("a scattered store must not be distributable")
