@@ -52,16 +52,61 @@ def measured_peak():
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
+    """SM clock and throttle reasons of one GPU, read (never set) every few milliseconds by a thread of
+    this process through NVML while the benchmark runs; every sample carries its time, so the samples
+    that fall inside the timed region can be told from those of the per-kernel table.  Falls back to an
+    `nvidia-smi -lms 100` child process when the NVML binding is missing."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
 
     def __init__(self, index: int):
         self.index = index
         self.proc = None
         self.path = None
+        self.samples = []          # (time, sm MHz, reasons bit mask)
+        self.sm_max = None
+        self.thread = None
+        self.stop_flag = False
+        self.marks = {}
+
+    def mark(self, name: str):
+        self.marks[name] = time.perf_counter()
+
+    def _nvml_loop(self, nv, handle):
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)
+                try:
+                    bits = nv.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                except Exception:
+                    bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.samples.append((time.perf_counter(), float(mhz), int(bits)))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self):
+        try:
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            # NVML counts physical GPUs; honour CUDA_VISIBLE_DEVICES when it is a list of indices
+            phys = self.index
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if vis:
+                ids = [v.strip() for v in vis.split(",") if v.strip()]
+                if self.index < len(ids) and ids[self.index].isdigit():
+                    phys = int(ids[self.index])
+            handle = nv.nvmlDeviceGetHandleByIndex(phys)
+            self.sm_max = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -71,7 +116,28 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def _summary(self, rows):
+        out = {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": len(rows)}
+        if rows:
+            out["sm_mhz"] = statistics.median(r[1] for r in rows)
+            out["sm_mhz_min"] = min(r[1] for r in rows)
+            bits = 0
+            for r in rows:
+                bits |= r[2]
+            out["reasons"] = sorted(name for name, bit in self.REASONS if bits & bit)
+        return out
+
     def stop(self) -> dict:
+        if self.thread is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            out = self._summary(self.samples)
+            out["source"] = "NVML, one reading every ~2 ms"
+            t0, t1 = self.marks.get("timed_start"), self.marks.get("timed_end")
+            if t0 is not None and t1 is not None:
+                # the timed region is short: readings from 50 ms before it to its end count as "during"
+                out["timed_region"] = self._summary([r for r in self.samples if t0 - 0.05 <= r[0] <= t1])
+            return out
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if self.proc is None:
             return out
@@ -103,6 +169,7 @@ class ClockSampler:
             out["sm_max_mhz"] = max(mx)
             out["samples"] = len(sm)
         out["reasons"] = sorted(reasons)
+        out["source"] = "nvidia-smi -lms 100"
         return out
 
 
@@ -132,6 +199,54 @@ def masked_sum_into_p2p(a, mask, out):
     #pragma parallel for simd
     for i in range(a.shape[0]):
         out[0] += a[i] if mask[i] else 0.0
+
+@appy.jit(distribute=True)
+def d_vec_add(a, b, c):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        c[i] = a[i] + b[i]
+
+@appy.jit(distribute=True, combine="p2p")
+def d_sum_into_p2p(a, out):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        out[0] += a[i]
+
+@appy.jit(distribute=True)
+def d_sum_into(a, out):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        out[0] += a[i]
+
+@appy.jit(distribute=True)
+def d_spmv(A_data, A_indptr, A_indices, x, y, M):
+    #pragma parallel for
+    for i in range(M):
+        start, end = A_indptr[i], A_indptr[i+1]
+        s = 0.0
+        #pragma simd
+        for j in range(start, end):
+            s += A_data[j] * x[A_indices[j]]
+        y[i] = s
+
+@appy.jit(distribute=True)
+def d_gemv(alpha, A, x, y):
+    #pragma parallel for
+    for i in range(A.shape[0]):
+        yi = 0.0
+        #pragma simd
+        for j in range(A.shape[1]):
+            yi += alpha * A[i, j] * x[j]
+        y[i] = yi
+
+@appy.jit(distribute=True)
+def d_spmm(A_data, A_indptr, A_indices, B, y, M):
+    #pragma parallel for
+    for i in range(M):
+        start, end = A_indptr[i], A_indptr[i+1]
+        y[i, :] = 0
+        for k in range(start, end):
+            y[i, :] += A_data[k] * B[A_indices[k], :]
 
 @appy.jit
 def vec_sum(a):
@@ -331,12 +446,114 @@ def kernel_table(torch, L, peak, rank, quick=False, with_triton=True, world=1):
     return rows
 
 
+def strong_table(torch, L, peak, rank, world, quick=False, use_p2p=True):
+    """The configured problems split over the ranks (`@jit(distribute=True)`): contiguous ranges of the
+    outer index, balanced by non-zeros for the CSR loops; the gathered operands (x, B) whole on every
+    GPU; every rank writes its own slice of the result, which stays where it is.  Inputs are the same on
+    every rank and resident before the timed launches.  Per kernel: `us` = maximum over ranks of the
+    rank's own average launch time, `one_gpu_us` = the same loop on the whole problem on one GPU
+    (maximum over ranks, same run), `strong_speedup` = their ratio.  Each rank rotates over enough
+    copies of its inputs that consecutive launches find nothing of theirs in the 126 MB L2."""
+    import torch.distributed as dist
+    from appy_b200 import workloads as W
+    dev = "cuda"
+    rows = {}
+    L2 = 126e6
+
+    def copies(per_gpu_bytes):
+        return int(max(2, min(24, -(-2.2 * L2 // max(per_gpu_bytes, 1)))))
+
+    def both(name, byts, one_fn, dist_fn, rot, iters, note):
+        t1 = time_kernel(torch, one_fn, rot, max(4, iters // 2))
+        tn = time_kernel(torch, dist_fn, rot, iters)
+        t = torch.tensor([t1, tn], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t1, tn = float(t[0]), float(t[1])
+        rows[name] = {"us": round(tn, 2), "one_gpu_us": round(t1, 2), "strong_speedup": round(t1 / tn, 2),
+                      "gbs": round(byts / tn / 1e3, 1), "frac_per_gpu": round(byts / world / tn / 1e3 / peak, 4),
+                      "bytes": int(byts), "split": note, "copies_rotated": rot}
+
+    # C1
+    n = 1 << 24
+    a, b = W.vec_add(n, seed=0)
+    rot = copies(W.bytes_vec_add(n) / world)
+    sets = [(torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev), torch.empty(n, device=dev)) for _ in range(rot)]
+    both("C1 vec_add f32 n=2^24", W.bytes_vec_add(n), lambda i: L.vec_add(*sets[i]), lambda i: L.d_vec_add(*sets[i]),
+         rot, 8 * rot, "contiguous index ranges, cuts at multiples of 32")
+    from appy_b200.backends.cuda_sm100 import multi_gpu as mg
+    lo, hi = mg.split_range(0, n, world, rank)
+    assert np.array_equal(sets[0][2][lo:hi].cpu().numpy(), (a + b)[lo:hi])
+    del sets
+    # C2a with the combine inside the kernel's tail
+    n = N_HEADLINE
+    av = W.vec_sum(n, seed=0)
+    rot = copies(W.bytes_sum(n) / world)
+    das = [torch.from_numpy(av).to(dev) for _ in range(rot)]
+    cell = torch.zeros(1, dtype=torch.float64, device=dev)
+    d_sum = L.d_sum_into_p2p if use_p2p else L.d_sum_into
+    both("C2a sum f32 n=2^26", W.bytes_sum(n), lambda i: L.sum_into(das[i], cell), lambda i: d_sum(das[i], cell),
+         rot, 8 * rot, "contiguous index ranges; the scalar is combined " +
+         ("in the kernel's tail over peer mailboxes" if use_p2p else "by an NCCL all-reduce"))
+    cell.zero_()
+    d_sum(das[0], cell)
+    assert np.isclose(float(cell.item()), float(np.sum(av, dtype=np.float64)), rtol=1e-5)
+    del das
+    # C4
+    al, A, x = W.gemv(16384, seed=0)
+    rot = copies(W.bytes_gemv(16384, 16384) / world)
+    dAs = [torch.from_numpy(A).to(dev) for _ in range(rot)]
+    dx, dy = torch.from_numpy(x).to(dev), torch.empty(16384, device=dev)
+    both("C4 gemv f32 16384x16384", W.bytes_gemv(16384, 16384), lambda i: L.gemv(1.0, dAs[i], dx, dy),
+         lambda i: L.d_gemv(1.0, dAs[i], dx, dy), rot, 6 * rot, "row blocks; x on every GPU")
+    del dAs, A
+    if quick:
+        return rows
+    # C3
+    for kind in ("poisson", "zipf"):
+        Am, xv = W.spmv(kind=kind, seed=0)
+        byts = W.bytes_spmv(Am.shape[0], Am.shape[1], Am.nnz)
+        rot = copies(byts / world)
+        sets = []
+        for _ in range(rot):
+            sets.append([torch.from_numpy(v).to(dev) for v in (Am.data, Am.indptr, Am.indices, xv)] +
+                        [torch.empty(Am.shape[0], device=dev)])
+        M = Am.shape[0]
+        both(f"C3 spmv {kind} M=2^20 nnz={Am.nnz}", byts,
+             lambda i: L.spmv(sets[i][0], sets[i][1], sets[i][2], sets[i][3], sets[i][4], M),
+             lambda i: L.d_spmv(sets[i][0], sets[i][1], sets[i][2], sets[i][3], sets[i][4], M),
+             rot, 8 * rot, "row ranges balanced by non-zeros; x on every GPU")
+        del sets
+    # C5
+    Am, B = W.spmm(seed=0)
+    b1, b2 = W.bytes_spmm(Am.shape[0], B.shape[0], Am.nnz, B.shape[1])
+    rot = 2
+    sets = []
+    for _ in range(rot):
+        sets.append([torch.from_numpy(v).to(dev) for v in (Am.data, Am.indptr, Am.indices, B)] +
+                    [torch.empty((Am.shape[0], B.shape[1]), device=dev)])
+    M = Am.shape[0]
+    both(f"C5 spmm M=2^18 nnz={Am.nnz} B=2^18x128", b1,
+         lambda i: L.spmm(sets[i][0], sets[i][1], sets[i][2], sets[i][3], sets[i][4], M),
+         lambda i: L.d_spmm(sets[i][0], sets[i][1], sets[i][2], sets[i][3], sets[i][4], M),
+         rot, 6 * rot, "row ranges balanced by non-zeros; B (134 MB) on every GPU, never read from a peer")
+    return rows
+
+
 # --------------------------------------------------------------------------- CPU arms
+_cpu_inputs = {}
+
+
 def cpu_port_numbers(n_sample: int, reps: int):
-    """Oracle C port (OpenMP) of the two headline loops on a bounded sample."""
+    """Oracle C port (OpenMP) of the two headline loops on n_sample elements per loop, on every core
+    this process may use: the thread count is set explicitly, whatever OMP_NUM_THREADS the launcher
+    exported (torch.distributed.run sets it to 1)."""
     from appy_b200 import workloads as W
     from oracle import c_loops
-    a, m = W.masked_sum(n_sample, seed=0)
+    threads = c_loops.set_threads(c_loops.host_cores())
+    if n_sample not in _cpu_inputs:
+        _cpu_inputs.clear()
+        _cpu_inputs[n_sample] = W.masked_sum(n_sample, seed=0)
+    a, m = _cpu_inputs[n_sample]
     c_loops.vec_sum(a)
     t0 = time.perf_counter()
     for _ in range(reps):
@@ -344,7 +561,7 @@ def cpu_port_numbers(n_sample: int, reps: int):
         c_loops.masked_sum(a, m)
     dt = (time.perf_counter() - t0) / reps
     byts = 9 * n_sample
-    return byts / dt / 1e9, dt, c_loops.threads()
+    return byts / dt / 1e9, dt, threads
 
 
 def python_loop_number(n_sample: int):
@@ -360,13 +577,14 @@ def python_loop_number(n_sample: int):
 
 
 def run_reference(args, rank):
+    """The CPU arm: the same two loops on the same n = 2**26 elements per loop, every step one full pass
+    of both, on all the host cores this process may use.  Rank 0 only; other ranks leave at once."""
     if rank != 0:
         return
-    n_sample = 1 << 24
+    n = args.n
     for _ in range(max(args.warmup, 1)):
-        cpu_port_numbers(n_sample, 1)
-    t0 = time.perf_counter()
-    gbs, dt, threads = cpu_port_numbers(n_sample, args.steps)
+        cpu_port_numbers(n, 1)
+    gbs, dt, threads = cpu_port_numbers(n, args.steps)
     py_gbs, py_dt = python_loop_number(1 << 20)
     line = {
         "impl": "reference", "metric": "effective HBM GB/s of the generated-kernel path (shared-scalar reductions)",
@@ -374,11 +592,14 @@ def run_reference(args, rank):
         "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": "C2 shared-scalar reductions: (a) sum, (b) masked sum (Bernoulli 0.5 bool mask), "
-                               f"f32, n={N_HEADLINE} per GPU, host cores; each step a sample of n=2^24 per loop"},
+                               f"f32, n={n} per GPU, through @appy_b200.jit",
+                   "l2": "inputs larger than L2 (256 MiB + 64 MiB read per step)",
+                   "accumulate": "float64 (the shared scalar is a float64 cell, as in the reference)",
+                   "collective": "none"},
         "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
-                         "sample": f"oracle/loops.c with OpenMP on n=2^24 of 2^26 elements per loop, {args.steps} "
-                                   f"passes; the interpreted Python loops (the reference's own CPU execution) reach "
-                                   f"{py_gbs:.5f} GB/s on n=2^20 on 1 core"},
+                         "sample": f"oracle/loops.c with OpenMP on the full n={n} elements per loop, {args.steps} "
+                                   f"passes, {threads} threads set explicitly; the interpreted Python loops (the "
+                                   f"reference's own CPU execution) reach {py_gbs:.5f} GB/s on n=2^20 on 1 core"},
         "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -533,22 +754,24 @@ def main():
     ref = [float(np.sum(a_h, dtype=np.float64)), float(np.sum(a_h[m_h], dtype=np.float64))]
     assert np.allclose(got, ref, rtol=1e-5, atol=0), (got, ref)
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
+    sampler = ClockSampler(local_rank)          # every rank watches its own GPU
+    sampler.start()
+    for _ in range(20):                         # clocks under load before the region, as during it
+        step()
     out.zero_()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     launches0 = rt.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.mark("timed_start")
     e0.record()
     for _ in range(args.steps):
         step()
     drain()
     e1.record()
     torch.cuda.synchronize()
+    sampler.mark("timed_end")
     if world > 1:
         dist.barrier()
     ms = e0.elapsed_time(e1)
@@ -582,7 +805,6 @@ def main():
     dom_bytes, dom_us, dom_name = (W.bytes_masked_sum(n), us_msk, "masked sum (T2 reduction template)") \
         if us_msk >= us_sum else (W.bytes_sum(n), us_sum, "sum (T2 reduction template)")
     achieved = dom_bytes / dom_us / 1e3
-    clocks = sampler.stop() if rank == 0 else {}
 
     # ---- e2e: NumPy host buffers through the public API, copies inside the timed region.
     # (a) the step as a user of the reference's API writes it when two loops share an input: upload the
@@ -656,6 +878,24 @@ def main():
                 table[name].update({"numpy_ms": round(best * 1e3, 2), "numpy_threads": os.cpu_count(),
                                     "speedup_vs_numpy": round(best * 1e6 / us, 1)})
 
+    strong = None
+    if world > 1 and not args.no_table:
+        strong = strong_table(torch, L, peak, rank, world, quick=args.quick_table, use_p2p=use_p2p)
+
+    clocks = sampler.stop()                     # covers the timed region and the per-kernel tables
+    if world > 1:                               # one line per rank's GPU: median MHz, minimum MHz, readings
+        mine = torch.tensor([clocks.get("sm_mhz") or 0.0, clocks.get("sm_mhz_min") or 0.0,
+                             float(clocks.get("samples") or 0),
+                             float(sum(1 << i for i, (nm, _b) in enumerate(ClockSampler.REASONS)
+                                       if nm in clocks.get("reasons", [])))], dtype=torch.float64, device="cuda")
+        allc = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allc, mine)
+        clocks["per_rank"] = [{"sm_mhz": float(c[0]), "sm_mhz_min": float(c[1]), "samples": int(c[2]),
+                               "reasons": [nm for i, (nm, _b) in enumerate(ClockSampler.REASONS)
+                                           if int(c[3]) >> i & 1]} for c in allc]
+        for c in clocks["per_rank"]:            # a throttle seen on any rank's GPU counts for the run
+            clocks["reasons"] = sorted(set(clocks["reasons"]) | set(c["reasons"]))
+
     # host cost of one call through the whole @jit path (wall clock; the kernel on 4096 elements is
     # shorter than the call, so the loop is host-bound and wall time per call is the launch path)
     small, small_out = a[:4096], torch.zeros(1, dtype=torch.float64, device="cuda")
@@ -670,9 +910,12 @@ def main():
 
     cpu = None
     if rank == 0 and world == 1:
-        gbs, dt, threads = cpu_port_numbers(1 << 24, 20)
+        _cpu_inputs[n] = (a_h, m_h)
+        cpu_port_numbers(n, 1)
+        gbs, dt, threads = cpu_port_numbers(n, 10)
         cpu = {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
-               "sample": "oracle/loops.c (OpenMP) on n=2^24 of the 2^26 elements per loop, 20 passes"}
+               "sample": f"oracle/loops.c (OpenMP, {threads} threads set explicitly) on the full n={n} elements "
+                         "per loop, 10 passes"}
 
     if rank == 0:
         line = {
@@ -703,6 +946,9 @@ def main():
             "clocks": clocks,
             "kernels": table,
         }
+        if strong is not None:
+            line["strong"] = {"what": "the configured problems split over the GPUs with @jit(distribute=True); "
+                                      "time = maximum over ranks; strong_speedup = one_gpu_us / us", "kernels": strong}
         if n == N_HEADLINE:
             line["roofline"]["traffic"] = NCU_TRAFFIC.get(dom_name.split(" (")[0])
         print(json.dumps(line), flush=True)

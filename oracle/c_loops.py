@@ -41,6 +41,20 @@ def threads() -> int:
     return int(lib().oracle_threads())
 
 
+def set_threads(n: int) -> int:
+    """Use `n` OpenMP threads from now on (whatever OMP_NUM_THREADS says); returns the count in effect."""
+    lib().oracle_set_threads(C.c_int(int(n)))
+    return threads()
+
+
+def host_cores() -> int:
+    """Cores this process may run on (the affinity mask, not the machine's total)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def _p(a):
     return C.c_void_p(a.ctypes.data)
 

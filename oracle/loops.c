@@ -29,6 +29,16 @@ int oracle_threads(void) {
 #endif
 }
 
+/* Number of OpenMP threads for the loops below.  A launcher may have set OMP_NUM_THREADS=1 for
+ * every child process; the timed CPU baseline states its thread count instead of inheriting one. */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 void oracle_vec_add_f32(const float* a, const float* b, float* c, int64_t n) {
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; ++i) c[i] = a[i] + b[i];

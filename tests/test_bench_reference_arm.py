@@ -31,3 +31,11 @@ def test_reference_arm_prints_one_json_line():
 
 def test_reference_arm_is_silent_on_other_ranks():
     assert _run({"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1"}) == []
+
+
+def test_reference_arm_sets_its_thread_count_itself():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to every rank; the CPU arm must still use the
+    cores it is allowed to run on, and time the full n = 2**26 of the headline configuration."""
+    d = json.loads(_run({"OMP_NUM_THREADS": "1", "RANK": "0", "WORLD_SIZE": "2", "LOCAL_RANK": "0"})[0])
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+    assert "n=67108864" in d["config"]["workload"] and "full n=67108864" in d["cpu_baseline"]["sample"]
