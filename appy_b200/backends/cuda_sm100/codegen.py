@@ -178,6 +178,16 @@ class Variant:
             self.handles[key] = h
         return h
 
+    def post_handle(self, tun: dict) -> int:
+        """The plan's second kernel (same source, same options), launched after the main one."""
+        key = ("post",) + tuple(sorted(tun.items()))
+        h = self.handles.get(key)
+        if h is None:
+            opts = [f"-D{k}={v}" for k, v in tun.items()] + list(self.plan.info.get("nvrtc", []))
+            h = rt.compile_kernel(self.plan.source, self.plan.post, opts)
+            self.handles[key] = h
+        return h
+
 
 class CompiledLoop:
     def __init__(self, loop_source: str, loop_name: str, names: list, signature: tuple, options: dict):
@@ -296,7 +306,10 @@ class CompiledLoop:
             if sig[0] == "M":
                 infos.append(ArgInfo(name, "module"))
             elif sig[0] == "S":
-                infos.append(ArgInfo(name, "scalar", _scalar_type(sig[1])))
+                sty = _scalar_type(sig[1])
+                if sig[1] == "pyfloat" and self.options.get("fp_contract") == "triton":
+                    sty = T.F32          # a Python float reaches the reference's Triton kernel as fp32
+                infos.append(ArgInfo(name, "scalar", sty))
             else:
                 a = by_name[name]
                 aligned, unit_last, vec, small = flags[name]
@@ -311,7 +324,9 @@ class CompiledLoop:
         if self.options.get("fp_contract", "numpy") == "numpy":
             plan.info["nvrtc"] = ["--fmad=false", "--prec-div=true", "--prec-sqrt=true", "--ftz=false"]
         else:
-            plan.info["nvrtc"] = ["--fmad=true"]
+            # the reference backend's numerics: FMA contraction, float32 `/` as div.full.f32 (emitted
+            # explicitly), float literals float64, Python floats float32 (emit.py, Env.numerics)
+            plan.info["nvrtc"] = ["--fmad=true", "--prec-div=true", "--prec-sqrt=true", "--ftz=false"]
         v = Variant(plan)
         self.variants[key] = v
         self.last_source = plan.source
@@ -328,7 +343,7 @@ class CompiledLoop:
                 scope.setdefault(f"{a.name}_shape_{d}", n)
         return scope
 
-    def _pack(self, variant: Variant, args, arrays, lo, hi, stream):
+    def _pack(self, variant: Variant, args, arrays, lo, hi, stream, scratch_bytes: int = 0):
         by_name = {a.name: a for a in arrays}
         scal = dict(zip(self.arg_names, args))
         vals = []
@@ -349,6 +364,8 @@ class CompiledLoop:
                 vals.append(C.c_int64(hi))
             elif p.kind == "ws":
                 vals.append(C.c_void_p(rt.workspace(stream)))
+            elif p.kind == "scratch":
+                vals.append(C.c_void_p(rt.scratch(stream, max(scratch_bytes, 1 << 20))))
             elif p.kind == "mb":
                 from . import multi_gpu
                 vals.append(C.c_void_p(multi_gpu.combiner().descriptor))
@@ -424,6 +441,12 @@ class CompiledLoop:
                 else:
                     ov.update({"P_G": 32, "P_BLOCK": 128, "P_U": u, "P_R": 2 if light else 1, "P_MINB": 1})
             return ("rows", bucket, max(trip, 1).bit_length()), ov
+        if plan.kind == "csrdense" and "P_STREAM" in plan.tunables:
+            # The streaming form starts one wave of CTAs and a second kernel whatever the size; below a few
+            # thousand rows the row-tiled form (one CTA per 32 rows) is over before that pays.
+            if n_iter < 4096 or n_iter >= 2 ** 31:
+                return ("n", bucket, "tiled"), dict(plan.info["row_tiled"], P_STREAM=0)
+            return ("n", bucket, "stream"), {}
         if plan.kind == "csr" and plan.info.get("indptr"):
             row_class, ov = self._csr_profile(variant, arrays, stream)
             return ("csr", bucket, row_class), ov
@@ -498,7 +521,8 @@ class CompiledLoop:
         best, best_t = dict(start), float("inf")
         # coordinate descent over the tunables, starting from this class's defaults
         cur = dict(start)
-        pack = self._pack(variant, args, arrays, lo, hi, stream)
+        widest = {k: max(v) for k, v in plan.tunables.items()}     # the largest scratch any candidate needs
+        pack = self._pack(variant, args, arrays, lo, hi, stream, plan.scratch_bytes(widest, n_iter, self.sm_count))
         for name in list(plan.tunables):
             for cand in plan.tunables[name]:
                 trial = dict(cur)
@@ -507,6 +531,10 @@ class CompiledLoop:
                     h = variant.handle(trial)
                     grid, block, smem = plan.launch_config(trial, n_iter, self.sm_count)
                     t = rt.time_launches(h, grid, block, pack, smem, stream, warmup=1, iters=5)
+                    post = plan.post_config(trial, n_iter, self.sm_count)
+                    if post is not None:       # the second kernel of a two-kernel plan is part of the cost
+                        t += rt.time_launches(variant.post_handle(trial), post[0], post[1], pack, 0, stream,
+                                              warmup=1, iters=5)
                 except rt.AppyRuntimeError:
                     continue
                 if t < best_t:
@@ -718,7 +746,7 @@ class CompiledLoop:
         return memo is not None and self._replay(memo, args)
 
     def _replay(self, memo, args) -> bool:
-        handle, grid, block, smem, pack, seq_slot, memo_stream, cells, host_slots, scalar_slots = memo
+        handle, grid, block, smem, pack, seq_slot, memo_stream, cells, host_slots, scalar_slots, post, scratch = memo
         torch = sys.modules.get("torch")
         if torch is not None and (self.has_device_args or not host_slots):
             stream = _torch_stream(torch, self.device)      # orders with the producers of the device tensors
@@ -740,7 +768,11 @@ class CompiledLoop:
             if seq_slot is not None:
                 from . import multi_gpu
                 pack.values[seq_slot].value = multi_gpu.combiner().next_seq()
+            if scratch is not None:     # the stream's scratch buffer may have been replaced by a larger one
+                pack.values[scratch[0]].value = rt.scratch(stream, scratch[1])
             rt.launch(handle, grid, block, pack, smem, stream)
+            if post is not None:
+                rt.launch(post[0], post[1], post[2], pack, 0, stream)
         if cells:
             self._post_combine(cells)
         if host_slots:
@@ -803,10 +835,17 @@ class CompiledLoop:
                 self._pre_combine(cells)
         if hi > lo or exchange_only:
             tun = self._choose_tunables(variant, args, arrays, scope, lo, hi, stream)
-            pack = self._pack(variant, args, arrays, lo, hi, stream)
+            need = variant.plan.scratch_bytes(tun, hi - lo, self.sm_count)
+            pack = self._pack(variant, args, arrays, lo, hi, stream, need)
             h = variant.handle(tun)
             grid, block, smem = variant.plan.launch_config(tun, hi - lo, self.sm_count)
             rt.launch(h, grid, block, pack, smem, stream)
+            post = variant.plan.post_config(tun, hi - lo, self.sm_count)
+            if post is not None:        # second kernel of a two-kernel plan: same arguments, same stream
+                post = (variant.post_handle(tun), post[0], post[1])
+                rt.launch(post[0], post[1], post[2], pack, 0, stream)
+            kinds_ = [p.kind for p in variant.plan.params]
+            scratch = (kinds_.index("scratch"), max(need, 1 << 20)) if "scratch" in kinds_ else None
             # Launch record.  With host arrays it is kept when they are contiguous, none of them had to
             # be copied to become so, the stored ones overlap nothing, and the loop does not distribute
             # or combine (those paths look at the arrays again).
@@ -829,10 +868,10 @@ class CompiledLoop:
                 scalar_slots = tuple((i, pslot[self.arg_names[i]]) for i in sorted(self.data_scalars)
                                      if self.arg_names[i] in pslot)
                 self.memo[mkey] = (h, grid, block, smem, pack, seq_slot,
-                                   stream if (variant.plan.uses_ws or any_host) else None, cells, tuple(host_slots),
-                                   scalar_slots)
+                                   stream if (variant.plan.uses_ws or any_host or scratch) else None, cells,
+                                   tuple(host_slots), scalar_slots, post, scratch)
         elif not any_host and mkey is not None:
-            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells, (), ())
+            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells, (), (), None, None)
         if cells:
             self._post_combine(cells)
         if any_host:

@@ -47,6 +47,7 @@ class Env:
     locals: dict = field(default_factory=dict)       # name -> Ty
     indices: dict = field(default_factory=dict)      # loop index name -> Ty
     implicit: dict = field(default_factory=dict)     # X_shape_d / X_stride_d actually used -> (array, kind, dim)
+    numerics: str = "numpy"     # "numpy": NEP-50 weak literals, IEEE division; "triton": the reference backend's rules
 
 
 # python/numpy function name -> (double name, float name)
@@ -77,7 +78,83 @@ MATH2 = {
     "fdim": ("fdim", "fdimf"), "nextafter": ("nextafter", "nextafterf"), "rhypot": ("rhypot", "rhypotf"),
     "fmax": ("fmax", "fmaxf"), "fmin": ("fmin", "fminf"),
 }
-PREDICATES = {"isnan": "isnan", "isinf": "isinf", "isfinite": "isfinite", "signbit": "signbit"}
+PREDICATES = {"isnan": "isnan", "isinf": "isinf", "isfinite": "isfinite", "signbit": "signbit",
+              "finitef": "isfinite", "isfinited": "isfinite"}
+
+# Names of the reference's device-function table (device_passes/tl_libdevice.py, 198 stubs bound to
+# Triton's libdevice) that are not plain math-library calls: every one maps to the CUDA intrinsic or
+# math function of the same meaning.  Entry: list of overloads (argument types, CUDA name, result type);
+# the overload is chosen by the width of the promoted arguments, arguments are converted to its types.
+_F, _D, _I, _U, _L, _UL = T.F32, T.F64, T.I32, Ty("u", 32), T.I64, Ty("u", 64)
+DEVICE_FUNCS: dict = {}
+
+
+def _dev(name, *overloads):
+    DEVICE_FUNCS[name] = list(overloads)
+
+
+for _m in ("rn", "rz", "rd", "ru"):
+    for _op in ("add", "sub", "mul", "div"):
+        _dev(f"{_op}_{_m}", ((_D, _D), f"__d{_op}_{_m}", _D), ((_F, _F), f"__f{_op}_{_m}", _F))
+    _dev(f"fma_{_m}", ((_D, _D, _D), f"__fma_{_m}", _D), ((_F, _F, _F), f"__fmaf_{_m}", _F))
+    _dev(f"rcp_{_m}", ((_D,), f"__drcp_{_m}", _D), ((_F,), f"__frcp_{_m}", _F))
+    _dev(f"sqrt_{_m}", ((_D,), f"__dsqrt_{_m}", _D), ((_F,), f"__fsqrt_{_m}", _F))
+    _dev(f"double2float_{_m}", ((_D,), f"__double2float_{_m}", _F))
+    for _src, _sty in (("double", _D), ("float", _F)):
+        _dev(f"{_src}2int_{_m}", ((_sty,), f"__{_src}2int_{_m}", _I))
+        _dev(f"{_src}2uint_{_m}", ((_sty,), f"__{_src}2uint_{_m}", _U))
+        _dev(f"{_src}2ll_{_m}", ((_sty,), f"__{_src}2ll_{_m}", _L))
+        _dev(f"{_src}2ull_{_m}", ((_sty,), f"__{_src}2ull_{_m}", _UL))
+    _dev(f"int2float_{_m}", ((_I,), f"__int2float_{_m}", _F))
+    _dev(f"uint2float_{_m}", ((_U,), f"__uint2float_{_m}", _F))
+    _dev(f"ll2float_{_m}", ((_L,), f"__ll2float_{_m}", _F))
+    _dev(f"ull2float_{_m}", ((_UL,), f"__ull2float_{_m}", _F))
+    _dev(f"ll2double_{_m}", ((_L,), f"__ll2double_{_m}", _D))
+    _dev(f"ull2double_{_m}", ((_UL,), f"__ull2double_{_m}", _D))
+_dev("int2double_rn", ((_I,), "__int2double_rn", _D))
+_dev("uint2double_rn", ((_U,), "__uint2double_rn", _D))
+_dev("rsqrt_rn", ((_F,), "__frsqrt_rn", _F))
+_dev("hiloint2double", ((_I, _I), "__hiloint2double", _D))
+_dev("double2loint", ((_D,), "__double2loint", _I))
+_dev("double2hiint", ((_D,), "__double2hiint", _I))
+_dev("int_as_float", ((_I,), "__int_as_float", _F))
+_dev("float_as_int", ((_F,), "__float_as_int", _I))
+_dev("uint_as_float", ((_U,), "__uint_as_float", _F))
+_dev("float_as_uint", ((_F,), "__float_as_uint", _U))
+_dev("longlong_as_double", ((_L,), "__longlong_as_double", _D))
+_dev("double_as_longlong", ((_D,), "__double_as_longlong", _L))
+for _n, _c in (("sinf", "__sinf"), ("cosf", "__cosf"), ("tanf", "__tanf"), ("log2f", "__log2f"), ("logf", "__logf"),
+               ("expf", "__expf"), ("exp10f", "__exp10f"), ("log10f", "__log10f"), ("tanhf", "appy_tanh_approx")):
+    _dev(f"fast_{_n}", ((_F,), _c, _F))
+_dev("fast_powf", ((_F, _F), "__powf", _F))
+_dev("fast_dividef", ((_F, _F), "__fdividef", _F))
+_dev("saturatef", ((_F,), "__saturatef", _F))
+_dev("clz", ((_I,), "__clz", _I), ((_L,), "__clzll", _I))
+_dev("popc", ((_U,), "__popc", _I), ((_UL,), "__popcll", _I))
+_dev("brev", ((_U,), "__brev", _U), ((_UL,), "__brevll", _UL))
+_dev("ffs", ((_I,), "__ffs", _I), ((_L,), "__ffsll", _I))
+_dev("mulhi", ((_I, _I), "__mulhi", _I), ((_L, _L), "__mul64hi", _L), ((_U, _U), "__umulhi", _U),
+     ((_UL, _UL), "__umul64hi", _UL))
+_dev("mul24", ((_I, _I), "__mul24", _I), ((_U, _U), "__umul24", _U))
+_dev("hadd", ((_I, _I), "__hadd", _I), ((_U, _U), "__uhadd", _U))
+_dev("rhadd", ((_I, _I), "__rhadd", _I), ((_U, _U), "__urhadd", _U))
+_dev("sad", ((_I, _I, _U), "__sad", _U), ((_U, _U, _U), "__usad", _U))
+_dev("byte_perm", ((_U, _U, _U), "__byte_perm", _U))
+_dev("llrint", ((_D,), "llrint", _L), ((_F,), "llrintf", _L))
+_dev("llround", ((_D,), "llround", _L), ((_F,), "llroundf", _L))
+_dev("ilogb", ((_D,), "ilogb", _I), ((_F,), "ilogbf", _I))
+_dev("ldexp", ((_D, _I), "ldexp", _D), ((_F, _I), "ldexpf", _F))
+_dev("scalbn", ((_D, _I), "scalbn", _D), ((_F, _I), "scalbnf", _F))
+_dev("yn", ((_I, _D), "yn", _D), ((_I, _F), "ynf", _F))
+_dev("jn", ((_I, _D), "jn", _D), ((_I, _F), "jnf", _F))
+_dev("cyl_bessel_i0", ((_D,), "cyl_bessel_i0", _D), ((_F,), "cyl_bessel_i0f", _F))
+_dev("cyl_bessel_i1", ((_D,), "cyl_bessel_i1", _D), ((_F,), "cyl_bessel_i1f", _F))
+_dev("norm3d", ((_D, _D, _D), "norm3d", _D), ((_F, _F, _F), "norm3df", _F))
+_dev("rnorm3d", ((_D, _D, _D), "rnorm3d", _D), ((_F, _F, _F), "rnorm3df", _F))
+_dev("norm4d", ((_D, _D, _D, _D), "norm4d", _D), ((_F, _F, _F, _F), "norm4df", _F))
+_dev("rnorm4d", ((_D, _D, _D, _D), "rnorm4d", _D), ((_F, _F, _F, _F), "rnorm4df", _F))
+# the one name of the reference's table without a CUDA C counterpart: rcp64h (upper half of a float64
+# reciprocal estimate, an internal of libdevice's own division); it raises "Unknown function"
 CASTS = {"float32": T.F32, "float64": T.F64, "double": T.F64, "single": T.F32, "int8": Ty("i", 8),
          "int16": Ty("i", 16), "int32": T.I32, "int64": T.I64, "uint8": Ty("u", 8), "uint16": Ty("u", 16),
          "uint32": Ty("u", 32), "uint64": Ty("u", 64), "bool_": T.BOOL, "intc": T.I32, "int_": T.I64}
@@ -199,6 +276,10 @@ class Emitter:
         if isinstance(v, int):
             return (f"{v}LL" if abs(v) >= 2 ** 31 else str(v), T.WEAK_INT)
         if isinstance(v, float):
+            if self.env.numerics == "triton":
+                # the reference turns every float literal into a float64 scalar tensor
+                # (device_passes/lower_constants.py:22-38): arithmetic that touches it runs in float64
+                return (float_literal(v), T.F64)
             return (float_literal(v), T.WEAK_FLOAT)
         raise NotImplementedError(f"Unsupported constant: {v!r}")
 
@@ -263,6 +344,8 @@ class Emitter:
         if isinstance(op, ast.Mult):
             return (f"({a} * {b})", rty)
         if isinstance(op, ast.Div):
+            if self.env.numerics == "triton" and rty.is_float and rty.bits == 32:
+                return (f"appy_div_full({a}, {b})", rty)     # Triton's float32 `/` is div.full.f32 (2 ulp)
             return (f"({a} / {b})", rty)
         targ = "" if rty.is_float else f"<{rty.strong().c}>"    # integer literals are plain `int` in C
         if isinstance(op, ast.FloorDiv):
@@ -393,6 +476,28 @@ class Emitter:
             ft = T.float_of(T.promote(at, bt))
             fn = MATH2[name][1 if ft.bits == 32 else 0]
             return (f"{fn}({cast(ac, at, ft.strong())}, {cast(bc, bt, ft.strong())})", ft)
+        if name in DEVICE_FUNCS:
+            over = [o for o in DEVICE_FUNCS[name] if len(o[0]) == len(args)]
+            if not over:
+                raise ValueError(f"Unknown function: {ast.unparse(node.func)} with {len(args)} arguments")
+            vals = [self.expr(a) for a in args]
+            pick = over[0]
+            if len(over) > 1:
+                # width and kind of the arguments that the overloads disagree on
+                vary = [i for i in range(len(args)) if len({o[0][i] for o in over}) > 1]
+                ty = vals[vary[0]][1]
+                for i in vary[1:]:
+                    ty = T.promote(ty, vals[i][1])
+                if over[0][0][vary[0]].is_float:
+                    ty = T.float_of(ty)
+                    pick = next((o for o in over if o[0][vary[0]].bits == ty.bits), over[0])
+                else:
+                    bits = 64 if (not ty.weak and ty.bits == 64) else 32
+                    kind = "u" if ty.kind == "u" else "i"
+                    pick = next((o for o in over if o[0][vary[0]].bits == bits and o[0][vary[0]].kind == kind),
+                                next((o for o in over if o[0][vary[0]].bits == bits), over[0]))
+            code = f"{pick[1]}(" + ", ".join(cast(c, t, want) for (c, t), want in zip(vals, pick[0])) + ")"
+            return (code, pick[2])
         if name in PREDICATES and len(args) == 1:
             c, t = self.expr(args[0])
             ft = T.float_of(t)

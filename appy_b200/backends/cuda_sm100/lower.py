@@ -60,6 +60,20 @@ class KernelPlan:
     uses_ws: bool = False
     vec: int = 1
     info: dict = field(default_factory=dict)
+    post: str | None = None          # name of a second kernel launched after the main one (same arguments)
+
+    def post_config(self, tun: dict, n_iter: int, sm_count: int):
+        """(grid, block) of the second kernel, or None when this choice of tunables has none."""
+        if self.post and self.kind == "csrdense" and tun.get("P_STREAM"):
+            return 4 * sm_count, 256
+        return None
+
+    def scratch_bytes(self, tun: dict, n_iter: int, sm_count: int) -> int:
+        """Bytes of per-stream scratch the launch needs (pieces of rows cut by share boundaries)."""
+        if self.kind == "csrdense" and tun.get("P_STREAM"):
+            workers = sm_count * tun["P_MINB"] * tun["P_WARPS"]
+            return (16 + 16 * workers + 255) // 256 * 256 + workers * 2 * self.info["row_bytes_padded"]
+        return 0
 
     def launch_config(self, tun: dict, n_iter: int, sm_count: int):
         """(grid, block, dynamic shared bytes) for `n_iter` outer iterations."""
@@ -82,6 +96,11 @@ class KernelPlan:
         if k == "csr":
             rows = tun["P_ROWS"]
             return max(1, min((n_iter + rows - 1) // rows, 2 ** 31 - 1)), tun["P_BLOCK"], 0
+        if k == "csrdense" and tun.get("P_STREAM"):
+            # one wave of resident CTAs; every warp of the grid takes an equal share of the non-zeros
+            w = tun["P_WARPS"]
+            dyn = w * tun["P_D"] * self.info["row_bytes_padded"] + w * 32 * 4
+            return sm_count * tun["P_MINB"], 32 * w, dyn
         if k == "csrdense":
             rows = tun["P_ROWS"]
             dyn = tun["P_WARPS"] * tun["P_S"] * (self.info["row_bytes"] + 8) if "P_S" in tun else 0   # ring + barriers
@@ -212,6 +231,7 @@ class Lowering:
         body = self.loop.body
         st_arr = stored_arrays(body)
         self.env = Env()
+        self.env.numerics = "triton" if options.get("fp_contract") == "triton" else "numpy"
         for a in args:
             if a.kind == "array":
                 self.env.arrays[a.name] = ArraySym(a.name, a.ty, a.ndim, a.unit_last,
@@ -276,6 +296,8 @@ class Lowering:
         ps.append(Param("__hi", "hi", T.I64))
         if uses_ws:
             ps.append(Param("__ws", "ws"))
+        if getattr(self, "_uses_scratch", False):
+            ps.append(Param("__scratch", "scratch"))
         if uses_ws and self.options.get("combine") == "p2p":
             ps.append(Param("__mb", "mb"))
             ps.append(Param("__seq", "seq", Ty("u", 64)))
@@ -291,6 +313,8 @@ class Lowering:
             return f"{a.ty.c}* {p.name}"
         if p.kind == "ws":
             return "void* __ws"
+        if p.kind == "scratch":
+            return "void* __scratch"
         if p.kind == "mb":
             return "const appy_mailbox* __mb"
         return f"{p.ty.strong().c} {p.name}"
@@ -299,9 +323,9 @@ class Lowering:
         return [self._c_param(p) + ";" for p in params if p.kind not in ("lo", "hi")]
 
     def _kernel_wrapper(self, params, body_struct: str, call: str, smem_decl: str, extra_init: list[str] = (),
-                        launch_bounds: str = "P_BLOCK") -> list[str]:
+                        launch_bounds: str = "P_BLOCK", name: str | None = None) -> list[str]:
         sig = ", ".join(self._c_param(p) for p in params)
-        lines = [f'extern "C" __global__ void __launch_bounds__({launch_bounds}) {self.name}({sig}) {{',
+        lines = [f'extern "C" __global__ void __launch_bounds__({launch_bounds}) {name or self.name}({sig}) {{',
                  f"  {smem_decl}",
                  f"  {body_struct} __body;"]
         for p in params:
@@ -977,6 +1001,10 @@ class Lowering:
         init_c = cast(*em.expr(z.body[0].value), elt)
         struct = f"{self.name}_body"
         bulk = bool(self.options.get("_bulk_rows")) and nc > 0 and V > 1
+        # the streaming form (non-zeros dealt out to the warps, t_csr_dense_stream.cuh) keeps the pieces of
+        # rows cut by share boundaries in a scratch buffer between its two kernels
+        stream = not bulk and self.options.get("_spmm_stream", True)
+        self._uses_scratch = stream
         params = self._params(uses_ws=bulk)           # the bulk variant reports a wait that ran out at ws+8
         ptr = env.arrays[indptr]
         src = ['#include "t_csr_dense.cuh"', f"struct {struct} {{",
@@ -998,7 +1026,23 @@ class Lowering:
             smem += "\n  extern __shared__ __align__(128) unsigned char __dyn[];"
             call = (f"appy_csr_dense_bulk<{V}, {Tn}, P_S, P_WARPS, P_ROWS, {nc}, {ptr.ty.c}>(__body, {indptr}, __lo, "
                     f"__hi, __smem, __dyn, reinterpret_cast<unsigned*>(reinterpret_cast<char*>(__ws) + 8), 1u << 22);")
+        row_bytes_padded = 32 * V * Tn * (elt.bits // 8)
+        if stream:
+            src[0] = '#include "t_csr_dense_stream.cuh"'
+            src += ["#if P_STREAM"]
+            src += self._kernel_wrapper(
+                params, struct,
+                f"appy_csr_dense_stream<{V}, {Tn}, P_D, P_WARPS, {nc}, {ptr.ty.c}>(__body, {indptr}, __lo, __hi, {ncols}, "
+                f"__scratch, __dyn);",
+                "extern __shared__ __align__(16) unsigned char __dyn[];", launch_bounds="32 * P_WARPS, P_MINB")
+            src += self._kernel_wrapper(
+                params, struct,
+                f"appy_csr_dense_fixup<{V}, {Tn}, {nc}, {ptr.ty.c}>(__body, {indptr}, __lo, __hi, {ncols}, __scratch);",
+                "", launch_bounds="256", name=f"{self.name}_fixup")
+            src += ["#else"]
         src += self._kernel_wrapper(params, struct, call, smem, launch_bounds="32 * P_WARPS, P_MINB")
+        if stream:
+            src += ["#endif"]
         if bulk:
             tun = {"P_WARPS": [8, 4, 16], "P_ROWS": [32, 16, 64], "P_S": [4, 8, 16], "P_MINB": [2, 1]}
             return KernelPlan("csrdense", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr,
@@ -1014,8 +1058,29 @@ class Lowering:
                "P_D": ([4, 8, 2] if one_pack else [8, 4, 2]) if small else [2, 4],
                "P_MINB": ([3, 4, 2] if one_pack else [4, 3, 5, 2]) if small else [2, 1],
                "P_ROLL": [0, 1] if one_pack else [1, 0]}
-        return KernelPlan("csrdense", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr, vec=V,
-                          info={"template": "T5 CSR x dense", "ncols": ncols, "vector_width": V, "indptr": indptr})
+        info = {"template": "T5 CSR x dense", "ncols": ncols, "vector_width": V, "indptr": indptr,
+                "row_bytes_padded": row_bytes_padded}
+        if not stream:
+            return KernelPlan("csrdense", self.name, "\n".join(src), params, tun, self.lo_expr, self.hi_expr, vec=V,
+                              info=info)
+        # Streaming form: rows in flight per warp (P_D, a ring in shared memory) and warps per SM sized so that
+        # about 192 KB of B rows are in flight per SM; the accumulators (V*T per lane) bound the CTAs per SM.
+        warps = 16 if row_bytes_padded <= 512 else 8
+        d = 8 if row_bytes_padded <= 1024 else 16
+        while d > 1 and warps * d * row_bytes_padded > 64 * 1024:
+            d //= 2
+        while warps > 2 and warps * d * row_bytes_padded > 64 * 1024:
+            warps //= 2
+        minb = 3 if V * Tn <= 8 else 2 if V * Tn <= 16 else 1
+        info["row_tiled"] = {k: v[0] for k, v in tun.items()}       # defaults of the row-tiled form (small inputs)
+        info["template"] = "T5 CSR x dense (streaming: non-zeros dealt out to the warps)"
+        stun = {"P_STREAM": [1, 0],
+                "P_WARPS": [warps] + [w for w in (16, 8, 4) if w != warps],
+                "P_D": [d] + [x for x in (16, 8, 4, 2) if x != d],
+                "P_MINB": [minb] + [x for x in (4, 3, 2, 1) if x != minb],
+                "P_ROWS": tun["P_ROWS"], "P_ROLL": tun["P_ROLL"]}
+        return KernelPlan("csrdense", self.name, "\n".join(src), params, stun, self.lo_expr, self.hi_expr, vec=V,
+                          info=info, post=f"{self.name}_fixup")
 
 
 def _replace_index(sub: ast.Subscript, var: str, new: str) -> ast.Subscript:

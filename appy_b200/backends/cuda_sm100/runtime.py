@@ -41,6 +41,8 @@ SIGNATURES = {
     "appy_d2d_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "appy_compile": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, c_void_pp]),
     "appy_compile_check": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, C.POINTER(C.c_size_t)]),
+    "appy_compile_image": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, C.POINTER(C.c_size_t),
+                                     C.POINTER(C.c_int)]),
     "appy_compile_log": (C.c_char_p, []),
     "appy_kernel_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int),
                                    C.POINTER(C.c_int)]),
@@ -49,6 +51,7 @@ SIGNATURES = {
     "appy_time_launches": (C.c_int, [C.c_void_p, C.c_uint, C.c_uint, C.c_size_t, c_void_pp,
                                      C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "appy_workspace": (C.c_int, [C.c_void_p, c_void_pp, C.POINTER(C.c_size_t)]),
+    "appy_scratch": (C.c_int, [C.c_void_p, C.c_size_t, c_void_pp]),
     "appy_partition_range": (C.c_int, [C.c_int64, C.c_int64, C.c_int, C.c_int64,
                                        C.POINTER(C.c_int64)]),
     "appy_partition_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int,
@@ -190,6 +193,13 @@ def workspace(stream_: int = 0) -> int:
     return p.value
 
 
+def scratch(stream_: int, nbytes: int) -> int:
+    """Grow-only scratch buffer of the current device for kernels queued on `stream_`."""
+    p = C.c_void_p()
+    check(lib().appy_scratch(C.c_void_p(stream_), nbytes, C.byref(p)))
+    return p.value
+
+
 def nvrtc_options(extra: list[str] | None = None) -> bytes:
     opts = ["-I" + template_dir()]
     if extra:
@@ -223,6 +233,14 @@ def compile_check(src: str, name: str, extra_opts: list[str] | None = None) -> i
     n = C.c_size_t()
     check(lib().appy_compile_check(src.encode(), name.encode(), nvrtc_options(extra_opts), C.byref(n)))
     return n.value
+
+
+def compile_image(src: str, name: str, extra_opts: list[str] | None = None, cache_dir: str | None = None):
+    """(cubin size, came from the on-disk cache) — the compile step of `compile_kernel` without loading."""
+    n, hit = C.c_size_t(), C.c_int()
+    check(lib().appy_compile_image(src.encode(), name.encode(), nvrtc_options(extra_opts),
+                                   cache_dir.encode() if cache_dir else None, C.byref(n), C.byref(hit)))
+    return n.value, bool(hit.value)
 
 
 def kernel_info(handle: int) -> dict:

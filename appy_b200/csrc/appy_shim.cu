@@ -11,12 +11,14 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <dirent.h>
 #include <fstream>
 #include <map>
 #include <mutex>
 #include <sstream>
 #include <string>
 #include <unordered_map>
+#include <unordered_set>
 #include <vector>
 
 #include "../../include/appy_sm100.h"
@@ -55,6 +57,9 @@ struct DeviceState {
   std::unordered_map<cudaStream_t, void*> workspaces;
   std::multimap<size_t, void*> free_blocks;          // cached allocator: size -> block
   std::unordered_map<void*, size_t> live_blocks;     // block -> rounded size
+  std::unordered_set<void*> free_set;                // blocks that sit in free_blocks right now
+  struct Scratch { void* dptr; size_t bytes; };
+  std::unordered_map<cudaStream_t, Scratch> scratch; // grow-only scratch of the two-kernel templates, per stream
   struct Mirror { void* dptr; size_t bytes; uint64_t last_use; };
   std::unordered_map<const void*, Mirror> mirrors;   // host pointer -> device mirror
   size_t mirror_bytes = 0;
@@ -107,12 +112,118 @@ struct Kernel {
 };
 std::unordered_map<std::string, Kernel*> g_kernels;  // key: hash + name
 
-uint64_t fnv1a(const std::string& s, uint64_t h = 1469598103934665603ull) {
-  for (unsigned char c : s) {
-    h ^= c;
-    h *= 1099511628211ull;
+// SHA-256 (FIPS 180-4), used for the key of the compiled-kernel cache
+struct Sha256 {
+  uint32_t h[8] = {0x6a09e667u, 0xbb67ae85u, 0x3c6ef372u, 0xa54ff53au, 0x510e527fu, 0x9b05688cu, 0x1f83d9abu, 0x5be0cd19u};
+  unsigned char buf[64];
+  size_t fill = 0;
+  uint64_t total = 0;
+  static uint32_t rotr(uint32_t x, int n) { return (x >> n) | (x << (32 - n)); }
+  void block(const unsigned char* p) {
+    static const uint32_t K[64] = {
+        0x428a2f98u, 0x71374491u, 0xb5c0fbcfu, 0xe9b5dba5u, 0x3956c25bu, 0x59f111f1u, 0x923f82a4u, 0xab1c5ed5u,
+        0xd807aa98u, 0x12835b01u, 0x243185beu, 0x550c7dc3u, 0x72be5d74u, 0x80deb1feu, 0x9bdc06a7u, 0xc19bf174u,
+        0xe49b69c1u, 0xefbe4786u, 0x0fc19dc6u, 0x240ca1ccu, 0x2de92c6fu, 0x4a7484aau, 0x5cb0a9dcu, 0x76f988dau,
+        0x983e5152u, 0xa831c66du, 0xb00327c8u, 0xbf597fc7u, 0xc6e00bf3u, 0xd5a79147u, 0x06ca6351u, 0x14292967u,
+        0x27b70a85u, 0x2e1b2138u, 0x4d2c6dfcu, 0x53380d13u, 0x650a7354u, 0x766a0abbu, 0x81c2c92eu, 0x92722c85u,
+        0xa2bfe8a1u, 0xa81a664bu, 0xc24b8b70u, 0xc76c51a3u, 0xd192e819u, 0xd6990624u, 0xf40e3585u, 0x106aa070u,
+        0x19a4c116u, 0x1e376c08u, 0x2748774cu, 0x34b0bcb5u, 0x391c0cb3u, 0x4ed8aa4au, 0x5b9cca4fu, 0x682e6ff3u,
+        0x748f82eeu, 0x78a5636fu, 0x84c87814u, 0x8cc70208u, 0x90befffau, 0xa4506cebu, 0xbef9a3f7u, 0xc67178f2u};
+    uint32_t w[64];
+    for (int i = 0; i < 16; ++i)
+      w[i] = (uint32_t)p[4 * i] << 24 | (uint32_t)p[4 * i + 1] << 16 | (uint32_t)p[4 * i + 2] << 8 | p[4 * i + 3];
+    for (int i = 16; i < 64; ++i) {
+      const uint32_t s0 = rotr(w[i - 15], 7) ^ rotr(w[i - 15], 18) ^ (w[i - 15] >> 3);
+      const uint32_t s1 = rotr(w[i - 2], 17) ^ rotr(w[i - 2], 19) ^ (w[i - 2] >> 10);
+      w[i] = w[i - 16] + s0 + w[i - 7] + s1;
+    }
+    uint32_t a = h[0], b = h[1], c = h[2], d = h[3], e = h[4], f = h[5], g = h[6], hh = h[7];
+    for (int i = 0; i < 64; ++i) {
+      const uint32_t t1 = hh + (rotr(e, 6) ^ rotr(e, 11) ^ rotr(e, 25)) + ((e & f) ^ (~e & g)) + K[i] + w[i];
+      const uint32_t t2 = (rotr(a, 2) ^ rotr(a, 13) ^ rotr(a, 22)) + ((a & b) ^ (a & c) ^ (b & c));
+      hh = g; g = f; f = e; e = d + t1; d = c; c = b; b = a; a = t1 + t2;
+    }
+    h[0] += a; h[1] += b; h[2] += c; h[3] += d; h[4] += e; h[5] += f; h[6] += g; h[7] += hh;
   }
-  return h;
+  void update(const void* data, size_t n) {
+    const unsigned char* p = static_cast<const unsigned char*>(data);
+    total += n;
+    while (n) {
+      const size_t take = std::min(n, sizeof buf - fill);
+      memcpy(buf + fill, p, take);
+      fill += take; p += take; n -= take;
+      if (fill == 64) { block(buf); fill = 0; }
+    }
+  }
+  void update(const std::string& t) { update(t.data(), t.size()); }
+  std::string hex() {
+    const uint64_t bits = total * 8;
+    const unsigned char one = 0x80, zero = 0;
+    update(&one, 1);
+    while (fill != 56) update(&zero, 1);
+    unsigned char len[8];
+    for (int i = 0; i < 8; ++i) len[i] = (unsigned char)(bits >> (56 - 8 * i));
+    update(len, 8);
+    char out[65];
+    for (int i = 0; i < 8; ++i) snprintf(out + 8 * i, 9, "%08x", h[i]);
+    return std::string(out, 64);
+  }
+};
+
+// Digest of every file in a template directory (the generated sources only say
+// `#include "t_flat.cuh"`, so the headers' contents have to enter the cache key themselves).
+std::unordered_map<std::string, std::string> g_dir_digest;
+std::string dir_digest(const std::string& dir) {
+  auto it = g_dir_digest.find(dir);
+  if (it != g_dir_digest.end()) return it->second;
+  std::vector<std::string> names;
+  if (DIR* d = opendir(dir.c_str())) {
+    while (dirent* e = readdir(d))
+      if (e->d_name[0] != '.') names.push_back(e->d_name);
+    closedir(d);
+  }
+  std::sort(names.begin(), names.end());
+  Sha256 sh;
+  for (auto& n : names) {
+    std::ifstream f(dir + "/" + n, std::ios::binary);
+    if (!f) continue;
+    std::string body((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+    sh.update(n);
+    sh.update("\x1f");
+    sh.update(body);
+    sh.update("\x1e");
+  }
+  return g_dir_digest[dir] = sh.hex();
+}
+
+// A cache file is: "APPYCUBIN1\n" + 64 hex digits of the key + "\n" + 16 hex digits of the image
+// length + "\n" + the image.  Anything else (another key, a torn or truncated file) is not loaded.
+const char kCacheMagic[] = "APPYCUBIN1\n";
+bool read_cache_file(const std::string& path, const std::string& key_hex, std::vector<char>& image) {
+  std::ifstream f(path, std::ios::binary);
+  if (!f) return false;
+  std::string all((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+  const size_t head = sizeof kCacheMagic - 1 + 64 + 1 + 16 + 1;
+  if (all.size() < head || all.compare(0, sizeof kCacheMagic - 1, kCacheMagic) != 0) return false;
+  if (all.compare(sizeof kCacheMagic - 1, 64, key_hex) != 0) return false;
+  unsigned long long len = 0;
+  if (sscanf(all.c_str() + sizeof kCacheMagic - 1 + 65, "%16llx", &len) != 1) return false;
+  if (all.size() != head + len || len == 0) return false;
+  image.assign(all.begin() + head, all.end());
+  return true;
+}
+void write_cache_file(const std::string& path, const std::string& key_hex, const std::vector<char>& image,
+                      const void* unique) {
+  const std::string tmp = path + ".tmp" + std::to_string((unsigned long long)(uintptr_t)unique);
+  std::ofstream f(tmp, std::ios::binary);
+  if (!f) return;
+  char len[18];
+  snprintf(len, sizeof len, "%016llx\n", (unsigned long long)image.size());
+  f << kCacheMagic << key_hex << "\n" << len;
+  f.write(image.data(), (std::streamsize)image.size());
+  f.close();
+  if (f) std::rename(tmp.c_str(), path.c_str());    // readers never see a torn file
+  else std::remove(tmp.c_str());
 }
 
 int load_cubin(const std::vector<char>& image, const char* name, Kernel** out) {
@@ -283,6 +394,7 @@ int appy_malloc(void** dptr, size_t bytes) {
   auto it = d.free_blocks.lower_bound(want);
   if (it != d.free_blocks.end() && it->first <= 2 * want) {
     *dptr = it->second;
+    d.free_set.erase(it->second);
     d.free_blocks.erase(it);
     return APPY_OK;
   }
@@ -295,6 +407,7 @@ int appy_malloc(void** dptr, size_t bytes) {
       d.live_blocks.erase(kv.second);
     }
     d.free_blocks.clear();
+    d.free_set.clear();
     e = cudaMalloc(&p, want);
   }
   if (e != cudaSuccess)
@@ -312,7 +425,12 @@ int appy_free(void* dptr) {
   DeviceState& d = g_dev[dev];
   auto it = d.live_blocks.find(dptr);
   if (it == d.live_blocks.end()) return fail(APPY_ERR_ARG, "appy_free: unknown block %p", dptr);
+  if (d.free_set.count(dptr)) return fail(APPY_ERR_ARG, "appy_free: block %p is already free", dptr);
+  for (auto& m : d.mirrors)
+    if (m.second.dptr == dptr)
+      return fail(APPY_ERR_ARG, "appy_free: block %p is the mirror of a host range; use appy_evict", dptr);
   d.free_blocks.emplace(it->second, dptr);
+  d.free_set.insert(dptr);
   return APPY_OK;
 }
 
@@ -327,6 +445,7 @@ int appy_trim(void) {
     d.live_blocks.erase(kv.second);
   }
   d.free_blocks.clear();
+  d.free_set.clear();
   return APPY_OK;
 }
 
@@ -381,6 +500,7 @@ const size_t kMirrorMaxBytes = (size_t)16 << 30;
 static void drop_mirror_locked(DeviceState& d, std::unordered_map<const void*, DeviceState::Mirror>::iterator it) {
   d.mirror_bytes -= it->second.bytes;
   d.free_blocks.emplace(d.live_blocks[it->second.dptr], it->second.dptr);
+  d.free_set.insert(it->second.dptr);
   d.mirrors.erase(it);
 }
 
@@ -494,56 +614,110 @@ int appy_workspace(void* stream, void** dptr, size_t* bytes) {
   return APPY_OK;
 }
 
+int appy_scratch(void* stream, size_t bytes, void** dptr) {
+  if (!dptr) return fail(APPY_ERR_ARG, "appy_scratch: NULL argument");
+  int dev;
+  if (int rc = cur_device(&dev)) return rc;
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceState& d = g_dev[dev];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  auto it = d.scratch.find(s);
+  if (it == d.scratch.end() || it->second.bytes < bytes) {
+    const size_t want = std::max<size_t>((bytes + (1u << 20) - 1) >> 20 << 20, 1u << 20);
+    void* p = nullptr;
+    CK(cudaMalloc(&p, want));
+    if (it != d.scratch.end()) {
+      // kernels queued on this stream may still use the old buffer: let them finish first
+      CK(cudaStreamSynchronize(s));
+      CK(cudaFree(it->second.dptr));
+      it->second = DeviceState::Scratch{p, want};
+    } else {
+      it = d.scratch.emplace(s, DeviceState::Scratch{p, want}).first;
+    }
+  }
+  *dptr = it->second.dptr;
+  return APPY_OK;
+}
+
 // ---------------------------------------------------------------- compile / launch
+
+// Key of a compiled kernel: source, options, contents of every include directory, NVRTC version and
+// target architecture.  Caller holds g_mu.
+static std::string compile_key(const char* src, const std::vector<std::string>& opts) {
+  int nv_major = 0, nv_minor = 0;
+  nvrtcVersion(&nv_major, &nv_minor);
+  Sha256 sh;
+  sh.update(src);
+  sh.update("\x1f");
+  for (auto& o : opts) {
+    sh.update(o);
+    sh.update("\x1f");
+    if (o.compare(0, 2, "-I") == 0) sh.update(dir_digest(o.substr(2)));
+  }
+  sh.update("nvrtc " + std::to_string(nv_major) + "." + std::to_string(nv_minor) + " sm_100a");
+  return sh.hex();
+}
+
+// The cubin of `src`, from the cache directory when it holds a valid entry for the key, otherwise
+// compiled (and then written there, best effort).  Caller holds g_mu.
+static int image_through_cache(const char* src, const char* kernel_name, const std::vector<std::string>& opts,
+                               const std::string& hex, const char* cache_dir, std::vector<char>& image,
+                               bool* from_cache, bool force_compile) {
+  std::string path;
+  *from_cache = false;
+  if (cache_dir && *cache_dir) {
+    path = std::string(cache_dir) + "/" + hex + ".cubin";
+    if (!force_compile && read_cache_file(path, hex, image)) {
+      *from_cache = true;
+      return APPY_OK;
+    }
+    image.clear();
+  }
+  if (int rc = nvrtc_build(src, kernel_name, opts, image)) return rc;
+  if (!path.empty()) write_cache_file(path, hex, image, &image);
+  return APPY_OK;
+}
 
 int appy_compile(const char* src, const char* kernel_name, const char* options,
                  const char* cache_dir, void** handle) {
   if (!src || !kernel_name || !handle) return fail(APPY_ERR_ARG, "appy_compile: NULL argument");
   g_log.clear();
   std::vector<std::string> opts = nvrtc_options(options);
-  int nv_major = 0, nv_minor = 0;
-  nvrtcVersion(&nv_major, &nv_minor);
-  std::string keystr = std::string(src) + "\x1f";
-  for (auto& o : opts) keystr += o + "\x1f";
-  keystr += std::to_string(nv_major) + "." + std::to_string(nv_minor);
-  char hex[32];
-  snprintf(hex, sizeof hex, "%016llx", (unsigned long long)fnv1a(keystr));
-  const std::string key = std::string(hex) + ":" + kernel_name;
-
   std::lock_guard<std::mutex> lk(g_mu);
+  const std::string hex = compile_key(src, opts);
+  const std::string key = hex + ":" + kernel_name;
   auto it = g_kernels.find(key);
   if (it != g_kernels.end()) {
     *handle = it->second;
     return APPY_OK;
   }
   std::vector<char> image;
-  std::string path;
-  if (cache_dir && *cache_dir) {
-    path = std::string(cache_dir) + "/" + hex + ".cubin";
-    std::ifstream f(path, std::ios::binary);
-    if (f) image.assign(std::istreambuf_iterator<char>(f), std::istreambuf_iterator<char>());
-  }
+  bool from_cache = false;
+  if (int rc = image_through_cache(src, kernel_name, opts, hex, cache_dir, image, &from_cache, false)) return rc;
   Kernel* k = nullptr;
-  if (!image.empty() && load_cubin(image, kernel_name, &k) != APPY_OK) {
-    image.clear();  // corrupt or stale cache entry: recompile
-    k = nullptr;
-  }
-  if (!k) {
-    if (int rc = nvrtc_build(src, kernel_name, opts, image)) return rc;
+  if (load_cubin(image, kernel_name, &k) != APPY_OK) {
+    if (!from_cache) return APPY_ERR_CUDA;
+    // an entry the driver refuses (or that lacks this kernel): compile afresh and replace it
+    if (int rc = image_through_cache(src, kernel_name, opts, hex, cache_dir, image, &from_cache, true)) return rc;
     if (int rc = load_cubin(image, kernel_name, &k)) return rc;
-    if (!path.empty()) {  // best effort; write to a temp name then rename so readers never see a torn file
-      const std::string tmp = path + ".tmp" + std::to_string((unsigned long long)(uintptr_t)k);
-      std::ofstream f(tmp, std::ios::binary);
-      if (f) {
-        f.write(image.data(), (std::streamsize)image.size());
-        f.close();
-        if (f) std::rename(tmp.c_str(), path.c_str());
-        else std::remove(tmp.c_str());
-      }
-    }
   }
   g_kernels[key] = k;
   *handle = k;
+  return APPY_OK;
+}
+
+int appy_compile_image(const char* src, const char* kernel_name, const char* options, const char* cache_dir,
+                       size_t* cubin_bytes, int* from_cache) {
+  if (!src || !kernel_name) return fail(APPY_ERR_ARG, "appy_compile_image: NULL argument");
+  g_log.clear();
+  std::vector<std::string> opts = nvrtc_options(options);
+  std::lock_guard<std::mutex> lk(g_mu);
+  const std::string hex = compile_key(src, opts);
+  std::vector<char> image;
+  bool cached = false;
+  if (int rc = image_through_cache(src, kernel_name, opts, hex, cache_dir, image, &cached, false)) return rc;
+  if (cubin_bytes) *cubin_bytes = image.size();
+  if (from_cache) *from_cache = cached ? 1 : 0;
   return APPY_OK;
 }
 

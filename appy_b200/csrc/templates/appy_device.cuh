@@ -132,6 +132,16 @@ template <class T> APPY_DEV T appy_shfl(T v, int src, int width) {
   }
 }
 
+template <class T> APPY_DEV T appy_shfl_up(T v, int delta) {
+  if (sizeof(T) == 8) {
+    union { T t; u64 u; } x; x.t = v;
+    x.u = __shfl_up_sync(APPY_FULL_MASK, x.u, delta, 32);
+    return x.t;
+  } else {
+    return __shfl_up_sync(APPY_FULL_MASK, v, delta, 32);
+  }
+}
+
 // all-reduce over a group of G consecutive lanes (G a power of two, 1..32);
 // every lane of the group receives the result.  All 32 lanes of the warp must
 // reach the call (groups never diverge from one another in the templates).
@@ -236,6 +246,18 @@ APPY_DEV double appy_pymod(double a, double b) {
 APPY_DEV float appy_pymod(float a, float b) {
   float r = fmodf(a, b);
   if (r != 0.0f && ((r < 0.0f) != (b < 0.0f))) r += b;
+  return r;
+}
+// float32 division as the reference's Triton backend performs it: div.full.f32 (full range, 2 ulp)
+APPY_DEV float appy_div_full(float a, float b) {
+  float r;
+  asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+// tanh.approx.f32, the instruction behind libdevice's fast_tanhf
+APPY_DEV float appy_tanh_approx(float a) {
+  float r;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(a));
   return r;
 }
 template <class T> APPY_DEV T appy_tmax(T a, T b) { return a > b ? a : b; }

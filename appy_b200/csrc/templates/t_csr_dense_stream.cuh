@@ -12,7 +12,11 @@
 // The grid is one wave of resident CTAs.  The non-zeros of rows [lo, hi) are one contiguous
 // span of the CSR arrays; it is cut into one equal share per warp of the grid, and a warp
 // streams its share from start to end: 32 (coef, brow) pairs per coalesced load (fetched one
-// block ahead), D B-row gathers in flight, the C row in registers.  A warp therefore runs
+// block ahead), the C row in registers, and D B rows in flight at all times: the rows travel by
+// asynchronous 16-byte copies (cp.async) into a ring of D slots in shared memory, one commit group
+// per non-zero; before a row is folded the warp waits for the oldest group, and at once refills
+// the slot with the row D non-zeros ahead.  A lane reads back only the 16 bytes it copied itself,
+// so the ring needs no barrier, and the rows in flight cost no registers.  A warp therefore runs
 // one long, uniform pipeline whatever the row lengths are: a matrix with a few very long rows
 // and many short ones costs the same as a regular one, and no warp idles while a CTA starts
 // up or drains.
@@ -78,7 +82,43 @@ APPY_DEV void appy_sd_row_span(const IdxT* __restrict__ indptr, i64 lo, int row,
   }
 }
 
-// blockDim.x == 32*NWARPS; smem_raw holds NWARPS*32 ints.
+// ---- asynchronous 4/8/16-byte copies global -> shared (cp.async), one group per non-zero ----
+APPY_DEV unsigned appy_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+template <int BYTES> APPY_DEV void appy_cp_async(unsigned saddr, const void* g) {
+  if (BYTES == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(g) : "memory");
+  else if (BYTES == 8) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(saddr), "l"(g) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(saddr), "l"(g) : "memory");
+}
+APPY_DEV void appy_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> APPY_DEV void appy_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+template <class T, int V> APPY_DEV appy_pack<T, V> appy_ld_shared(unsigned saddr) {
+  union { unsigned r[4]; appy_pack<T, V> k; } u;
+  if (sizeof(T) * V == 16)
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(u.r[0]), "=r"(u.r[1]), "=r"(u.r[2]), "=r"(u.r[3]) : "r"(saddr) : "memory");
+  else if (sizeof(T) * V == 8)
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(u.r[0]), "=r"(u.r[1]) : "r"(saddr) : "memory");
+  else
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(u.r[0]) : "r"(saddr) : "memory");
+  return u.k;
+}
+
+// bytes of dynamic shared memory: the warps' rings of D rows, then 32 row numbers per warp
+#define APPY_SD_SMEM_BYTES(nwarps, d, w, esize) ((size_t)(nwarps) * (d) * (w) * (esize) + (size_t)(nwarps) * 32 * 4)
+
+// Copy of B row piece [off + lane*V + t*32*V, +V) for t < T into ring slot `slot` (this lane's own 16 bytes
+// of every 512: a lane later reads back exactly what it copied, so the ring needs no barrier).
+template <int V, int T, int NC, class Body>
+APPY_DEV void appy_sd_fetch(const typename Body::Elt* blane, typename Body::Off off, unsigned slot_addr, int lane,
+                            int ncols) {
+  typedef typename Body::Elt Elt;
+#pragma unroll
+  for (int t = 0; t < T; ++t)
+    if (NC > 0 || (t * 32 + lane) * V < ncols)
+      appy_cp_async<(int)sizeof(Elt) * V>(slot_addr + t * 32 * V * (int)sizeof(Elt), blane + off + t * 32 * V);
+}
+
+// blockDim.x == 32*NWARPS; smem_raw: APPY_SD_SMEM_BYTES(NWARPS, D, 32*V*T, sizeof(Elt)) bytes, 16-byte aligned.
+// D (rows in flight per warp) divides 32 and is at most 16.
 template <int V, int T, int D, int NWARPS, int NC, class IdxT, class Body>
 APPY_DEV void appy_csr_dense_stream(const Body& body, const IdxT* __restrict__ indptr, i64 lo, i64 hi, int ncols,
                                     void* scratch, void* smem_raw) {
@@ -86,7 +126,9 @@ APPY_DEV void appy_csr_dense_stream(const Body& body, const IdxT* __restrict__ i
   typedef typename Body::Off Off;
   const int W = 32 * V * T;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int* s_row = reinterpret_cast<int*>(smem_raw) + warp * 32;
+  // this lane's first element of slot 0 of the warp's ring; slot j is j*W elements further
+  const unsigned ring = appy_smem_addr(reinterpret_cast<Elt*>(smem_raw) + (size_t)warp * D * W + lane * V);
+  int* s_row = reinterpret_cast<int*>(reinterpret_cast<Elt*>(smem_raw) + (size_t)NWARPS * D * W) + warp * 32;
   const i64 workers = (i64)gridDim.x * NWARPS;
   const i64 w = (i64)blockIdx.x * NWARPS + warp;
   const int nrows = (int)(hi - lo);
@@ -95,108 +137,121 @@ APPY_DEV void appy_csr_dense_stream(const Body& body, const IdxT* __restrict__ i
   chunk = (chunk + 31) / 32 * 32;
   const i64 ks = s + w * chunk;
   const int n_tot = (ks >= e) ? 0 : (int)((e - ks < chunk) ? e - ks : chunk);
-  appy_sd_meta meta;
-  meta.head_row = meta.tail_row = -1;
-  meta.head_closed = meta.pad = 0;
-  if (w == 0 && lane == 0) *reinterpret_cast<int*>(scratch) = (int)workers;
-  if (n_tot > 0) {
-    Elt* part = appy_sd_parts<Elt>(scratch, workers) + (size_t)w * 2 * W;
-    const Elt* blane = body.bbase() + lane * V;
-    // the first block's coefficients and offsets travel while the start row is searched
-    Elt nxt_c = Elt(0);
-    Off nxt_off = 0;
-    if (lane < n_tot) {
-      nxt_c = body.coef(ks + lane);
-      nxt_off = body.brow_off(ks + lane);
-    }
-    // row that holds non-zero ks: the largest r with indptr[lo + r] <= ks (32 probes per round)
-    int r0 = 0;
-    {
-      int len = nrows;                       // answer in [r0, r0 + len)
-      while (len > 1) {
-        const int step = (len + 31) / 32;
-        const int probe = r0 + (lane + 1) * step;
-        const bool le = probe < r0 + len && (i64)appy_ldg1(indptr + lo + probe) <= ks;
-        const int c = __popc(__ballot_sync(APPY_FULL_MASK, le));
-        const int end = r0 + len;
-        r0 += c * step;
-        len = (end - r0 < step) ? end - r0 : step;
-      }
-    }
-    int wbase = r0, sr, er;
-    appy_sd_row_span<IdxT>(indptr, lo, wbase + lane, nrows, ks, n_tot + 32, sr, er);
-    bool entered = __shfl_sync(APPY_FULL_MASK, sr, 0) < 0;     // the open row began before ks
-    appy_rowacc<V, T, Body> acc;
-    acc.fill(entered ? Elt(0) : body.init());
-    unsigned ends = 0;
-    int n = 0;
-    for (int kb = 0; kb < n_tot; kb += 32) {
-      n = (n_tot - kb < 32) ? n_tot - kb : 32;
-      const Elt my_c = nxt_c;
-      const Off my_off = nxt_off;
-      if (kb + 32 + lane < n_tot) {          // next block's coefficients and offsets, one block ahead
-        nxt_c = body.coef(ks + kb + 32 + lane);
-        nxt_off = body.brow_off(ks + kb + 32 + lane);
-      }
-      // first gathers of the block go out before the row bookkeeping
-      appy_pack<Elt, V> b[D][T];
+  appy_sd_meta* meta = appy_sd_metas(scratch) + w;     // written by lane 0 only
+  if (lane == 0) {
+    meta->head_row = meta->tail_row = -1;
+    meta->head_closed = 0;
+    if (w == 0) *reinterpret_cast<int*>(scratch) = (int)workers;
+  }
+  if (n_tot <= 0) return;
+  const Elt* blane = body.bbase() + lane * V;
+  // the first two blocks' coefficients and offsets, and the first D rows, travel while the start row is searched
+  Elt my_c = Elt(0), nxt_c = Elt(0);
+  Off my_off = 0, nxt_off = 0;
+  if (lane < n_tot) {
+    nxt_c = body.coef(ks + lane);
+    nxt_off = body.brow_off(ks + lane);
+  }
 #pragma unroll
-      for (int j = 0; j < D; ++j)
-        if (j < n) appy_csr_dense_load<V, T, NC, Body>(blane, appy_shfl<Off>(my_off, j, 32), lane, ncols, b[j]);
-      // rows that end inside [kb, kb + 32): bit of their last non-zero, row number into the table
-      ends = 0;
-      __syncwarp();
-      for (;;) {
-        const bool has = sr < er && er > kb && er <= kb + 32;
-        if (has) s_row[er - 1 - kb] = wbase + lane;
-        ends |= __reduce_or_sync(APPY_FULL_MASK, has ? 1u << (er - 1 - kb) : 0u);
-        if (__shfl_sync(APPY_FULL_MASK, er, 31) > kb + 32) break;   // the window reaches past this block
-        wbase += 32;
-        appy_sd_row_span<IdxT>(indptr, lo, wbase + lane, nrows, ks, n_tot + 32, sr, er);
-      }
-      __syncwarp();
+  for (int j = 0; j < D; ++j) {
+    if (j < n_tot) appy_sd_fetch<V, T, NC, Body>(blane, appy_shfl<Off>(nxt_off, j, 32), ring + j * W * (int)sizeof(Elt), lane, ncols);
+    appy_cp_commit();
+  }
+  // row that holds non-zero ks: the largest r with indptr[lo + r] <= ks (32 probes per round)
+  int wbase = 0;
+  {
+    int len = nrows;                       // answer in [wbase, wbase + len)
+    while (len > 1) {
+      const int step = (len + 31) / 32;
+      const int probe = wbase + (lane + 1) * step;
+      const bool le = probe < wbase + len && (i64)appy_ldg1(indptr + lo + probe) <= ks;
+      const int c = __popc(__ballot_sync(APPY_FULL_MASK, le));
+      const int end = wbase + len;
+      wbase += c * step;
+      len = (end - wbase < step) ? end - wbase : step;
+    }
+  }
+  int sr, er;
+  appy_sd_row_span<IdxT>(indptr, lo, wbase + lane, nrows, ks, n_tot + 32, sr, er);
+  bool entered = __shfl_sync(APPY_FULL_MASK, sr, 0) < 0;     // the open row began before ks
+  appy_rowacc<V, T, Body> acc;
+  acc.fill(entered ? Elt(0) : body.init());
+  unsigned ends = 0;
+  int n = 0;
+  for (int kb = 0; kb < n_tot; kb += 32) {
+    n = (n_tot - kb < 32) ? n_tot - kb : 32;
+    my_c = nxt_c;
+    my_off = nxt_off;
+    if (kb + 32 + lane < n_tot) {          // next block's coefficients and offsets, one block ahead
+      nxt_c = body.coef(ks + kb + 32 + lane);
+      nxt_off = body.brow_off(ks + kb + 32 + lane);
+    }
+    // rows that end inside [kb, kb + 32): bit of their last non-zero, row number into the table
+    // (D rows of this block are in flight already, so this bookkeeping costs no memory time)
+    ends = 0;
+    __syncwarp();
+    for (;;) {
+      const bool has = sr < er && er > kb && er <= kb + 32;
+      if (has) s_row[er - 1 - kb] = wbase + lane;
+      ends |= __reduce_or_sync(APPY_FULL_MASK, has ? 1u << (er - 1 - kb) : 0u);
+      if (__shfl_sync(APPY_FULL_MASK, er, 31) > kb + 32) break;   // the window reaches past this block
+      wbase += 32;
+      appy_sd_row_span<IdxT>(indptr, lo, wbase + lane, nrows, ks, n_tot + 32, sr, er);
+    }
+    __syncwarp();
 #pragma unroll 1
-      for (int q = 0; q < n; q += D) {
-        if (q > 0) {
+    for (int q = 0; q < 32; q += D) {
 #pragma unroll
-          for (int j = 0; j < D; ++j)
-            if (q + j < n) appy_csr_dense_load<V, T, NC, Body>(blane, appy_shfl<Off>(my_off, q + j, 32), lane, ncols, b[j]);
-        }
+      for (int j = 0; j < D; ++j) {
+        if (q + j < n) {
+          appy_cp_wait<D - 1>();             // the oldest of the D groups in flight has landed
+          appy_pack<Elt, V> b[T];
 #pragma unroll
-        for (int j = 0; j < D; ++j) {
-          if (q + j < n) {
-            appy_csr_dense_fma<V, T, Body>(acc, appy_shfl<Elt>(my_c, q + j, 32), b[j]);
-            if ((ends >> (q + j)) & 1u) {
-              const int row = s_row[q + j];
-              if (entered) {     // the row was open when this share began: its piece goes to the head slot
-                appy_csr_dense_park<V, T, Body>(part, lane, acc);
-                meta.head_row = row;
-                meta.head_closed = 1;
-                entered = false;
-              } else {
-                appy_csr_dense_store<V, T, NC, Body>(body, lo + row, lane, ncols, acc);
+          for (int t = 0; t < T; ++t)
+            if (NC > 0 || (t * 32 + lane) * V < ncols)
+              b[t] = appy_ld_shared<Elt, V>(ring + (j * W + t * 32 * V) * (int)sizeof(Elt));
+          appy_csr_dense_fma<V, T, Body>(acc, appy_shfl<Elt>(my_c, q + j, 32), b);
+          if ((ends >> (q + j)) & 1u) {
+            const int row = s_row[q + j];
+            if (entered) {     // the row was open when this share began: its piece goes to the head slot
+              appy_csr_dense_park<V, T, Body>(appy_sd_parts<Elt>(scratch, workers) + (size_t)w * 2 * W, lane, acc);
+              if (lane == 0) {
+                meta->head_row = row;
+                meta->head_closed = 1;
               }
-              acc.fill(body.init());
+              entered = false;
+            } else {
+              appy_csr_dense_store<V, T, NC, Body>(body, lo + row, lane, ncols, acc);
             }
+            acc.fill(body.init());
           }
         }
-      }
-    }
-    if (((ends >> (n - 1)) & 1u) == 0) {
-      // the share ended inside a row: the first row of the window that reaches past the share
-      const unsigned m = __ballot_sync(APPY_FULL_MASK, sr < er && er > n_tot);
-      const int row = wbase + __ffs(m) - 1;
-      if (entered) {
-        appy_csr_dense_park<V, T, Body>(part, lane, acc);
-        meta.head_row = row;
-        meta.head_closed = 0;
-      } else {
-        appy_csr_dense_park<V, T, Body>(part + W, lane, acc);
-        meta.tail_row = row;
+        // refill the slot with the row D non-zeros ahead (from this block's offsets or the next block's)
+        const int ahead = q + j + D;
+        if (kb + ahead < n_tot)
+          appy_sd_fetch<V, T, NC, Body>(blane, appy_shfl<Off>(ahead < 32 ? my_off : nxt_off, ahead & 31, 32),
+                                        ring + j * W * (int)sizeof(Elt), lane, ncols);
+        appy_cp_commit();                    // one group per step, empty or not, keeps the count uniform
       }
     }
   }
-  if (lane == 0) appy_sd_metas(scratch)[w] = meta;
+  appy_cp_wait<0>();
+  if (((ends >> (n - 1)) & 1u) == 0) {
+    // the share ended inside a row: the first row of the window that reaches past the share
+    const unsigned m = __ballot_sync(APPY_FULL_MASK, sr < er && er > n_tot);
+    const int row = wbase + __ffs(m) - 1;
+    Elt* part = appy_sd_parts<Elt>(scratch, workers) + (size_t)w * 2 * W;
+    if (entered) {
+      appy_csr_dense_park<V, T, Body>(part, lane, acc);
+      if (lane == 0) {
+        meta->head_row = row;
+        meta->head_closed = 0;
+      }
+    } else {
+      appy_csr_dense_park<V, T, Body>(part + W, lane, acc);
+      if (lane == 0) meta->tail_row = row;
+    }
+  }
 }
 
 // Second kernel: rows without non-zeros get `init`; every row cut by share boundaries is summed in

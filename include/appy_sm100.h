@@ -93,6 +93,14 @@ int appy_compile(const char* src, const char* kernel_name, const char* options,
  * sources on build machines. */
 int appy_compile_check(const char* src, const char* kernel_name, const char* options,
                        size_t* cubin_bytes);
+/* The cubin of appy_compile without loading it (needs no GPU), through the same on-disk cache:
+ * `from_cache` receives 1 when a valid entry was found.  A cache entry is keyed by SHA-256 of the
+ * source, the options, the contents of every -I directory, the NVRTC version and the target
+ * architecture, and carries its key and length in a header: an entry that is truncated, torn or
+ * belongs to another key is compiled afresh and replaced, never loaded.  (The reference leaves one
+ * /tmp/appy_temp_<uuid>.py per compile and keeps no cache across processes, appy/utils.py:46-80.) */
+int appy_compile_image(const char* src, const char* kernel_name, const char* options,
+                       const char* cache_dir, size_t* cubin_bytes, int* from_cache);
 /* compile log of the last appy_compile on this thread (warnings or errors) */
 const char* appy_compile_log(void);
 /* regs per thread, static shared bytes, max threads per block of a compiled kernel */
@@ -109,6 +117,13 @@ int appy_time_launches(void* handle, unsigned grid, unsigned block, size_t dyn_s
 /* Zero-initialised reduction workspace of the current device for `stream`
  * (ticket + per-CTA partial cells); `bytes` receives its size. */
 int appy_workspace(void* stream, void** dptr, size_t* bytes);
+/* Scratch buffer of at least `bytes` bytes of the current device for kernels queued on `stream`
+ * (grow-only, one per stream, contents undefined).  The two-kernel CSR x dense template keeps
+ * the pieces of rows cut by share boundaries there between its two launches; the reference's
+ * lowering of that loop needs no such buffer because it sends every row through C itself, once
+ * per non-zero (examples/06-spmm.py:4-11 after appy/backends/triton/passes/block_loop.py:77-159).
+ * Growing the buffer waits for the work queued on the stream. */
+int appy_scratch(void* stream, size_t bytes, void** dptr);
 
 /* ---- multi-GPU partitioning (host-side integer work) ------------------- */
 

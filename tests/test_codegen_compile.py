@@ -203,6 +203,36 @@ def test_bulk_copy_variant_of_the_csr_dense_template_compiles():
     assert dyn == 8 * 4 * (plan.info["row_bytes"] + 8) and block == 256
 
 
+def test_streaming_form_of_the_csr_dense_template_is_a_two_kernel_plan():
+    src, scope = CASES["spmm"][0], CASES["spmm"][1]
+    plan, code = build(src, scope)
+    assert plan.post == "kernel_loop_1_fixup" and "appy_csr_dense_stream<4, 1, P_D, P_WARPS, 128" in code
+    assert 'extern "C" __global__ void __launch_bounds__(256) kernel_loop_1_fixup(' in code
+    assert [p.kind for p in plan.params].count("scratch") == 1
+    tun = {k: v[0] for k, v in plan.tunables.items()}
+    assert (tun["P_STREAM"], tun["P_WARPS"], tun["P_D"], tun["P_MINB"]) == (1, 16, 8, 3)
+    grid, block, dyn = plan.launch_config(tun, 1 << 18, 148)
+    assert (grid, block, dyn) == (148 * 3, 512, 16 * 8 * 512 + 16 * 32 * 4)       # one wave; ring + row tables
+    assert plan.post_config(tun, 1 << 18, 148) == (4 * 148, 256)
+    workers = 148 * 3 * 16
+    assert plan.scratch_bytes(tun, 1 << 18, 148) == (16 + 16 * workers + 255) // 256 * 256 + workers * 2 * 512
+    tiled = dict(tun, **plan.info["row_tiled"], P_STREAM=0)
+    assert plan.post_config(tiled, 100, 148) is None and plan.scratch_bytes(tiled, 100, 148) == 0
+    assert plan.launch_config(tiled, 100, 148)[0] == 4                            # a CTA per 32 rows
+    # wide float64 rows: fewer rows in flight per warp, fewer CTAs per SM, same shared-memory budget
+    wide = dict(scope, B=np.ones((10, 200)), y=np.ones((10, 200)), D=np.ones(1000))
+    plan2, _code = build(src, wide)
+    t2 = {k: v[0] for k, v in plan2.tunables.items()}
+    assert plan2.info["row_bytes_padded"] == 2048 and t2["P_WARPS"] * t2["P_D"] * 2048 <= 64 * 1024
+    # small problems keep the row-tiled form
+    vm = dispatcher.build_val_map(src, scope, {"np": np, "math": math})
+    e = cg.CompiledLoop(src, "kernel_loop_1", list(vm), tuple(cg._kind_of(v) for v in vm.values()), {})
+    e.source_for(*[v for v in vm.values() if not isinstance(v, types.ModuleType)])
+    v = list(e.variants.values())[0]
+    assert e._shape_class(v, {}, [], 1000, 0)[1]["P_STREAM"] == 0
+    assert e._shape_class(v, {}, [], 1 << 18, 0)[1] == {}
+
+
 def test_triangular_inner_ranges_are_sized_by_their_mean_length():
     A = np.ones((64, 64), f32)
     src = "#pragma parallel for\nfor i in range(n):\n    #pragma simd\n    for j in range(0, i + 1):\n        C[i, j] = C[i, j] * 2.0"
