@@ -444,7 +444,7 @@ class CompiledLoop:
         if plan.kind == "csrdense" and "P_STREAM" in plan.tunables:
             # The streaming form starts one wave of CTAs and a second kernel whatever the size; below a few
             # thousand rows the row-tiled form (one CTA per 32 rows) is over before that pays.
-            if n_iter < 4096 or n_iter >= 2 ** 31:
+            if n_iter < self.options.get("_stream_rows", 4096) or n_iter >= 2 ** 31:
                 return ("n", bucket, "tiled"), dict(plan.info["row_tiled"], P_STREAM=0)
             return ("n", bucket, "stream"), {}
         if plan.kind == "csr" and plan.info.get("indptr"):
@@ -981,7 +981,8 @@ def _register_finalizer(obj, hptr: int) -> None:
 
 
 _OPTION_KEYS = ("ordered_reduction", "combine", "distribute", "fp_contract", "autotune", "pin_host", "_generic_only", "_vectorize",
-                "_stream_hint", "_hoist_safe", "_shape_spec", "_neighbours", "_bulk_rows", "_group_vectorize")
+                "_stream_hint", "_hoist_safe", "_shape_spec", "_neighbours", "_bulk_rows", "_group_vectorize",
+                "_spmm_stream", "_stream_rows")
 
 
 _site_options: dict = {}       # site number -> option key; the loops of one rewritten function always pass the same options

@@ -629,7 +629,7 @@ class Lowering:
                 em.load_override[text] = (f"appy_side(__rg.{sl}, __rg.{sl}lo, __rg.{sl}hi, __k + ({d}))", arr.ty)
             for n_out, (text, (name, node)) in enumerate(stores.items()):
                 arr = env.arrays[name]
-                o = f"o{n_out}"
+                o = f"__o{n_out}"       # generated names begin with two underscores: users' names cannot
                 out_decl.append(f"appy_pack<{arr.ty.c}, {V}> {o};")
                 em.store_override[text] = (lambda code, t, o=o, ty=arr.ty: [f"{o}.v[__k] = {cast(code, t, ty)};"])
                 off, _ = Emitter(env).offset(_replace_index(node, self.var, "__i0"))
@@ -1071,7 +1071,9 @@ class Lowering:
             d //= 2
         while warps > 2 and warps * d * row_bytes_padded > 64 * 1024:
             warps //= 2
-        minb = 3 if V * Tn <= 8 else 2 if V * Tn <= 16 else 1
+        minb = 2 if (row_bytes_padded <= 512 or V * Tn > 8) else 3      # 128-192 KB of rings per SM
+        if V * Tn > 16:
+            minb = 1
         info["row_tiled"] = {k: v[0] for k, v in tun.items()}       # defaults of the row-tiled form (small inputs)
         info["template"] = "T5 CSR x dense (streaming: non-zeros dealt out to the warps)"
         stun = {"P_STREAM": [1, 0],

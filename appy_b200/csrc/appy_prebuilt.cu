@@ -7,7 +7,7 @@
 #include <cstdint>
 
 #include "../../include/appy_sm100.h"
-#include "templates/t_csr_dense.cuh"
+#include "templates/t_csr_dense_stream.cuh"
 #include "templates/t_csr_rows.cuh"
 #include "templates/t_flat.cuh"
 #include "templates/t_rowdot.cuh"
@@ -216,6 +216,46 @@ int launch_spmm(const SpmmBody<OffT>& body, const int* indptr, i64 lo, i64 hi, i
   return finish_launch("spmm launch");
 }
 
+// Streaming form (t_csr_dense_stream.cuh): one wave of CTAs, every warp an equal share of the non-zeros, D rows
+// of B in flight per warp in a shared-memory ring, and a second kernel for rows cut by share boundaries and
+// rows without non-zeros.  Used from kSpmmStreamRows rows on; below that one CTA per 32 rows is over sooner.
+const int kSpmmStreamRows = 4096;
+
+template <int V, int T, int D, int WARPS, int MINB, int NC, class OffT>
+__global__ void __launch_bounds__(32 * WARPS, MINB)
+k_spmm_stream(SpmmBody<OffT> body, const int* indptr, i64 lo, i64 hi, int ncols, void* scratch) {
+  extern __shared__ __align__(16) unsigned char dyn[];
+  appy_csr_dense_stream<V, T, D, WARPS, NC, int>(body, indptr, lo, hi, ncols, scratch, dyn);
+}
+template <int V, int T, int NC, class OffT>
+__global__ void __launch_bounds__(256)
+k_spmm_fixup(SpmmBody<OffT> body, const int* indptr, i64 lo, i64 hi, int ncols, void* scratch) {
+  appy_csr_dense_fixup<V, T, NC, int>(body, indptr, lo, hi, ncols, scratch);
+}
+
+template <int V, int T, int D, int WARPS, int MINB, int NC, class OffT>
+int launch_spmm_stream(const SpmmBody<OffT>& body, const int* indptr, i64 lo, i64 hi, int ncols, cudaStream_t s) {
+  const int sms = sm_count();
+  const unsigned grid = (unsigned)(sms * MINB);
+  const size_t workers = (size_t)grid * WARPS;
+  void* scratch = nullptr;
+  if (int rc = appy_scratch(s, APPY_SD_SCRATCH_BYTES(workers, 32 * V * T, sizeof(float)), &scratch)) return rc;
+  const size_t dyn = APPY_SD_SMEM_BYTES(WARPS, D, 32 * V * T, sizeof(float));
+  static bool allowed[16] = {false};       // per instantiation and device: raise the dynamic shared-memory limit once
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 16 && !allowed[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(k_spmm_stream<V, T, D, WARPS, MINB, NC, OffT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+    if (e != cudaSuccess) return appy_fail_cuda(e, "cudaFuncSetAttribute(spmm stream)");
+    allowed[dev] = true;
+  }
+  k_spmm_stream<V, T, D, WARPS, MINB, NC, OffT><<<grid, 32 * WARPS, dyn, s>>>(body, indptr, lo, hi, ncols, scratch);
+  if (int rc = finish_launch("spmm stream launch")) return rc;
+  k_spmm_fixup<V, T, NC, OffT><<<(unsigned)(4 * sms), 256, 0, s>>>(body, indptr, lo, hi, ncols, scratch);
+  return finish_launch("spmm fix-up launch");
+}
+
 // ------------------------------------------------------------------ row-length histogram
 template <class IdxT>
 __global__ void k_row_hist(const IdxT* indptr, i64 nrows, u64* counts, u64* max_len) {
@@ -357,6 +397,16 @@ int appy_spmm_csr_f32(const float* ddata, const int32_t* dindptr, const int32_t*
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   SpmmBody<i64> body{ddata, dindices, dB, ldb, dC, ldc};
   const bool vec = aligned16(dB) && aligned16(dC) && ldb % 4 == 0 && ldc % 4 == 0 && ncols % 4 == 0;
+  if (vec && row_hi - row_lo >= kSpmmStreamRows && row_hi - row_lo < (i64)1 << 31) {
+    const int T = (ncols + 127) / 128;
+    if (ncols == 128) return launch_spmm_stream<4, 1, 8, 16, 2, 128, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+    switch (T) {
+      case 1: return launch_spmm_stream<4, 1, 8, 16, 2, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+      case 2: return launch_spmm_stream<4, 2, 8, 8, 3, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+      case 3: return launch_spmm_stream<4, 3, 4, 8, 2, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+      default: return launch_spmm_stream<4, 4, 4, 8, 2, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+    }
+  }
   if (vec) {
     const int T = (ncols + 127) / 128;
     if (ncols == 128) return launch_spmm<4, 1, 4, 3, 128, i64>(body, dindptr, row_lo, row_hi, ncols, s);

@@ -189,6 +189,80 @@ def test_spmm(rt, nrows, ncols_b, avg, cap):
     assert np.all(err <= 1e-5 * scale + 1e-30), float((err / (scale + 1e-30)).max())
 
 
+def _ragged_csr(nrows, ncols, lens, seed):
+    rng = np.random.default_rng(seed)
+    return W.csr_from_lengths(np.asarray(lens, np.int64), ncols, rng)
+
+
+@pytest.mark.parametrize("case", ["zipf", "empty_rows", "one_giant_row", "all_empty", "few_nonzeros", "sub_range"])
+@pytest.mark.parametrize("ncols_b", [128, 96, 256])
+def test_spmm_streaming_form(rt, case, ncols_b):
+    """From 4096 rows on appy_spmm_csr_f32 deals the non-zeros out to the warps of one wave of CTAs and
+    mends the rows cut by share boundaries in a second kernel: rows without non-zeros, a row that spans
+    hundreds of shares, a matrix with fewer non-zeros than warps, and a sub-range of rows."""
+    nrows, ncols_a = 6000, 50000
+    rng = np.random.default_rng(len(case) + ncols_b)
+    if case == "zipf":
+        lens = W.zipf_lengths(nrows, nrows * 24, 5000, rng)
+    elif case == "empty_rows":
+        lens = W.zipf_lengths(nrows, nrows * 8, 2000, rng)
+        lens[rng.random(nrows) < 0.6] = 0
+        lens[:70] = 0                       # a long run of empty rows at the start, and one at the end
+        lens[-45:] = 0
+    elif case == "one_giant_row":
+        lens = np.full(nrows, 3)
+        lens[1234] = 45000                  # spans many warps' shares
+        lens[1235] = 0
+    elif case == "all_empty":
+        lens = np.zeros(nrows, np.int64)
+    elif case == "few_nonzeros":
+        lens = np.zeros(nrows, np.int64)
+        lens[rng.integers(0, nrows, 40)] = 1
+    else:
+        lens = W.zipf_lengths(nrows + 3000, (nrows + 3000) * 12, 3000, rng)
+    A = _ragged_csr(len(lens), ncols_a, lens, 7)
+    B = rng.uniform(-1, 1, (ncols_a, ncols_b)).astype(np.float32)
+    lo, hi = (1500, 1500 + nrows) if case == "sub_range" else (0, len(lens))
+    d = [dev(A.data), dev(A.indptr), dev(A.indices), dev(B)]
+    Cm = torch.full((len(lens), ncols_b), 9.0, dtype=torch.float32, device="cuda")
+    for _ in range(2):                      # the scratch buffer is reused by the second call
+        ok(rt, rt.lib().appy_spmm_csr_f32(ptr(d[0]), ptr(d[1]), ptr(d[2]), ptr(d[3]), ncols_b, ptr(Cm), ncols_b,
+                                          lo, hi, ncols_b, None))
+    torch.cuda.synchronize()
+    got = Cm.cpu().numpy()
+    ref = O.spmm(A.data, A.indptr, A.indices, B)
+    scale = O.spmm_abs(A.data, A.indptr, A.indices, B)
+    err = np.abs(got[lo:hi] - ref[lo:hi])
+    assert np.all(err <= 1e-5 * scale[lo:hi] + 1e-30), float((err / (scale[lo:hi] + 1e-30)).max())
+    assert np.all(got[:lo] == 9.0) and np.all(got[hi:] == 9.0)        # rows outside the range are not touched
+
+
+def test_free_of_a_free_or_mirrored_block_is_refused(rt):
+    p = rt.malloc(4096)
+    rt.free(p)
+    with pytest.raises(rt.AppyRuntimeError, match="already free"):
+        rt.free(p)
+    host = np.ones(1 << 16, np.float32)
+    m, _created = rt.mirror(host.ctypes.data, host.nbytes)
+    with pytest.raises(rt.AppyRuntimeError, match="mirror of a host range"):
+        rt.free(m)
+    rt.check(rt.lib().appy_evict(C.c_void_p(host.ctypes.data)))
+    q = rt.malloc(4096)                       # the cached block comes back, once
+    r = rt.malloc(4096)
+    assert q != r
+    rt.free(q)
+    rt.free(r)
+
+
+def test_scratch_grows_and_is_kept_per_stream(rt):
+    a = rt.scratch(0, 1000)
+    assert rt.scratch(0, 500) == a and rt.scratch(0, 1 << 20) == a      # at least 1 MiB from the start
+    b = rt.scratch(0, 3 << 20)
+    assert rt.scratch(0, 1 << 20) == b
+    s1 = rt.stream(1)
+    assert rt.scratch(s1, 1000) != b
+
+
 def test_row_histogram(rt):
     A, _ = W.spmv(10000, 16, kind="zipf", cap=512, seed=4)
     dptr = dev(A.indptr)

@@ -210,11 +210,11 @@ def test_streaming_form_of_the_csr_dense_template_is_a_two_kernel_plan():
     assert 'extern "C" __global__ void __launch_bounds__(256) kernel_loop_1_fixup(' in code
     assert [p.kind for p in plan.params].count("scratch") == 1
     tun = {k: v[0] for k, v in plan.tunables.items()}
-    assert (tun["P_STREAM"], tun["P_WARPS"], tun["P_D"], tun["P_MINB"]) == (1, 16, 8, 3)
+    assert (tun["P_STREAM"], tun["P_WARPS"], tun["P_D"], tun["P_MINB"]) == (1, 16, 8, 2)
     grid, block, dyn = plan.launch_config(tun, 1 << 18, 148)
-    assert (grid, block, dyn) == (148 * 3, 512, 16 * 8 * 512 + 16 * 32 * 4)       # one wave; ring + row tables
+    assert (grid, block, dyn) == (148 * 2, 512, 16 * 8 * 512 + 16 * 32 * 4)       # one wave; ring + row tables
     assert plan.post_config(tun, 1 << 18, 148) == (4 * 148, 256)
-    workers = 148 * 3 * 16
+    workers = 148 * 2 * 16
     assert plan.scratch_bytes(tun, 1 << 18, 148) == (16 + 16 * workers + 255) // 256 * 256 + workers * 2 * 512
     tiled = dict(tun, **plan.info["row_tiled"], P_STREAM=0)
     assert plan.post_config(tiled, 100, 148) is None and plan.scratch_bytes(tiled, 100, 148) == 0

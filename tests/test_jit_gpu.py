@@ -554,6 +554,40 @@ def test_c5_spmm(fn, nrows, ncols):
     assert np.all(np.abs(y - ref) <= 1e-5 * scale + 1e-30)
 
 
+@appy.jit(_stream_rows=0)
+def k_spmm_streamed(A_data, A_indptr, A_indices, B, y, M):
+    #pragma parallel for
+    for i in range(M):
+        start, end = A_indptr[i], A_indptr[i+1]
+        y[i, :] = 0
+        for k in range(start, end):
+            y[i, :] += A_data[k] * B[A_indices[k], :]
+
+
+@pytest.mark.parametrize("nrows,ncols,dtype,itype", [(3000, 128, np.float32, np.int32), (700, 200, np.float64, np.int64),
+                                                    (300, 33, np.float32, np.int32), (40, 64, np.float32, np.int64),
+                                                    (5000, 512, np.float32, np.int32)])
+def test_c5_spmm_streaming_form_on_small_and_ragged_inputs(nrows, ncols, dtype, itype):
+    """The form used from 4096 rows on (non-zeros dealt out to the warps, second kernel for cut and empty
+    rows), forced here on inputs of any size: more warps than non-zeros, rows cut by many share
+    boundaries, empty rows, column counts that fill no whole 16-byte pack, float64 with int64 indices."""
+    A, B = W.spmm(nrows, 24, 4000, ncols, seed=nrows)
+    rng = np.random.default_rng(nrows)
+    lens = np.diff(A.indptr).astype(np.int64)
+    lens[rng.random(nrows) < 0.3] = 0
+    A = W.csr_from_lengths(lens, nrows, rng)
+    data, B = A.data.astype(dtype), B.astype(dtype)
+    ref = O.spmm(data, A.indptr, A.indices, B)
+    scale = O.spmm_abs(data, A.indptr, A.indices, B)
+    y = np.full((nrows, ncols), np.nan, dtype)
+    k_spmm_streamed(data, A.indptr.astype(itype), A.indices.astype(itype), B, y, nrows)
+    tol = 1e-5 if dtype == np.float32 else 1e-13
+    assert np.all(np.abs(y - ref) <= tol * scale + 1e-30)
+    from appy_b200.backends.cuda_sm100 import codegen as cg
+    entry = [e for e in cg.code_cache.values() if e.kernel_name.startswith("k_spmm_streamed_")][-1]
+    assert entry.last_variant.last_tun["P_STREAM"] == 1 and entry.last_variant.plan.post
+
+
 @pytest.mark.parametrize("density", [0.0001, 0.001, 0.01, 0.1])
 def test_c5_spmm_as_the_reference_example_checks_it(density):
     """The one check the reference holds for this loop (examples/06-spmm.py:30-48): float64
