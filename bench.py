@@ -312,8 +312,10 @@ def spmm(A_data, A_indptr, A_indices, B, y, M):
 
 
 def time_kernel(torch, fn, rot: int, iters: int, warm: int = 3):
-    """Average device time (us) of one call of fn(i), with CUDA events on the current stream."""
-    for i in range(warm):
+    """Average device time (us) of one call of fn(i), with CUDA events on the current stream.
+    Every one of the `rot` rotating input sets is used at least once before the timed calls, so that
+    no first call of a set (launch record, row-length profile, row partition) falls inside them."""
+    for i in range(max(warm, rot)):
         fn(i % rot)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
