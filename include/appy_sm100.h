@@ -198,8 +198,11 @@ int appy_spmm_csr_f32(const float* ddata, const int32_t* dindptr, const int32_t*
 /* ---- allocation-free variant ---------------------------------------------
  * No counterpart in the reference (it has no native code and allocates through torch).
  *
- * Same result as appy_sum_f32(da, n, dresult, 1, stream): *dresult += sum(a[0:n]) with a
- * float64 accumulator and a commit that does not depend on CTA scheduling — but for
+ * The same value as appy_sum_f32(da, n, dresult, 1, stream) up to floating-point association:
+ * *dresult += sum(a[0:n]) with a float64 accumulator and a commit that does not depend on CTA
+ * scheduling, so the result is the same on every run for a given n and alignment of `da`; the
+ * partial sums are formed per 8192-element tile here and per CTA of a persistent grid there, so the
+ * two entry points may differ in the last bits (the test allows rtol 1e-5).  It is meant for
  * callers that must not allocate device memory where they reduce (inside a memory budget
  * fixed by a host application, between a pool allocator's sync points, or where the
  * device-wide synchronisation of a first-use cudaMalloc is unacceptable).  The scratch
@@ -207,8 +210,9 @@ int appy_spmm_csr_f32(const float* ddata, const int32_t* dindptr, const int32_t*
  * library image, present on every GPU that loads the library.
  *   - n may not exceed 134,217,728 elements (16384 tiles) for a 16-byte aligned `da`, a
  *     quarter of that otherwise; longer inputs return APPY_ERR_ARG and launch nothing;
- *   - the first call on a device looks up the array's device address; make it before any
- *     stream capture begins;
+ *   - the first call on a device looks up the array's device address and keeps it; make that
+ *     call before any stream capture begins.  A cudaDeviceReset by the host application makes
+ *     the kept address stale: do not call this entry point again on that device afterwards;
  *   - all calls share the array: calls that can overlap on the GPU race, so keep them
  *     ordered (one stream, or events between streams);
  *   - no cudaMalloc / cudaFree / allocating library routine is called. */
