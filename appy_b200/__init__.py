@@ -119,6 +119,27 @@ def _to_gpu(a):
     raise AssertionError("Unsupported type to transfer to GPU")
 
 
+def resident(*arrays):
+    """Declare NumPy arrays resident: a loop uploads such an array the first time it uses it and then
+    trusts its device copy until ``touch`` says that the host copy was written.  Without this every call
+    uploads every NumPy argument, as the reference's generated host code does
+    (appy/backends/triton/passes/host_passes/gen_data_movement.py:14-96).  Returns its argument(s)."""
+    from .backends.cuda_sm100 import codegen
+    return codegen.resident(*arrays)
+
+
+def touch(*arrays):
+    """The host copies of these resident arrays were modified: upload them again at their next use."""
+    from .backends.cuda_sm100 import codegen
+    codegen.touch(*arrays)
+
+
+def release(*arrays):
+    """Undo ``resident``: the arrays are uploaded on every call again."""
+    from .backends.cuda_sm100 import codegen
+    codegen.release(*arrays)
+
+
 def to_cpu(*args):
     out = [_to_cpu(a) for a in args]
     return out[0] if len(out) == 1 else out

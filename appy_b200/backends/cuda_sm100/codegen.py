@@ -262,7 +262,15 @@ class CompiledLoop:
             if a.nbytes == 0:
                 a.dptr = 0
                 continue
-            a.dptr, _created = rt.mirror(a.hptr, a.nbytes)
+            a.dptr, created = rt.mirror(a.hptr, a.nbytes)
+            state = _resident.get(a.hptr) if (_resident and not slices and a.tmp is None) else None
+            if state is not None and state[0] == a.nbytes:
+                if state[1] and not created:
+                    if state[2] != stream:           # the upload was queued on another stream: let it finish
+                        rt.sync(state[2])
+                        state[2] = stream
+                    continue                         # the mirror holds what the host holds: nothing to move
+                state[1], state[2] = True, stream
             b0, b1 = slices.get(a.name, (0, a.nbytes)) if slices else (0, a.nbytes)
             transfer_stats["h2d"] += max(0, b1 - b0)
             _upload(a.dptr + b0, a.hptr + b0, b1 - b0, a.hptr, a.nbytes, a.obj,
@@ -950,6 +958,54 @@ def to_device(array):
         transfer_stats["h2d"] += h.nbytes
         rt.sync(stream)
     return t
+
+
+# ---- host arrays declared resident: uploaded once, then again only after `touch`
+#
+# The reference's generated host code copies every NumPy argument to the device on every call
+# (host_passes/gen_data_movement.py:14-96), and so does this backend by default: it cannot know whether
+# the caller wrote to the array in between.  `resident(a)` is the caller's promise to say so: the
+# array's device mirror is filled by the next loop that uses it and trusted from then on; `touch(a)`
+# after a host-side write makes the next loop upload it again.  A loop that stores to the array copies
+# it back as always, after which host and mirror agree again.
+_resident: dict = {}        # host pointer -> [bytes, mirror is current, stream of the last upload]
+
+
+def _host_base(a):
+    if not (isinstance(a, np.ndarray) and a.flags.c_contiguous):
+        raise TypeError("resident/touch/release take C-contiguous NumPy arrays")
+    return a.ctypes.data
+
+
+def resident(*arrays):
+    import weakref
+    for a in arrays:
+        p = _host_base(a)
+        if p not in _resident:
+            _resident[p] = [a.nbytes, False, 0]
+            base = a
+            while getattr(base, "base", None) is not None and isinstance(base.base, np.ndarray):
+                base = base.base
+            try:
+                weakref.finalize(base, _resident.pop, p, None)      # the address may be reused once the owner dies
+            except TypeError:
+                pass
+        elif _resident[p][0] != a.nbytes:
+            _resident[p] = [a.nbytes, False, 0]
+    return arrays[0] if len(arrays) == 1 else arrays
+
+
+def touch(*arrays):
+    """The host copies of these arrays were written: the next loop that uses them uploads them again."""
+    for a in arrays:
+        st = _resident.get(_host_base(a))
+        if st is not None:
+            st[1] = False
+
+
+def release(*arrays):
+    for a in arrays:
+        _resident.pop(_host_base(a), None)
 
 
 _finalizers: dict = {}

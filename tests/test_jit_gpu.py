@@ -984,3 +984,46 @@ def test_scalars_that_only_feed_the_arithmetic_share_one_launch_record():
     assert np.array_equal(x.cpu().numpy(), expect)
     entry = [e for e in cg.code_cache.values() if e.kernel_name.startswith("scale_prefix_")][0]
     assert len(entry.memo) == 2                      # m = 1000 and m = 10
+
+
+@appy.jit
+def k_axpy_host(alpha, x, y):
+    #pragma parallel for simd
+    for i in range(x.shape[0]):
+        y[i] = alpha * x[i] + y[i]
+
+
+def test_resident_host_arrays_are_uploaded_once_and_again_after_touch():
+    """`appy.resident(a)`: the array's device mirror is trusted until `appy.touch(a)`; without it every call
+    uploads every NumPy argument (what the reference's generated host code does on every call)."""
+    import ctypes as C
+    from appy_b200.backends.cuda_sm100 import codegen as cg, runtime as rtm
+    n = 1 << 16
+    x = np.arange(n, dtype=np.float32)
+    y = np.ones(n, np.float32)
+    cg.transfer_stats.update(h2d=0, d2h=0)
+    k_axpy_host(2.0, x, y)
+    k_axpy_host(2.0, x, y)
+    assert cg.transfer_stats == {"h2d": 4 * 4 * n, "d2h": 2 * 4 * n}          # both arrays, both calls
+    assert np.array_equal(y, 1 + 4 * x)
+    appy.resident(x, y)
+    cg.transfer_stats.update(h2d=0, d2h=0)
+    k_axpy_host(1.0, x, y)                      # first use after the declaration: uploaded, then trusted
+    k_axpy_host(1.0, x, y)
+    k_axpy_host(1.0, x, y)
+    assert cg.transfer_stats == {"h2d": 2 * 4 * n, "d2h": 3 * 4 * n}          # y still comes back every time
+    assert np.array_equal(y, 1 + 7 * x)
+    x[:] = 1.0                                  # a host write ...
+    appy.touch(x)                               # ... that the caller reports
+    cg.transfer_stats.update(h2d=0, d2h=0)
+    k_axpy_host(1.0, x, y)
+    assert cg.transfer_stats["h2d"] == 4 * n and np.array_equal(y, 2 + 7 * np.arange(n, dtype=np.float32))
+    # a mirror that was dropped in between is filled again without being asked
+    rtm.check(rtm.lib().appy_evict(C.c_void_p(x.ctypes.data)))
+    cg.transfer_stats.update(h2d=0, d2h=0)
+    k_axpy_host(1.0, x, y)
+    assert cg.transfer_stats["h2d"] == 4 * n and np.array_equal(y, 3 + 7 * np.arange(n, dtype=np.float32))
+    appy.release(x, y)
+    cg.transfer_stats.update(h2d=0, d2h=0)
+    k_axpy_host(1.0, x, y)
+    assert cg.transfer_stats["h2d"] == 2 * 4 * n
