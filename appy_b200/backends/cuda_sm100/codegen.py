@@ -787,6 +787,7 @@ class CompiledLoop:
             for a in harr:
                 if a.name in self.stored and a.nbytes:
                     rt.d2h(a.hptr, a.dptr, a.nbytes, stream)
+                    transfer_stats["d2h"] += a.nbytes
             rt.sync(stream)
         return True
 

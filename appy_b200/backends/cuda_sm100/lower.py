@@ -99,7 +99,7 @@ class KernelPlan:
         if k == "csrdense" and tun.get("P_STREAM"):
             # one wave of resident CTAs; every warp of the grid takes an equal share of the non-zeros
             w = tun["P_WARPS"]
-            dyn = w * tun["P_D"] * self.info["row_bytes_padded"] + w * 32 * 4
+            dyn = (w * tun["P_D"] * self.info["row_bytes_padded"] if tun.get("P_RING", 1) else 0) + w * 32 * 4
             return sm_count * tun["P_MINB"], 32 * w, dyn
         if k == "csrdense":
             rows = tun["P_ROWS"]
@@ -1032,7 +1032,7 @@ class Lowering:
             src += ["#if P_STREAM"]
             src += self._kernel_wrapper(
                 params, struct,
-                f"appy_csr_dense_stream<{V}, {Tn}, P_D, P_WARPS, {nc}, {ptr.ty.c}>(__body, {indptr}, __lo, __hi, {ncols}, "
+                f"appy_csr_dense_stream<{V}, {Tn}, P_D, P_WARPS, {nc}, (P_RING != 0), {ptr.ty.c}>(__body, {indptr}, __lo, __hi, {ncols}, "
                 f"__scratch, __dyn);",
                 "extern __shared__ __align__(16) unsigned char __dyn[];", launch_bounds="32 * P_WARPS, P_MINB")
             src += self._kernel_wrapper(
@@ -1080,6 +1080,10 @@ class Lowering:
                 "P_WARPS": [warps] + [w for w in (16, 8, 4) if w != warps],
                 "P_D": [d] + [x for x in (16, 8, 4, 2) if x != d],
                 "P_MINB": [minb] + [x for x in (4, 3, 2, 1) if x != minb],
+                # where the rows in flight wait: 1 = ring in shared memory (cp.async; more rows in flight, best
+                # when most gathers miss L2), 0 = ring in registers (less traffic through the L1/shared-memory
+                # pipe, best when the gathered rows are L2-resident)
+                "P_RING": [1, 0],
                 "P_ROWS": tun["P_ROWS"], "P_ROLL": tun["P_ROLL"]}
         return KernelPlan("csrdense", self.name, "\n".join(src), params, stun, self.lo_expr, self.hi_expr, vec=V,
                           info=info, post=f"{self.name}_fixup")

@@ -225,7 +225,7 @@ template <int V, int T, int D, int WARPS, int MINB, int NC, class OffT>
 __global__ void __launch_bounds__(32 * WARPS, MINB)
 k_spmm_stream(SpmmBody<OffT> body, const int* indptr, i64 lo, i64 hi, int ncols, void* scratch) {
   extern __shared__ __align__(16) unsigned char dyn[];
-  appy_csr_dense_stream<V, T, D, WARPS, NC, int>(body, indptr, lo, hi, ncols, scratch, dyn);
+  appy_csr_dense_stream<V, T, D, WARPS, NC, true, int>(body, indptr, lo, hi, ncols, scratch, dyn);
 }
 template <int V, int T, int NC, class OffT>
 __global__ void __launch_bounds__(256)

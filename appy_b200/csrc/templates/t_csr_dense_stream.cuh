@@ -119,7 +119,12 @@ APPY_DEV void appy_sd_fetch(const typename Body::Elt* blane, typename Body::Off 
 
 // blockDim.x == 32*NWARPS; smem_raw: APPY_SD_SMEM_BYTES(NWARPS, D, 32*V*T, sizeof(Elt)) bytes, 16-byte aligned.
 // D (rows in flight per warp) divides 32 and is at most 16.
-template <int V, int T, int D, int NWARPS, int NC, class IdxT, class Body>
+// SMEM = false keeps the ring in registers instead (plain ld.global.nc into D packs per lane, refilled as
+// they are folded; smem_raw then only holds the NWARPS*32 row numbers): half the traffic through the
+// L1/shared-memory pipe, but the registers bound the rows in flight.  Measured on the 2^18-row, 128-column
+// case: shared-memory ring 404 us whether the gathered rows fit L2 or not; register ring 441 us when they
+// do not (134 MB of rows), 327 us when they do (34 MB).
+template <int V, int T, int D, int NWARPS, int NC, bool SMEM, class IdxT, class Body>
 APPY_DEV void appy_csr_dense_stream(const Body& body, const IdxT* __restrict__ indptr, i64 lo, i64 hi, int ncols,
                                     void* scratch, void* smem_raw) {
   typedef typename Body::Elt Elt;
@@ -127,8 +132,9 @@ APPY_DEV void appy_csr_dense_stream(const Body& body, const IdxT* __restrict__ i
   const int W = 32 * V * T;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // this lane's first element of slot 0 of the warp's ring; slot j is j*W elements further
-  const unsigned ring = appy_smem_addr(reinterpret_cast<Elt*>(smem_raw) + (size_t)warp * D * W + lane * V);
-  int* s_row = reinterpret_cast<int*>(reinterpret_cast<Elt*>(smem_raw) + (size_t)NWARPS * D * W) + warp * 32;
+  const unsigned ring = SMEM ? appy_smem_addr(reinterpret_cast<Elt*>(smem_raw) + (size_t)warp * D * W + lane * V) : 0u;
+  int* s_row = reinterpret_cast<int*>(reinterpret_cast<Elt*>(smem_raw) + (SMEM ? (size_t)NWARPS * D * W : 0)) + warp * 32;
+  appy_pack<Elt, V> rr[SMEM ? 1 : D][T];      // the ring in registers (SMEM == false)
   const i64 workers = (i64)gridDim.x * NWARPS;
   const i64 w = (i64)blockIdx.x * NWARPS + warp;
   const int nrows = (int)(hi - lo);
@@ -154,8 +160,13 @@ APPY_DEV void appy_csr_dense_stream(const Body& body, const IdxT* __restrict__ i
   }
 #pragma unroll
   for (int j = 0; j < D; ++j) {
-    if (j < n_tot) appy_sd_fetch<V, T, NC, Body>(blane, appy_shfl<Off>(nxt_off, j, 32), ring + j * W * (int)sizeof(Elt), lane, ncols);
-    appy_cp_commit();
+    const Off o = appy_shfl<Off>(nxt_off, j, 32);
+    if (SMEM) {
+      if (j < n_tot) appy_sd_fetch<V, T, NC, Body>(blane, o, ring + j * W * (int)sizeof(Elt), lane, ncols);
+      appy_cp_commit();
+    } else if (j < n_tot) {
+      appy_csr_dense_load<V, T, NC, Body>(blane, o, lane, ncols, rr[SMEM ? 0 : j]);
+    }
   }
   // row that holds non-zero ks: the largest r with indptr[lo + r] <= ks (32 probes per round)
   int wbase = 0;
@@ -199,19 +210,31 @@ APPY_DEV void appy_csr_dense_stream(const Body& body, const IdxT* __restrict__ i
       appy_sd_row_span<IdxT>(indptr, lo, wbase + lane, nrows, ks, n_tot + 32, sr, er);
     }
     __syncwarp();
+    if (n == 32 && kb + 32 + D <= n_tot) {
+      // Full block, and every refill of it exists: no position or range checks.  The block's coefficients
+      // and offsets are rotated down by D lanes per group, so that the group's non-zeros sit in lanes
+      // 0..D-1 and the D after them in lanes D..2D-1: every shuffle below has a constant source lane.
+      Elt rc = my_c;
+      Off ro = my_off;
 #pragma unroll 1
-    for (int q = 0; q < 32; q += D) {
+      for (int q = 0; q < 32; q += D) {
+        const unsigned m = (ends >> q) & ((1u << D) - 1u);          // row ends among this group's non-zeros
+        const bool last = q + D == 32;                              // then the refills come from the next block
 #pragma unroll
-      for (int j = 0; j < D; ++j) {
-        if (q + j < n) {
-          appy_cp_wait<D - 1>();             // the oldest of the D groups in flight has landed
+        for (int j = 0; j < D; ++j) {
           appy_pack<Elt, V> b[T];
+          if (SMEM) {
+            appy_cp_wait<D - 1>();           // the oldest of the D groups in flight has landed
 #pragma unroll
-          for (int t = 0; t < T; ++t)
-            if (NC > 0 || (t * 32 + lane) * V < ncols)
-              b[t] = appy_ld_shared<Elt, V>(ring + (j * W + t * 32 * V) * (int)sizeof(Elt));
-          appy_csr_dense_fma<V, T, Body>(acc, appy_shfl<Elt>(my_c, q + j, 32), b);
-          if ((ends >> (q + j)) & 1u) {
+            for (int t = 0; t < T; ++t)
+              if (NC > 0 || (t * 32 + lane) * V < ncols)
+                b[t] = appy_ld_shared<Elt, V>(ring + (j * W + t * 32 * V) * (int)sizeof(Elt));
+          } else {
+#pragma unroll
+            for (int t = 0; t < T; ++t) b[t] = rr[SMEM ? 0 : j][t];
+          }
+          appy_csr_dense_fma<V, T, Body>(acc, appy_shfl<Elt>(rc, j, 32), b);
+          if (m != 0 && ((m >> j) & 1u)) {
             const int row = s_row[q + j];
             if (entered) {     // the row was open when this share began: its piece goes to the head slot
               appy_csr_dense_park<V, T, Body>(appy_sd_parts<Elt>(scratch, workers) + (size_t)w * 2 * W, lane, acc);
@@ -225,17 +248,64 @@ APPY_DEV void appy_csr_dense_stream(const Body& body, const IdxT* __restrict__ i
             }
             acc.fill(body.init());
           }
+          const Off ahead_off = last ? appy_shfl<Off>(nxt_off, j, 32) : appy_shfl<Off>(ro, (j + D) & 31, 32);
+          if (SMEM) {
+            appy_sd_fetch<V, T, NC, Body>(blane, ahead_off, ring + j * W * (int)sizeof(Elt), lane, ncols);
+            appy_cp_commit();
+          } else {
+            appy_csr_dense_load<V, T, NC, Body>(blane, ahead_off, lane, ncols, rr[SMEM ? 0 : j]);
+          }
         }
-        // refill the slot with the row D non-zeros ahead (from this block's offsets or the next block's)
-        const int ahead = q + j + D;
-        if (kb + ahead < n_tot)
-          appy_sd_fetch<V, T, NC, Body>(blane, appy_shfl<Off>(ahead < 32 ? my_off : nxt_off, ahead & 31, 32),
-                                        ring + j * W * (int)sizeof(Elt), lane, ncols);
-        appy_cp_commit();                    // one group per step, empty or not, keeps the count uniform
+        rc = appy_shfl<Elt>(rc, (lane + D) & 31, 32);
+        ro = appy_shfl<Off>(ro, (lane + D) & 31, 32);
+      }
+    } else {
+#pragma unroll 1
+      for (int q = 0; q < 32; q += D) {
+#pragma unroll
+        for (int j = 0; j < D; ++j) {
+          if (q + j < n) {
+            appy_pack<Elt, V> b[T];
+            if (SMEM) {
+              appy_cp_wait<D - 1>();
+#pragma unroll
+              for (int t = 0; t < T; ++t)
+                if (NC > 0 || (t * 32 + lane) * V < ncols)
+                  b[t] = appy_ld_shared<Elt, V>(ring + (j * W + t * 32 * V) * (int)sizeof(Elt));
+            } else {
+#pragma unroll
+              for (int t = 0; t < T; ++t) b[t] = rr[SMEM ? 0 : j][t];
+            }
+            appy_csr_dense_fma<V, T, Body>(acc, appy_shfl<Elt>(my_c, q + j, 32), b);
+            if ((ends >> (q + j)) & 1u) {
+              const int row = s_row[q + j];
+              if (entered) {
+                appy_csr_dense_park<V, T, Body>(appy_sd_parts<Elt>(scratch, workers) + (size_t)w * 2 * W, lane, acc);
+                if (lane == 0) {
+                  meta->head_row = row;
+                  meta->head_closed = 1;
+                }
+                entered = false;
+              } else {
+                appy_csr_dense_store<V, T, NC, Body>(body, lo + row, lane, ncols, acc);
+              }
+              acc.fill(body.init());
+            }
+          }
+          // refill the slot with the row D non-zeros ahead (from this block's offsets or the next block's)
+          const int ahead = q + j + D;
+          const Off o = appy_shfl<Off>(ahead < 32 ? my_off : nxt_off, ahead & 31, 32);
+          if (SMEM) {
+            if (kb + ahead < n_tot) appy_sd_fetch<V, T, NC, Body>(blane, o, ring + j * W * (int)sizeof(Elt), lane, ncols);
+            appy_cp_commit();                  // one group per step, empty or not, keeps the count uniform
+          } else if (kb + ahead < n_tot) {
+            appy_csr_dense_load<V, T, NC, Body>(blane, o, lane, ncols, rr[SMEM ? 0 : j]);
+          }
+        }
       }
     }
   }
-  appy_cp_wait<0>();
+  if (SMEM) appy_cp_wait<0>();
   if (((ends >> (n - 1)) & 1u) == 0) {
     // the share ended inside a row: the first row of the window that reaches past the share
     const unsigned m = __ballot_sync(APPY_FULL_MASK, sr < er && er > n_tot);

@@ -1,7 +1,9 @@
 """A collection of annotated loops of the shapes the reference's integration tests exercise
 (elementwise math, 2-D stencils, triangular inner ranges, running minima over a pivot,
 normalisations with rowwise reductions, masked accumulation, slice expressions, integer
-work).  The formulas are this repository's own.  Each entry: (function, make_args(rng),
+work, pivot loops on the host around column-strided reductions and updates, stores inside a
+reduction loop, diagonal reductions, two reductions of different types per bin, staggered
+neighbour updates in a time loop).  The formulas are this repository's own.  Each entry: (function, make_args(rng),
 numpy_reference, tolerance)."""
 import numpy as np
 
@@ -168,6 +170,127 @@ def running_max_abs_ref(a):
     return np.abs(a).max(), (a * a).min()
 
 
+def orthogonalise_columns(A, w):
+    """Host loop over pivots with NumPy statements between the parallel loops; inside, a parallel loop over
+    the remaining columns with a column-strided reduction followed by a column-strided update."""
+    Q = np.zeros_like(A)
+    R = np.zeros((A.shape[1], A.shape[1]), dtype=A.dtype)
+    for k in range(A.shape[1]):
+        R[k, k] = np.sqrt(np.dot(w * A[:, k], A[:, k]))
+        Q[:, k] = A[:, k] / R[k, k]
+        #pragma parallel for
+        for j in range(k + 1, A.shape[1]):
+            s = 0.0
+            #pragma simd
+            for i in range(A.shape[0]):
+                s += w[i] * Q[i, k] * A[i, j]
+            #pragma simd
+            for i in range(A.shape[0]):
+                A[i, j] -= Q[i, k] * s
+            R[k, j] = s
+    return Q, R
+
+
+def orthogonalise_columns_ref(A, w):
+    Q = np.zeros_like(A)
+    R = np.zeros((A.shape[1], A.shape[1]), dtype=A.dtype)
+    for k in range(A.shape[1]):
+        R[k, k] = np.sqrt(np.dot(w * A[:, k], A[:, k]))
+        Q[:, k] = A[:, k] / R[k, k]
+        for j in range(k + 1, A.shape[1]):
+            s = np.dot(w * Q[:, k], A[:, j])
+            A[:, j] -= Q[:, k] * s
+            R[k, j] = s
+    return Q, R
+
+
+def symmetric_accumulate(alpha, C, A, B, tmp):
+    """Host loop over rows; a parallel loop over columns whose inner simd loop both updates a column of C
+    (a store inside the reduction loop) and accumulates a scalar; a host-side slice statement after it."""
+    for i in range(C.shape[0]):
+        #pragma parallel for
+        for j in range(C.shape[1]):
+            s = 0.0
+            #pragma simd
+            for k in range(i):
+                C[k, j] += alpha * B[i, j] * A[i, k] - 0.25 * A[k, i]
+                s += B[k, j] * A[i, k]
+            tmp[j] = s
+        C[i, :] += alpha * (B[i, :] * A[i, i] + tmp)
+
+
+def symmetric_accumulate_ref(alpha, C, A, B, tmp):
+    for i in range(C.shape[0]):
+        C[:i, :] += alpha * np.outer(A[i, :i], B[i, :]) - 0.25 * A[:i, i:i + 1]
+        tmp[:] = A[i, :i] @ B[:i, :]
+        C[i, :] += alpha * (B[i, :] * A[i, i] + tmp)
+
+
+def diagonal_sum_shift(a):
+    """A shared reduction over the diagonal of a matrix (stride ncols + 1), then a NumPy expression."""
+    acc = 0.0
+    #pragma parallel for simd shared(acc)
+    for i in range(a.shape[0]):
+        acc += np.arctan(a[i, i]) * 0.5
+    return a - acc
+
+
+def diagonal_sum_shift_ref(a):
+    return a - 0.5 * np.arctan(np.diag(a)).sum()
+
+
+def binned_mean(data, radius, nbins, out):
+    """A parallel loop over bins; the inner simd loop carries two reductions of different types under a mask."""
+    top = radius.max() * 1.0000001
+    #pragma parallel for
+    for i in range(nbins):
+        lo = top * i / nbins
+        hi = top * (i + 1) / nbins
+        s, cnt = 0.0, 0
+        #pragma simd
+        for j in range(radius.shape[0]):
+            inside = (lo <= radius[j]) & (radius[j] < hi)
+            s += data[j] * data[j] if inside else 0.0
+            cnt += 1 if inside else 0
+        out[i] = s / max(cnt, 1)
+
+
+def binned_mean_ref(data, radius, nbins, out):
+    top = radius.max() * 1.0000001
+    for i in range(nbins):
+        sel = (top * i / nbins <= radius) & (radius < top * (i + 1) / nbins)
+        out[i] = (data[sel] ** 2).sum() / max(int(sel.sum()), 1)
+
+
+def staggered_fields(T, ex, ey, hz, src):
+    """A time loop with a host-side slice statement and three 2-D loops that read neighbours at -1 and +1."""
+    for t in range(T):
+        ey[0, :] = src[t]
+        #pragma parallel for
+        for i in range(1, ey.shape[0]):
+            #pragma simd
+            for j in range(ey.shape[1]):
+                ey[i, j] -= 0.4 * (hz[i, j] - hz[i - 1, j])
+        #pragma parallel for
+        for i in range(ex.shape[0]):
+            #pragma simd
+            for j in range(1, ex.shape[1]):
+                ex[i, j] -= 0.4 * (hz[i, j] - hz[i, j - 1])
+        #pragma parallel for
+        for i in range(hz.shape[0] - 1):
+            #pragma simd
+            for j in range(hz.shape[1] - 1):
+                hz[i, j] -= 0.6 * (ex[i, j + 1] - ex[i, j] + ey[i + 1, j] - ey[i, j])
+
+
+def staggered_fields_ref(T, ex, ey, hz, src):
+    for t in range(T):
+        ey[0, :] = src[t]
+        ey[1:, :] -= 0.4 * (hz[1:, :] - hz[:-1, :])
+        ex[:, 1:] -= 0.4 * (hz[:, 1:] - hz[:, :-1])
+        hz[:-1, :-1] -= 0.6 * (ex[:-1, 1:] - ex[:-1, :-1] + ey[1:, :-1] - ey[:-1, :-1])
+
+
 def _f(x):
     return np.ascontiguousarray(x)
 
@@ -204,6 +327,21 @@ def cases():
         n = 37
         return (1.5, 1.2, rng.random((n, n)), rng.random(n), rng.random(n), np.zeros(n), rng.random(n), rng.random(n))
     out.append(("axpy_rows_then_matvec", axpy_rows_then_matvec, axpy_rows_then_matvec_ref, mk_ax, (2, 5), 1e-12))
+
+    def mk_sym(rng):
+        m, n = 19, 23
+        return (1.5, rng.random((m, n)), rng.random((m, m)), rng.random((m, n)), np.zeros(n))
+    out.append(("symmetric_accumulate", symmetric_accumulate, symmetric_accumulate_ref, mk_sym, (1, 4), 1e-12))
+
+    def mk_bin(rng):
+        n = 3000
+        return (rng.random(n), rng.random(n) * 7.0, 40, np.zeros(40))
+    out.append(("binned_mean", binned_mean, binned_mean_ref, mk_bin, (3,), 1e-12))
+
+    def mk_stag(rng):
+        nx, ny, T = 31, 45, 4
+        return (T, rng.random((nx, ny)), rng.random((nx, ny)), rng.random((nx, ny)), rng.random(T))
+    out.append(("staggered_fields", staggered_fields, staggered_fields_ref, mk_stag, (1, 2, 3), 1e-12))
 
     def mk_int(rng):
         n = 1000

@@ -216,6 +216,9 @@ def test_streaming_form_of_the_csr_dense_template_is_a_two_kernel_plan():
     assert plan.post_config(tun, 1 << 18, 148) == (4 * 148, 256)
     workers = 148 * 2 * 16
     assert plan.scratch_bytes(tun, 1 << 18, 148) == (16 + 16 * workers + 255) // 256 * 256 + workers * 2 * 512
+    regs = dict(tun, P_RING=0)                  # the ring of rows in flight in registers instead of shared memory
+    rt.compile_check(code, "kernel_loop_1", [f"-D{k}={v}" for k, v in regs.items()] + plan.info["nvrtc"])
+    assert plan.launch_config(regs, 1 << 18, 148)[2] == 16 * 32 * 4
     tiled = dict(tun, **plan.info["row_tiled"], P_STREAM=0)
     assert plan.post_config(tiled, 100, 148) is None and plan.scratch_bytes(tiled, 100, 148) == 0
     assert plan.launch_config(tiled, 100, 148)[0] == 4                            # a CTA per 32 rows

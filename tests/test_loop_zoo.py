@@ -61,6 +61,19 @@ def test_zoo_scalar_results_cpu():
     a = rng.standard_normal(2000)
     m, lo = appy.jit(dry_run=True)(Z.running_max_abs)(a)
     assert (m, lo) == Z.running_max_abs_ref(a)
+    _returned_results(lambda f: appy.jit(dry_run=True)(f), 1e-12)
+
+
+def _returned_results(jit, tol):
+    """Zoo functions that return new arrays instead of writing into their arguments."""
+    rng = np.random.default_rng(11)
+    A, w = rng.random((30, 12)) + 0.5, rng.random(30) + 0.5
+    Q1, R1 = jit(Z.orthogonalise_columns)(A.copy(), w)
+    Q2, R2 = Z.orthogonalise_columns_ref(A.copy(), w)
+    assert np.allclose(Q1, Q2, rtol=tol, atol=tol) and np.allclose(R1, R2, rtol=tol, atol=tol)
+    assert np.allclose((Q1 * w[:, None]).T @ Q1, np.eye(12), atol=1e-9)      # columns orthonormal in the weighted product
+    a = rng.standard_normal((50, 50))
+    assert np.allclose(jit(Z.diagonal_sum_shift)(a), Z.diagonal_sum_shift_ref(a), rtol=tol, atol=tol)
 
 
 @pytest.mark.gpu
@@ -84,3 +97,4 @@ def test_zoo_scalar_results_gpu(rt):
     a = rng.standard_normal(200000)
     m, lo = appy.jit(Z.running_max_abs)(a)
     assert (m, lo) == Z.running_max_abs_ref(a)
+    _returned_results(appy.jit, 1e-10)
