@@ -380,7 +380,25 @@ class CompiledLoop:
             elif p.kind == "seq":
                 from . import multi_gpu
                 vals.append(C.c_uint64(multi_gpu.combiner().next_seq()))
+            elif p.kind == "pend":
+                from . import multi_gpu
+                vals.append(multi_gpu.combiner().pending_struct())
         return rt.ArgPack(vals)
+
+    _P2P_OPS = {"+": 0, "*": 1, "max": 2, "min": 3}
+
+    def _deferred_cells(self, args, arrays):
+        """(address, operator code, type code) of every reduction cell of this loop, for the launch that will
+        collect this one.  The cells must live in device memory: a host cell is read back right after the
+        launch, before anyone has collected it."""
+        out = []
+        for view, op in self._reduction_cells(args, arrays):
+            name = str(view.dtype).replace("torch.", "")
+            ty = {"float32": 0, "float64": 1, "int32": 2, "int64": 3}.get(name)
+            if ty is None or op not in self._P2P_OPS:
+                raise NotImplementedError(f"defer=True: unsupported reduction type {view.dtype} or operator {op!r}")
+            out.append((view.data_ptr(), self._P2P_OPS[op], ty))
+        return out
 
     def _inner_trip(self, plan, scope, lo=0, hi=0):
         """Trip count of the (first) inner simd loop for this call, or None when it is not known on the
@@ -754,7 +772,8 @@ class CompiledLoop:
         return memo is not None and self._replay(memo, args)
 
     def _replay(self, memo, args) -> bool:
-        handle, grid, block, smem, pack, seq_slot, memo_stream, cells, host_slots, scalar_slots, post, scratch = memo
+        (handle, grid, block, smem, pack, seq_slot, memo_stream, cells, host_slots, scalar_slots, post, scratch,
+         deferred) = memo
         torch = sys.modules.get("torch")
         if torch is not None and (self.has_device_args or not host_slots):
             stream = _torch_stream(torch, self.device)      # orders with the producers of the device tensors
@@ -775,7 +794,11 @@ class CompiledLoop:
         if grid:
             if seq_slot is not None:
                 from . import multi_gpu
-                pack.values[seq_slot].value = multi_gpu.combiner().next_seq()
+                comb = multi_gpu.combiner()
+                pack.values[seq_slot].value = comb.next_seq()
+                if deferred is not None:
+                    comb._fill_pending(pack.values[deferred[0]])      # what this launch collects ...
+                    comb.posted(pack.values[seq_slot].value, deferred[1])     # ... and what the next one will
             if scratch is not None:     # the stream's scratch buffer may have been replaced by a larger one
                 pack.values[scratch[0]].value = rt.scratch(stream, scratch[1])
             rt.launch(handle, grid, block, pack, smem, stream)
@@ -855,6 +878,13 @@ class CompiledLoop:
                 rt.launch(post[0], post[1], post[2], pack, 0, stream)
             kinds_ = [p.kind for p in variant.plan.params]
             scratch = (kinds_.index("scratch"), max(need, 1 << 20)) if "scratch" in kinds_ else None
+            deferred = None
+            if "pend" in kinds_:            # split-phase exchange: this launch posted, the next one collects it
+                if any_host and any(a.host and a.name in self.stored for a in arrays):
+                    raise NotImplementedError("defer=True needs the shared(...) cells in device memory "
+                                              "(a host cell is read back before the exchange has completed)")
+                deferred = (kinds_.index("pend"), tuple(self._deferred_cells(args, arrays)))
+                multi_gpu.combiner().posted(pack.values[kinds_.index("seq")].value, deferred[1])
             # Launch record.  With host arrays it is kept when they are contiguous, none of them had to
             # be copied to become so, the stored ones overlap nothing, and the loop does not distribute
             # or combine (those paths look at the arrays again).
@@ -878,9 +908,9 @@ class CompiledLoop:
                                      if self.arg_names[i] in pslot)
                 self.memo[mkey] = (h, grid, block, smem, pack, seq_slot,
                                    stream if (variant.plan.uses_ws or any_host or scratch) else None, cells,
-                                   tuple(host_slots), scalar_slots, post, scratch)
+                                   tuple(host_slots), scalar_slots, post, scratch, deferred)
         elif not any_host and mkey is not None:
-            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells, (), (), None, None)
+            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells, (), (), None, None, None)
         if cells:
             self._post_combine(cells)
         if any_host:
@@ -1037,7 +1067,7 @@ def _register_finalizer(obj, hptr: int) -> None:
         pass
 
 
-_OPTION_KEYS = ("ordered_reduction", "combine", "distribute", "fp_contract", "autotune", "pin_host", "_generic_only", "_vectorize",
+_OPTION_KEYS = ("ordered_reduction", "combine", "defer", "distribute", "fp_contract", "autotune", "pin_host", "_generic_only", "_vectorize",
                 "_stream_hint", "_hoist_safe", "_shape_spec", "_neighbours", "_bulk_rows", "_group_vectorize",
                 "_spmm_stream", "_stream_rows")
 

@@ -301,6 +301,8 @@ class Lowering:
         if uses_ws and self.options.get("combine") == "p2p":
             ps.append(Param("__mb", "mb"))
             ps.append(Param("__seq", "seq", Ty("u", 64)))
+            if self.options.get("defer"):
+                ps.append(Param("__pend", "pend"))       # earlier launches whose totals this kernel collects
         return ps
 
     def _c_param(self, p: Param) -> str:
@@ -317,6 +319,8 @@ class Lowering:
             return "void* __scratch"
         if p.kind == "mb":
             return "const appy_mailbox* __mb"
+        if p.kind == "pend":
+            return "appy_pending2 __pend"
         return f"{p.ty.strong().c} {p.name}"
 
     def _members(self, params) -> list[str]:
@@ -420,6 +424,15 @@ class Lowering:
                 out.append("  if (threadIdx.x < 32) {")
                 bits = ", ".join(f"appy_to_bits<{ty.c}>(__t{r})" for r, (op, ty, acc, _n) in enumerate(items))
                 out.append(f"    u64 __x[{len(items)}] = {{{bits}}};")
+                if self.options.get("defer"):
+                    # split phase: post this launch's totals, collect those of the launches before it; the
+                    # cells of this loop are updated by whoever collects this launch
+                    out.append(f"    appy_p2p_post<{len(items)}>(__mb, __seq, __x);")
+                    out.append("    appy_p2p_collect(__mb, __pend.e[0]);")
+                    out.append("    appy_p2p_collect(__mb, __pend.e[1]);")
+                    out.append("  }")
+                    out.append("}")
+                    return out
                 out.append(f"    const bool __ok = appy_p2p_exchange<{len(items)}>(__mb, __seq, __x);")
                 for r, ((op, ty, acc, _n), addr) in enumerate(zip(items, addrs)):
                     out.append(f"    __t{r} = appy_p2p_fold<{OPS[op]}, {ty.c}>(__mb, __x[{r}]);")

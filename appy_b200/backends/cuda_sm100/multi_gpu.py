@@ -9,6 +9,8 @@ No kernel reads a peer's memory.
 """
 from __future__ import annotations
 
+import ctypes as _C
+
 import numpy as np
 
 from . import runtime as rt
@@ -61,6 +63,16 @@ def all_reduce(values, op: str = "+"):
     return values
 
 
+class Pending(_C.Structure):
+    """One split-phase launch whose totals are still to be collected (struct appy_pending of t_flat.cuh)."""
+    _fields_ = [("seq", _C.c_uint64), ("nv", _C.c_int32), ("pad", _C.c_int32), ("cell", _C.c_void_p * 4),
+                ("op", _C.c_int32 * 4), ("ty", _C.c_int32 * 4)]
+
+
+class Pending2(_C.Structure):
+    _fields_ = [("e", Pending * 2)]
+
+
 class P2PCombiner:
     """Peer mailboxes for the in-kernel combine of ``shared(...)`` scalars
     (``@jit(combine="p2p")``).  Collective to create: every rank of the process group calls
@@ -94,6 +106,7 @@ class P2PCombiner:
         rt.check(rt.lib().appy_p2p_open(self._ctx, blob, spin_limit, C.byref(desc)))
         self.descriptor = desc.value
         self._seq = 0
+        self.pending = []           # split-phase launches not collected yet: (seq, [(cell address, op, dtype)])
         if world_size > 1 and not loopback_world:
             import torch.distributed as dist
             dist.barrier()          # every rank has mapped every mailbox before the first launch
@@ -120,6 +133,42 @@ class P2PCombiner:
             stream = torch.cuda.current_stream().cuda_stream
         rt.check(rt.lib().appy_p2p_combine(self._ctx, self.next_seq(), self._OPS[op], dt,
                                            C.c_void_p(values.data_ptr()), values.numel(), C.c_void_p(stream)))
+
+    # ---- split-phase exchange (`@jit(combine="p2p", defer=True)`)
+    def pending_struct(self):
+        """The launches still to be collected, marshalled as the kernels and appy_p2p_flush take them."""
+        return self._fill_pending(Pending2())
+
+    def _fill_pending(self, out):
+        assert len(self.pending) <= 2
+        for k in range(2):
+            e = out.e[k]
+            if k < len(self.pending):
+                seq, cells = self.pending[k]
+                e.seq, e.nv = seq, len(cells)
+                for v, (ptr, op, ty) in enumerate(cells):
+                    e.cell[v], e.op[v], e.ty[v] = ptr, op, ty
+            else:
+                e.seq, e.nv = 0, 0
+        return out
+
+    def posted(self, seq: int, cells) -> None:
+        """A kernel that collects `self.pending` and posts launch `seq` has been queued."""
+        self.pending = [(seq, list(cells))]
+
+    def flush(self, stream: int | None = None) -> None:
+        """Collect the totals of split-phase launches that no later kernel has collected; afterwards the
+        shared(...) cells of every loop launched so far hold their final values (once the stream has run).
+        Collective: every rank calls it at the same point of its launch sequence."""
+        import ctypes as C
+        if not self.pending:
+            return
+        if stream is None:
+            import torch
+            stream = torch.cuda.current_stream().cuda_stream
+        p = self.pending_struct()
+        rt.check(rt.lib().appy_p2p_flush(self._ctx, C.byref(p), C.c_void_p(stream)))
+        self.pending = []
 
     def timed_out(self) -> bool:
         import ctypes as C

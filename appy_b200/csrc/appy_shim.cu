@@ -855,9 +855,10 @@ int appy_p2p_create(int world, int rank, void** ctx, void* ipc_handle_out) {
   P2PContext* c = new P2PContext;
   c->world = world;
   c->rank = rank;
-  const size_t bytes = (size_t)2 * world * 8 * sizeof(unsigned long long);
-  cudaError_t e = cudaMalloc(&c->local, bytes < 4096 ? 4096 : bytes);
-  if (e == cudaSuccess) e = cudaMemset(c->local, 0, bytes < 4096 ? 4096 : bytes);
+  // [0, 4096): the two slots of the immediate exchange; from 4096: the ring of the split-phase exchange
+  const size_t bytes = 4096 + (size_t)APPY_MB_RING * world * 8 * sizeof(unsigned long long);
+  cudaError_t e = cudaMalloc(&c->local, bytes);
+  if (e == cudaSuccess) e = cudaMemset(c->local, 0, bytes);
   if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&c->d_err), 256);
   if (e == cudaSuccess) e = cudaMemset(c->d_err, 0, 256);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_desc, sizeof(MailboxDesc));
@@ -951,6 +952,34 @@ int appy_p2p_combine(void* ctx, uint64_t seq, int op, int dtype, void* dvalues, 
     default: return fail(APPY_ERR_ARG, "appy_p2p_combine: unknown dtype %d", dtype);
   }
   if (e != cudaSuccess) return fail(APPY_ERR_CUDA, "appy_p2p_combine launch failed: %s", cudaGetErrorString(e));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return APPY_OK;
+}
+
+}  // extern "C"
+
+namespace {
+// One warp: collect the totals of up to two earlier launches that only posted them (split-phase exchange).
+__global__ void __launch_bounds__(32) k_p2p_flush(const appy_mailbox* mb, appy_pending2 pend) {
+  appy_p2p_collect(mb, pend.e[0]);
+  appy_p2p_collect(mb, pend.e[1]);
+}
+}  // namespace
+
+extern "C" {
+
+int appy_p2p_flush(void* ctx, const void* pending, void* stream) {
+  if (!ctx || !pending) return fail(APPY_ERR_ARG, "appy_p2p_flush: NULL argument");
+  P2PContext* c = static_cast<P2PContext*>(ctx);
+  if (!c->opened) return fail(APPY_ERR_ARG, "appy_p2p_flush: appy_p2p_open has not been called");
+  appy_pending2 pend;
+  memcpy(&pend, pending, sizeof pend);
+  for (int k = 0; k < 2; ++k)
+    if (pend.e[k].seq != 0 && (pend.e[k].nv < 1 || pend.e[k].nv > 4))
+      return fail(APPY_ERR_ARG, "appy_p2p_flush: a pending launch must carry 1..4 variables");
+  k_p2p_flush<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const appy_mailbox*>(c->d_desc), pend);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(APPY_ERR_CUDA, "appy_p2p_flush launch failed: %s", cudaGetErrorString(e));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return APPY_OK;
 }

@@ -222,3 +222,112 @@ template <class Op, class T> APPY_DEV T appy_p2p_fold(const appy_mailbox* mb, u6
     total = Op::template op<T>(total, appy_from_bits<T>(__shfl_sync(0xffffffffu, bits, r)));
   return total;
 }
+
+// ---------------------------------------------------------------------------
+// Split-phase form of the exchange (`@jit(combine="p2p", defer=True)`).
+//
+// The exchange above makes every reduction kernel wait, in its tail, for the slowest rank and for one
+// NVLink round trip.  Here a kernel only POSTS its totals (stores into every rank's mailbox, its own
+// included) and leaves the shared(...) cells alone; the totals are COLLECTED one launch later, in the tail
+// of the next such kernel (or by the stand-alone flush kernel): by then the words have long arrived, so
+// the poll finds them at once, and the latency and the ranks' end-of-kernel skew hide behind that kernel's
+// own work.  The cells hold their final value once the collecting kernel has finished.
+//
+// Posted words live in a ring of APPY_MB_RING slots per mailbox, indexed by the launch number, at byte
+// offset 4096 (after the two slots of the immediate exchange).  A rank collects launch s before it posts
+// launch s + 2 at the latest, and collecting s needs every rank's words of s, so no rank runs more than two
+// launches ahead of the slowest one and a slot is never overwritten before every rank has read it.
+// A collect is described by values alone (cell addresses, operator and type codes), because the kernel
+// that collects was generated for another loop than the one that posted.
+// ---------------------------------------------------------------------------
+#define APPY_MB_RING 8
+enum { APPY_PEND_ADD = 0, APPY_PEND_MUL = 1, APPY_PEND_MAX = 2, APPY_PEND_MIN = 3 };
+enum { APPY_PEND_F32 = 0, APPY_PEND_F64 = 1, APPY_PEND_I32 = 2, APPY_PEND_I64 = 3 };
+
+struct appy_pending {      // one earlier launch whose totals are still to be collected; seq == 0: none
+  u64 seq;
+  int nv;                  // variables of that launch (1..4)
+  int pad;
+  void* cell[4];           // the shared(...) cells, in this GPU's memory
+  int op[4];               // APPY_PEND_ADD ..
+  int ty[4];               // APPY_PEND_F32 ..
+};
+struct appy_pending2 { appy_pending e[2]; };
+
+APPY_DEV u64* appy_mb_ring_words(u64* mailbox, u64 seq, int world, int src) {
+  return mailbox + 512 + ((seq % APPY_MB_RING) * (u64)world + src) * 8;
+}
+
+template <class T> APPY_DEV T appy_fold_any(int op, T a, T b) {
+  if (op == APPY_PEND_ADD) return a + b;
+  if (op == APPY_PEND_MUL) return a * b;
+  if (op == APPY_PEND_MAX) return a > b ? a : b;
+  return a < b ? a : b;
+}
+APPY_DEV u64 appy_fold_bits(int op, int ty, u64 a, u64 b) {
+  if (ty == APPY_PEND_F32) return appy_to_bits<float>(appy_fold_any<float>(op, appy_from_bits<float>(a), appy_from_bits<float>(b)));
+  if (ty == APPY_PEND_F64) return appy_to_bits<double>(appy_fold_any<double>(op, appy_from_bits<double>(a), appy_from_bits<double>(b)));
+  if (ty == APPY_PEND_I32) return appy_to_bits<int>(appy_fold_any<int>(op, appy_from_bits<int>(a), appy_from_bits<int>(b)));
+  return appy_to_bits<i64>(appy_fold_any<i64>(op, appy_from_bits<i64>(a), appy_from_bits<i64>(b)));
+}
+
+// Called by the 32 threads of warp 0: lane r stores this rank's totals of launch `seq` into rank r's ring.
+template <int NV> APPY_DEV void appy_p2p_post(const appy_mailbox* mb, u64 seq, const u64 (&x)[NV]) {
+  const int lane = threadIdx.x & 31;
+  if (lane < mb->world) {
+    const u64 tag = (u64)((unsigned)seq | 0x80000000u) << 32;
+    u64* dst = appy_mb_ring_words(mb->peer[lane], seq, mb->world, mb->rank);
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      appy_st_relaxed_sys(dst + 2 * v, tag | (x[v] & 0xffffffffull));
+      appy_st_relaxed_sys(dst + 2 * v + 1, tag | (x[v] >> 32));
+    }
+  }
+}
+
+// Called by the 32 threads of warp 0: waits (bounded) for every rank's words of launch p.seq in this rank's
+// own mailbox, folds them in rank order and applies the result to the cells.  A wait that runs out sets the
+// error word and turns floating-point results into NaN, as in the immediate exchange.
+APPY_DEV void appy_p2p_collect(const appy_mailbox* mb, const appy_pending& p) {
+  if (p.seq == 0) return;
+  const int world = mb->world, lane = threadIdx.x & 31;
+  const u64 tag = (u64)((unsigned)p.seq | 0x80000000u) << 32;
+  const u64* src = appy_mb_ring_words(mb->peer[mb->rank], p.seq, world, lane < world ? lane : 0);
+  const unsigned limit = mb->spin_limit;
+  unsigned spins = 0;
+  bool ok = true;
+  for (int v = 0; v < p.nv; ++v) {
+    u64 lo = 0, hi = 0;
+    if (lane < world) {
+      for (;;) {
+        lo = appy_ld_relaxed_sys(src + 2 * v);
+        hi = appy_ld_relaxed_sys(src + 2 * v + 1);
+        if (((lo ^ tag) >> 32) == 0 && ((hi ^ tag) >> 32) == 0) break;
+        if (!ok || ++spins > limit) {
+          ok = false;
+          break;
+        }
+        __nanosleep(spins < 256 ? 20 : 1000);
+      }
+    }
+    const bool all_ok = __all_sync(0xffffffffu, ok) != 0;
+    const u64 mine = (hi << 32) | (lo & 0xffffffffull);
+    u64 total = __shfl_sync(0xffffffffu, mine, 0);
+    for (int r = 1; r < world; ++r) total = appy_fold_bits(p.op[v], p.ty[v], total, __shfl_sync(0xffffffffu, mine, r));
+    if (lane == 0) {
+      const int ty = p.ty[v];
+      if (!all_ok) {
+        atomicExch(mb->err, 1u);
+        if (ty == APPY_PEND_F32) total = appy_to_bits<float>(appy_p2p_poison<float>(0.f));
+        if (ty == APPY_PEND_F64) total = appy_to_bits<double>(appy_p2p_poison<double>(0.0));
+      }
+      if (ty == APPY_PEND_F32 || ty == APPY_PEND_I32) {
+        unsigned* c = reinterpret_cast<unsigned*>(p.cell[v]);
+        *c = (unsigned)appy_fold_bits(p.op[v], ty, (u64)*c, total);
+      } else {
+        u64* c = reinterpret_cast<u64*>(p.cell[v]);
+        *c = appy_fold_bits(p.op[v], ty, *c, total);
+      }
+    }
+  }
+}

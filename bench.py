@@ -200,6 +200,18 @@ def masked_sum_into_p2p(a, mask, out):
     for i in range(a.shape[0]):
         out[0] += a[i] if mask[i] else 0.0
 
+@appy.jit(combine="p2p", defer=True)
+def sum_into_split(a, out):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        out[0] += a[i]
+
+@appy.jit(combine="p2p", defer=True)
+def masked_sum_into_split(a, mask, out):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        out[0] += a[i] if mask[i] else 0.0
+
 @appy.jit(distribute=True)
 def d_vec_add(a, b, c):
     #pragma parallel for simd
@@ -676,7 +688,7 @@ def main():
                     help="run a single configuration's kernel --steps times and exit (for profilers): "
                          "vec_add, sum, masked_sum, gemv, spmv_poisson, spmv_zipf, spmm")
     ap.add_argument("--scale", type=int, default=1, help="with --only: divide the problem size by this factor")
-    ap.add_argument("--combine", default="p2p", choices=["nccl", "p2p"],
+    ap.add_argument("--combine", default="p2p", choices=["nccl", "p2p", "p2p-immediate"],
                     help="N > 1: how the two result scalars are combined across GPUs: peer mailboxes inside "
                          "the reduction kernels (no collective call; falls back to NCCL when peer mappings "
                          "cannot be made), or an NCCL all-reduce per step")
@@ -717,7 +729,7 @@ def main():
     # launch stream.  (Overlapping it with the next step's kernels through a second buffer was
     # measured slower: the reduction kernels occupy every SM, so the NCCL kernel waits for them anyway.)
     outs = [out]
-    use_p2p = world > 1 and args.combine == "p2p"
+    use_p2p = world > 1 and args.combine in ("p2p", "p2p-immediate")
     if use_p2p:
         from appy_b200.backends.cuda_sm100 import multi_gpu as mg
         try:
@@ -730,9 +742,15 @@ def main():
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)       # every rank takes the same path
         use_p2p = bool(flag.item())
 
+    split = use_p2p and args.combine == "p2p"       # split-phase: post in this kernel, collect in the next
+
     def step():
-        out.zero_()
-        if use_p2p:
+        # the two result cells accumulate over the steps (`out[0] += a[i]`); they are zeroed before the timed
+        # region and checked against steps x the per-step totals after it
+        if split:
+            L.sum_into_split(a, out_a)
+            L.masked_sum_into_split(a, m, out_b)
+        elif use_p2p:
             L.sum_into_p2p(a, out_a)
             L.masked_sum_into_p2p(a, m, out_b)
         else:
@@ -742,7 +760,8 @@ def main():
                 dist.all_reduce(out)
 
     def drain():
-        pass
+        if split:
+            combiner.flush()        # the last launch's totals: collected inside the timed region
 
     for _ in range(args.warmup):
         step()
@@ -760,6 +779,7 @@ def main():
     sampler.start()
     for _ in range(20):                         # clocks under load before the region, as during it
         step()
+    drain()                                     # nothing of the warm-up steps is left to collect
     out.zero_()
     if world > 1:
         dist.barrier()
@@ -778,15 +798,15 @@ def main():
         dist.barrier()
     ms = e0.elapsed_time(e1)
     launches = rt.launch_count() - launches0
-    # every rank's last buffers hold the all-reduced sums of the last two steps
+    # every rank's cells hold the sums of all ranks, accumulated over the timed steps
     if world > 1:
         tot = torch.tensor(ref, dtype=torch.float64, device="cuda")
         dist.all_reduce(tot)
         for buf in outs:
-            assert np.allclose(buf.cpu().numpy(), tot.cpu().numpy(), rtol=1e-5, atol=0), (buf, tot)
+            assert np.allclose(buf.cpu().numpy(), args.steps * tot.cpu().numpy(), rtol=1e-5, atol=0), (buf, tot)
     else:
         for buf in outs:
-            assert np.allclose(buf.cpu().numpy(), ref, rtol=1e-5, atol=0), (buf, ref)
+            assert np.allclose(buf.cpu().numpy(), args.steps * np.asarray(ref), rtol=1e-5, atol=0), (buf, ref)
     if use_p2p:
         assert not combiner.timed_out(), "a peer-mailbox wait ran out"
     t = torch.tensor([ms], dtype=torch.float64, device="cuda")
@@ -940,6 +960,8 @@ def main():
                        "l2": "inputs larger than L2 (256 MiB + 64 MiB read per step)",
                        "accumulate": "float64 (the shared scalar is a float64 cell, as in the reference)",
                        "collective": ("none" if world == 1 else
+                                      "peer mailboxes, split phase: every reduction kernel posts its totals with P2P "
+                                      "stores over NVLink and collects those of the kernel before it" if split else
                                       "peer mailboxes inside the reduction kernels (P2P stores over NVLink)" if use_p2p
                                       else "NCCL all-reduce of the two result scalars per step")},
             "roofline": {"bound": "hbm", "kernel": dom_name, "achieved": round(achieved, 1), "peak": peak,

@@ -192,6 +192,17 @@ def test_shared_reduction_with_inner_simd_loops_uses_the_group_lowering():
     assert plan.uses_ws and "appy_ws_arrive" in code
 
 
+def test_split_phase_exchange_compiles():
+    src = "#pragma parallel for simd\nfor i in range(n):\n    s[0] += a[i]\n    m[0] = max(m[0], a[i])"
+    scope = dict(a=A1, s=np.array([0.0]), m=np.array([0.0], f32), n=1000)
+    plan, code = build(src, scope, combine="p2p", defer=True)
+    assert [p.kind for p in plan.params][-3:] == ["mb", "seq", "pend"]
+    assert "appy_p2p_post<2>(__mb, __seq, __x);" in code and "appy_p2p_collect(__mb, __pend.e[1]);" in code
+    assert "appy_p2p_exchange" not in code.split("struct kernel_loop_1_body")[1]
+    plan, code = build(src, scope, combine="p2p")
+    assert "appy_p2p_exchange<2>" in code and "pend" not in [p.kind for p in plan.params]
+
+
 def test_bulk_copy_variant_of_the_csr_dense_template_compiles():
     spmm = CASES["spmm"] if "spmm" in CASES else None
     assert spmm is not None

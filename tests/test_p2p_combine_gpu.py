@@ -87,6 +87,75 @@ def test_standalone_combine_of_prebuilt_kernel_results_one_rank(rt):
         mg.set_combiner(None)
 
 
+@appy.jit(combine="p2p", defer=True)
+def sum_and_max_into(a, out_s, out_m):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        out_s[0] += a[i]
+        out_m[0] = max(out_m[0], a[i])
+
+
+@appy.jit(combine="p2p", defer=True)
+def count_into(a, out_n):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        out_n[0] += 1 if a[i] > 0.5 else 0
+
+
+def test_split_phase_exchange_on_one_rank(rt):
+    """defer=True: a kernel posts its totals and collects those of the launch before it; the cells are final
+    once the next such kernel, or flush(), has run."""
+    mg.set_combiner(None)
+    c = mg.enable_p2p()
+    try:
+        a = W.vec_sum((1 << 20) + 5, seed=9)
+        da = torch.from_numpy(a).cuda()
+        s = torch.full((1,), 2.0, dtype=torch.float64, device="cuda")
+        m = torch.full((1,), -1.0, dtype=torch.float32, device="cuda")
+        n = torch.zeros(1, dtype=torch.int64, device="cuda")
+        sum_and_max_into(da, s, m)
+        torch.cuda.synchronize()
+        assert s.item() == 2.0 and m.item() == -1.0 and len(c.pending) == 1       # posted, not collected yet
+        count_into(da, n)                       # collects the launch before it, posts its own
+        torch.cuda.synchronize()
+        assert np.isclose(s.item(), 2.0 + float(np.sum(a, dtype=np.float64)), rtol=1e-5) and m.item() == float(a.max())
+        assert n.item() == 0 and len(c.pending) == 1
+        c.flush()
+        torch.cuda.synchronize()
+        assert n.item() == int((a > 0.5).sum()) and c.pending == []
+        for _ in range(12):                     # more launches than the ring has slots
+            sum_and_max_into(da, s, m)
+            count_into(da, n)
+        c.flush()
+        torch.cuda.synchronize()
+        assert np.isclose(s.item(), 2.0 + 13 * float(np.sum(a, dtype=np.float64)), rtol=1e-5)
+        assert n.item() == 13 * int((a > 0.5).sum()) and not c.timed_out()
+        with pytest.raises(NotImplementedError, match="device memory"):
+            sum_and_max_into(a, np.zeros(1), np.zeros(1, np.float32))      # host cells cannot be deferred
+    finally:
+        c.close()
+        mg.set_combiner(None)
+
+
+def test_split_phase_collect_times_out_with_a_status(rt):
+    c = mg.P2PCombiner(spin_limit=100_000, loopback_world=2)
+    mg.set_combiner(c)
+    try:
+        da = torch.from_numpy(W.vec_sum(1 << 16, seed=5)).cuda()
+        s = torch.zeros(1, dtype=torch.float64, device="cuda")
+        m = torch.zeros(1, dtype=torch.float32, device="cuda")
+        sum_and_max_into(da, s, m)              # posts only: nothing to wait for
+        torch.cuda.synchronize()
+        assert not c.timed_out()
+        c.flush()                               # rank 1 never posts: the bounded wait runs out
+        torch.cuda.synchronize()
+        assert np.isnan(s.item()) and np.isnan(m.item()) and c.timed_out()
+        assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0            # the context is still usable
+    finally:
+        c.close()
+        mg.set_combiner(None)
+
+
 @appy.jit(distribute=True)
 def d_vec_add(a, b, c):
     #pragma parallel for simd
@@ -184,6 +253,18 @@ def _rank_main(rank, world, port, out_dir):
         comb.combine(part[1:2], "max")
         torch.cuda.synchronize()
         assert np.isclose(part[0].item(), total, rtol=1e-5, atol=0) and part[1].item() == float(world)
+        assert not comb.timed_out()
+        # ---- split-phase exchange: every rank ends with the world's totals after the collecting launch
+        sd = torch.zeros(1, dtype=torch.float64, device="cuda")
+        md = torch.full((1,), -1.0, dtype=torch.float32, device="cuda")
+        nd = torch.zeros(1, dtype=torch.int64, device="cuda")
+        for _ in range(5):
+            sum_and_max_into(da, sd, md)
+            count_into(da, nd)
+        comb.flush()
+        torch.cuda.synchronize()
+        cnt = sum(int((W.vec_sum(1 << 20, seed=100 + r) > 0.5).sum()) for r in range(world))
+        assert np.isclose(sd.item(), 5 * total, rtol=1e-5, atol=0) and md.item() == big and nd.item() == 5 * cnt
         assert not comb.timed_out()
         # ---- the iteration space split over the ranks (`distribute=True`), replicated inputs
         x, y = W.vec_add(100003, seed=7)
