@@ -320,7 +320,7 @@ class Lowering:
         if p.kind == "mb":
             return "const appy_mailbox* __mb"
         if p.kind == "pend":
-            return "appy_pending2 __pend"
+            return "appy_pending __pend"
         return f"{p.ty.strong().c} {p.name}"
 
     def _members(self, params) -> list[str]:
@@ -416,6 +416,12 @@ class Lowering:
             for r, (op, ty, acc, _n) in enumerate(items):
                 out.append(f"appy_ws_publish<{ty.c}>(__w, {r}, {acc});")
             out.append("if (appy_ws_arrive(__w, __smem)) {")
+            defer = self.options.get("combine") == "p2p" and self.options.get("defer")
+            if defer:
+                # split phase: the reads that the collect of the previous launch needs go out first, so that
+                # their latency hides behind the fold of this kernel's own partials
+                out.append("  appy_mb_view __mv; appy_collect_regs __cr;")
+                out.append("  if (threadIdx.x < 32) { __mv = appy_mb_open(__mb); appy_p2p_collect_begin(__mv, __pend, __cr); }")
             if self.options.get("combine") == "p2p":
                 # this GPU's totals, then the exchange with the other ranks inside the same kernel
                 for r, (op, ty, acc, _n) in enumerate(items):
@@ -427,9 +433,8 @@ class Lowering:
                 if self.options.get("defer"):
                     # split phase: post this launch's totals, collect those of the launches before it; the
                     # cells of this loop are updated by whoever collects this launch
-                    out.append(f"    appy_p2p_post<{len(items)}>(__mb, __seq, __x);")
-                    out.append("    appy_p2p_collect(__mb, __pend.e[0]);")
-                    out.append("    appy_p2p_collect(__mb, __pend.e[1]);")
+                    out.append(f"    appy_p2p_post<{len(items)}>(__mv, __seq, __x);")
+                    out.append("    appy_p2p_collect_end(__mv, __pend, __cr);")
                     out.append("  }")
                     out.append("}")
                     return out

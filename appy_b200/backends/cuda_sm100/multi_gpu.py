@@ -69,10 +69,6 @@ class Pending(_C.Structure):
                 ("op", _C.c_int32 * 4), ("ty", _C.c_int32 * 4)]
 
 
-class Pending2(_C.Structure):
-    _fields_ = [("e", Pending * 2)]
-
-
 class P2PCombiner:
     """Peer mailboxes for the in-kernel combine of ``shared(...)`` scalars
     (``@jit(combine="p2p")``).  Collective to create: every rank of the process group calls
@@ -136,21 +132,18 @@ class P2PCombiner:
 
     # ---- split-phase exchange (`@jit(combine="p2p", defer=True)`)
     def pending_struct(self):
-        """The launches still to be collected, marshalled as the kernels and appy_p2p_flush take them."""
-        return self._fill_pending(Pending2())
+        """The launch still to be collected, marshalled as the kernels and appy_p2p_flush take it."""
+        return self._fill_pending(Pending())
 
-    def _fill_pending(self, out):
-        assert len(self.pending) <= 2
-        for k in range(2):
-            e = out.e[k]
-            if k < len(self.pending):
-                seq, cells = self.pending[k]
-                e.seq, e.nv = seq, len(cells)
-                for v, (ptr, op, ty) in enumerate(cells):
-                    e.cell[v], e.op[v], e.ty[v] = ptr, op, ty
-            else:
-                e.seq, e.nv = 0, 0
-        return out
+    def _fill_pending(self, e):
+        if self.pending:
+            seq, cells = self.pending[0]
+            e.seq, e.nv = seq, len(cells)
+            for v, (ptr, op, ty) in enumerate(cells):
+                e.cell[v], e.op[v], e.ty[v] = ptr, op, ty
+        else:
+            e.seq, e.nv = 0, 0
+        return e
 
     def posted(self, seq: int, cells) -> None:
         """A kernel that collects `self.pending` and posts launch `seq` has been queued."""

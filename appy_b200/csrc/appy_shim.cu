@@ -896,7 +896,8 @@ int appy_p2p_open(void* ctx, const void* all_handles, unsigned spin_limit, void*
   d.rank = c->rank;
   d.spin_limit = spin_limit ? spin_limit : (1u << 23);
   d.err = c->d_err;
-  for (int r = 0; r < c->world; ++r) d.peer[r] = static_cast<unsigned long long*>(c->peers[r]);
+  for (int r = 0; r < 16; ++r) d.peer[r] = static_cast<unsigned long long*>(c->peers[r < c->world ? r : c->rank]);
+  d.own = static_cast<unsigned long long*>(c->peers[c->rank]);
   CK(cudaMemcpy(c->d_desc, &d, sizeof d, cudaMemcpyHostToDevice));
   c->opened = true;
   *device_descriptor = c->d_desc;
@@ -959,10 +960,12 @@ int appy_p2p_combine(void* ctx, uint64_t seq, int op, int dtype, void* dvalues, 
 }  // extern "C"
 
 namespace {
-// One warp: collect the totals of up to two earlier launches that only posted them (split-phase exchange).
-__global__ void __launch_bounds__(32) k_p2p_flush(const appy_mailbox* mb, appy_pending2 pend) {
-  appy_p2p_collect(mb, pend.e[0]);
-  appy_p2p_collect(mb, pend.e[1]);
+// One warp: collect the totals of an earlier launch that only posted them (split-phase exchange).
+__global__ void __launch_bounds__(32) k_p2p_flush(const appy_mailbox* mb, appy_pending pend) {
+  const appy_mb_view mv = appy_mb_open(mb);
+  appy_collect_regs regs;
+  appy_p2p_collect_begin(mv, pend, regs);
+  appy_p2p_collect_end(mv, pend, regs);
 }
 }  // namespace
 
@@ -972,11 +975,10 @@ int appy_p2p_flush(void* ctx, const void* pending, void* stream) {
   if (!ctx || !pending) return fail(APPY_ERR_ARG, "appy_p2p_flush: NULL argument");
   P2PContext* c = static_cast<P2PContext*>(ctx);
   if (!c->opened) return fail(APPY_ERR_ARG, "appy_p2p_flush: appy_p2p_open has not been called");
-  appy_pending2 pend;
+  appy_pending pend;
   memcpy(&pend, pending, sizeof pend);
-  for (int k = 0; k < 2; ++k)
-    if (pend.e[k].seq != 0 && (pend.e[k].nv < 1 || pend.e[k].nv > 4))
-      return fail(APPY_ERR_ARG, "appy_p2p_flush: a pending launch must carry 1..4 variables");
+  if (pend.seq != 0 && (pend.nv < 1 || pend.nv > 4))
+    return fail(APPY_ERR_ARG, "appy_p2p_flush: a pending launch must carry 1..4 variables");
   k_p2p_flush<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const appy_mailbox*>(c->d_desc), pend);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(APPY_ERR_CUDA, "appy_p2p_flush launch failed: %s", cudaGetErrorString(e));

@@ -149,6 +149,7 @@ struct appy_mailbox {
   unsigned reserved;
   unsigned* err;            // set to 1 when a wait ran out
   u64* peer[16];            // peer[r] = mailbox of rank r as mapped into this process
+  u64* own;                 // peer[rank], so that it can be read without knowing the rank first
 };
 
 APPY_DEV void appy_st_relaxed_sys(u64* p, u64 v) {
@@ -238,7 +239,9 @@ template <class Op, class T> APPY_DEV T appy_p2p_fold(const appy_mailbox* mb, u6
 // launch s + 2 at the latest, and collecting s needs every rank's words of s, so no rank runs more than two
 // launches ahead of the slowest one and a slot is never overwritten before every rank has read it.
 // A collect is described by values alone (cell addresses, operator and type codes), because the kernel
-// that collects was generated for another loop than the one that posted.
+// that collects was generated for another loop than the one that posted.  Between a loop's launch and the
+// launch (or flush) that collects it, its cells must be left alone: they are read when the collect begins
+// and written when it ends.
 // ---------------------------------------------------------------------------
 #define APPY_MB_RING 8
 enum { APPY_PEND_ADD = 0, APPY_PEND_MUL = 1, APPY_PEND_MAX = 2, APPY_PEND_MIN = 3 };
@@ -252,7 +255,6 @@ struct appy_pending {      // one earlier launch whose totals are still to be co
   int op[4];               // APPY_PEND_ADD ..
   int ty[4];               // APPY_PEND_F32 ..
 };
-struct appy_pending2 { appy_pending e[2]; };
 
 APPY_DEV u64* appy_mb_ring_words(u64* mailbox, u64 seq, int world, int src) {
   return mailbox + 512 + ((seq % APPY_MB_RING) * (u64)world + src) * 8;
@@ -271,12 +273,32 @@ APPY_DEV u64 appy_fold_bits(int op, int ty, u64 a, u64 b) {
   return appy_to_bits<i64>(appy_fold_any<i64>(op, appy_from_bits<i64>(a), appy_from_bits<i64>(b)));
 }
 
+// The descriptor's fields read once, all loads independent of one another (it lives in device memory, and
+// every store of the exchange is a compiler barrier that would otherwise force them to be read again).
+struct appy_mb_view {
+  int world, rank;
+  unsigned limit;
+  unsigned* err;
+  u64* to;       // lane r: mailbox of rank r
+  u64* own;      // this rank's mailbox
+};
+APPY_DEV appy_mb_view appy_mb_open(const appy_mailbox* mb) {
+  appy_mb_view v;
+  v.world = mb->world;
+  v.rank = mb->rank;
+  v.limit = mb->spin_limit;
+  v.err = mb->err;
+  v.to = mb->peer[threadIdx.x & 15];
+  v.own = mb->own;
+  return v;
+}
+
 // Called by the 32 threads of warp 0: lane r stores this rank's totals of launch `seq` into rank r's ring.
-template <int NV> APPY_DEV void appy_p2p_post(const appy_mailbox* mb, u64 seq, const u64 (&x)[NV]) {
+template <int NV> APPY_DEV void appy_p2p_post(const appy_mb_view& mv, u64 seq, const u64 (&x)[NV]) {
   const int lane = threadIdx.x & 31;
-  if (lane < mb->world) {
+  if (lane < mv.world) {
     const u64 tag = (u64)((unsigned)seq | 0x80000000u) << 32;
-    u64* dst = appy_mb_ring_words(mb->peer[lane], seq, mb->world, mb->rank);
+    u64* dst = appy_mb_ring_words(mv.to, seq, mv.world, mv.rank);
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       appy_st_relaxed_sys(dst + 2 * v, tag | (x[v] & 0xffffffffull));
@@ -285,48 +307,65 @@ template <int NV> APPY_DEV void appy_p2p_post(const appy_mailbox* mb, u64 seq, c
   }
 }
 
-// Called by the 32 threads of warp 0: waits (bounded) for every rank's words of launch p.seq in this rank's
-// own mailbox, folds them in rank order and applies the result to the cells.  A wait that runs out sets the
-// error word and turns floating-point results into NaN, as in the immediate exchange.
-APPY_DEV void appy_p2p_collect(const appy_mailbox* mb, const appy_pending& p) {
+// Collecting launch p.seq, in two halves so that the memory latencies of the first hide behind whatever the
+// caller does in between (the kernels fold their own partials there).  Called by the 32 threads of warp 0.
+// begin: lane r reads rank r's words of that launch from this rank's own mailbox, lane 0 reads the cells.
+struct appy_collect_regs { u64 lo[4], hi[4], cell[4]; };
+APPY_DEV void appy_p2p_collect_begin(const appy_mb_view& mv, const appy_pending& p, appy_collect_regs& r) {
   if (p.seq == 0) return;
-  const int world = mb->world, lane = threadIdx.x & 31;
-  const u64 tag = (u64)((unsigned)p.seq | 0x80000000u) << 32;
-  const u64* src = appy_mb_ring_words(mb->peer[mb->rank], p.seq, world, lane < world ? lane : 0);
-  const unsigned limit = mb->spin_limit;
-  unsigned spins = 0;
-  bool ok = true;
-  for (int v = 0; v < p.nv; ++v) {
-    u64 lo = 0, hi = 0;
-    if (lane < world) {
-      for (;;) {
-        lo = appy_ld_relaxed_sys(src + 2 * v);
-        hi = appy_ld_relaxed_sys(src + 2 * v + 1);
-        if (((lo ^ tag) >> 32) == 0 && ((hi ^ tag) >> 32) == 0) break;
-        if (!ok || ++spins > limit) {
-          ok = false;
-          break;
-        }
-        __nanosleep(spins < 256 ? 20 : 1000);
+  const int lane = threadIdx.x & 31;
+  const u64* src = appy_mb_ring_words(mv.own, p.seq, mv.world, lane < mv.world ? lane : 0);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    if (v < p.nv) {
+      r.lo[v] = appy_ld_relaxed_sys(src + 2 * v);
+      r.hi[v] = appy_ld_relaxed_sys(src + 2 * v + 1);
+      if (lane == 0) {
+        if (p.ty[v] == APPY_PEND_F32 || p.ty[v] == APPY_PEND_I32) r.cell[v] = (u64)*reinterpret_cast<const unsigned*>(p.cell[v]);
+        else r.cell[v] = *reinterpret_cast<const u64*>(p.cell[v]);
       }
     }
-    const bool all_ok = __all_sync(0xffffffffu, ok) != 0;
-    const u64 mine = (hi << 32) | (lo & 0xffffffffull);
-    u64 total = __shfl_sync(0xffffffffu, mine, 0);
-    for (int r = 1; r < world; ++r) total = appy_fold_bits(p.op[v], p.ty[v], total, __shfl_sync(0xffffffffu, mine, r));
-    if (lane == 0) {
-      const int ty = p.ty[v];
-      if (!all_ok) {
-        atomicExch(mb->err, 1u);
-        if (ty == APPY_PEND_F32) total = appy_to_bits<float>(appy_p2p_poison<float>(0.f));
-        if (ty == APPY_PEND_F64) total = appy_to_bits<double>(appy_p2p_poison<double>(0.0));
+  }
+}
+// end: waits (bounded) for words that had not arrived yet, folds the ranks' totals in rank order and applies
+// the result to the cells.  A wait that runs out sets the error word and turns floating-point results into
+// NaN, as in the immediate exchange.
+APPY_DEV void appy_p2p_collect_end(const appy_mb_view& mv, const appy_pending& p, appy_collect_regs& r) {
+  if (p.seq == 0) return;
+  const int world = mv.world, lane = threadIdx.x & 31;
+  const u64 tag = (u64)((unsigned)p.seq | 0x80000000u) << 32;
+  const u64* src = appy_mb_ring_words(mv.own, p.seq, world, lane < world ? lane : 0);
+  unsigned spins = 0;
+  bool ok = true;
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    if (v < p.nv) {
+      u64 lo = r.lo[v], hi = r.hi[v];
+      if (lane < world) {
+        while (((lo ^ tag) >> 32) != 0 || ((hi ^ tag) >> 32) != 0) {
+          if (!ok || ++spins > mv.limit) {
+            ok = false;
+            break;
+          }
+          __nanosleep(spins < 256 ? 20 : 1000);
+          lo = appy_ld_relaxed_sys(src + 2 * v);
+          hi = appy_ld_relaxed_sys(src + 2 * v + 1);
+        }
       }
-      if (ty == APPY_PEND_F32 || ty == APPY_PEND_I32) {
-        unsigned* c = reinterpret_cast<unsigned*>(p.cell[v]);
-        *c = (unsigned)appy_fold_bits(p.op[v], ty, (u64)*c, total);
-      } else {
-        u64* c = reinterpret_cast<u64*>(p.cell[v]);
-        *c = appy_fold_bits(p.op[v], ty, *c, total);
+      const bool all_ok = __all_sync(0xffffffffu, ok) != 0;
+      const u64 mine = (hi << 32) | (lo & 0xffffffffull);
+      u64 total = __shfl_sync(0xffffffffu, mine, 0);
+      for (int q = 1; q < world; ++q) total = appy_fold_bits(p.op[v], p.ty[v], total, __shfl_sync(0xffffffffu, mine, q));
+      if (lane == 0) {
+        const int ty = p.ty[v];
+        if (!all_ok) {
+          atomicExch(mv.err, 1u);
+          if (ty == APPY_PEND_F32) total = appy_to_bits<float>(appy_p2p_poison<float>(0.f));
+          if (ty == APPY_PEND_F64) total = appy_to_bits<double>(appy_p2p_poison<double>(0.0));
+        }
+        const u64 res = appy_fold_bits(p.op[v], ty, r.cell[v], total);
+        if (ty == APPY_PEND_F32 || ty == APPY_PEND_I32) *reinterpret_cast<unsigned*>(p.cell[v]) = (unsigned)res;
+        else *reinterpret_cast<u64*>(p.cell[v]) = res;
       }
     }
   }

@@ -729,6 +729,7 @@ def main():
     # launch stream.  (Overlapping it with the next step's kernels through a second buffer was
     # measured slower: the reduction kernels occupy every SM, so the NCCL kernel waits for them anyway.)
     outs = [out]
+    part = torch.zeros(2, dtype=torch.float64, device="cuda")
     use_p2p = world > 1 and args.combine in ("p2p", "p2p-immediate")
     if use_p2p:
         from appy_b200.backends.cuda_sm100 import multi_gpu as mg
@@ -753,11 +754,17 @@ def main():
         elif use_p2p:
             L.sum_into_p2p(a, out_a)
             L.masked_sum_into_p2p(a, m, out_b)
+        elif world > 1:
+            # NCCL: this step's per-GPU sums go to a scratch pair, one all-reduce combines both, the
+            # result is added to the accumulating cells
+            part.zero_()
+            L.sum_into(a, part[0:1])
+            L.masked_sum_into(a, m, part[1:2])
+            dist.all_reduce(part)
+            out.add_(part)
         else:
             L.sum_into(a, out_a)
             L.masked_sum_into(a, m, out_b)
-            if world > 1:
-                dist.all_reduce(out)
 
     def drain():
         if split:

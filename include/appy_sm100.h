@@ -167,8 +167,8 @@ int appy_p2p_combine(void* ctx, uint64_t seq, int op, int dtype, void* dvalues, 
 /* Split-phase form of the exchange: kernels generated with `combine="p2p", defer=True` only post their
  * totals and collect those of the launch before them, so that no kernel waits for the slowest rank or
  * for an NVLink round trip.  appy_p2p_flush runs the collect for launches that no later kernel has
- * collected yet; `pending` points to two records {uint64 seq (0 = none); int32 nv; int32 pad;
- * void* cell[4]; int32 op[4] (APPY_OP_*); int32 dtype[4] (APPY_F32..)} as the kernels take them.
+ * collected yet; `pending` points to one record {uint64 seq (0 = none); int32 nv; int32 pad;
+ * void* cell[4]; int32 op[4] (APPY_OP_*); int32 dtype[4] (APPY_F32..)} as the kernels take it.
  * Collective like the kernels themselves: every rank flushes at the same point of its launch sequence.
  * (The reference has no multi-GPU path; north_star asks for the combine of shared(...) scalars.) */
 int appy_p2p_flush(void* ctx, const void* pending, void* stream);

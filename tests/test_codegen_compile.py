@@ -197,7 +197,8 @@ def test_split_phase_exchange_compiles():
     scope = dict(a=A1, s=np.array([0.0]), m=np.array([0.0], f32), n=1000)
     plan, code = build(src, scope, combine="p2p", defer=True)
     assert [p.kind for p in plan.params][-3:] == ["mb", "seq", "pend"]
-    assert "appy_p2p_post<2>(__mb, __seq, __x);" in code and "appy_p2p_collect(__mb, __pend.e[1]);" in code
+    assert "appy_p2p_post<2>(__mv, __seq, __x);" in code and "appy_p2p_collect_end(__mv, __pend, __cr);" in code
+    assert code.index("appy_p2p_collect_begin") < code.index("appy_ws_collect<")       # reads go out before the local fold
     assert "appy_p2p_exchange" not in code.split("struct kernel_loop_1_body")[1]
     plan, code = build(src, scope, combine="p2p")
     assert "appy_p2p_exchange<2>" in code and "pend" not in [p.kind for p in plan.params]
