@@ -63,6 +63,9 @@ SIGNATURES = {
     "appy_p2p_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "appy_p2p_destroy": (C.c_int, [C.c_void_p]),
     "appy_p2p_combine": (C.c_int, [C.c_void_p, C.c_uint64, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "appy_probe_row_gather_f32": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_void_p,
+                                            C.c_void_p]),
+    "appy_probe_gather_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "appy_p2p_flush": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "appy_vec_add_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "appy_sum_f32": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_void_p]),

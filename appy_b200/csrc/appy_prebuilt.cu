@@ -256,6 +256,54 @@ int launch_spmm_stream(const SpmmBody<OffT>& body, const int* indptr, i64 lo, i6
   return finish_launch("spmm fix-up launch");
 }
 
+// ------------------------------------------------------------------ gather ceilings (measurement aids)
+// What the memory system delivers for the gathers of T3 and T5 alone: the same index streams and the same
+// gathered operand as the kernels, no values, no row structure, no output besides one word per thread.
+template <int V, int D>
+__global__ void __launch_bounds__(512) k_probe_rows(const float* __restrict__ B, i64 ldb, const int* __restrict__ rows,
+                                                     i64 n, float* out) {
+  const int lane = threadIdx.x & 31;
+  const i64 warp = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = ((i64)gridDim.x * blockDim.x) >> 5;
+  const i64 per = ((n + nw - 1) / nw + 31) / 32 * 32;
+  const i64 ks = warp * per, ke = ks + per < n ? ks + per : n;
+  appy_pack<float, V> acc;
+#pragma unroll
+  for (int x = 0; x < V; ++x) acc.v[x] = 0.f;
+  const float* bl = B + lane * V;
+  for (i64 kb = ks; kb + 32 <= ke; kb += 32) {
+    const i64 my = (i64)appy_ld_cs<int, 1>(rows + kb + lane).v[0] * ldb;
+#pragma unroll 1
+    for (int q = 0; q < 32; q += D) {
+      appy_pack<float, V> b[D];
+#pragma unroll
+      for (int j = 0; j < D; ++j) b[j] = appy_ld_nc<float, V>(bl + appy_shfl<i64>(my, q + j, 32));
+#pragma unroll
+      for (int j = 0; j < D; ++j)
+#pragma unroll
+        for (int x = 0; x < V; ++x) acc.v[x] += b[j].v[x];
+    }
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int x = 0; x < V; ++x) s += acc.v[x];
+  out[(i64)blockIdx.x * blockDim.x + threadIdx.x] = s;
+}
+__global__ void __launch_bounds__(256) k_probe_gather(const float* __restrict__ x, const int* __restrict__ idx, i64 n,
+                                                       float* out) {
+  float s = 0.f;
+  const i64 stride = (i64)gridDim.x * blockDim.x;
+  i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n; i += 4 * stride) {
+    int c[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) c[u] = appy_ld_cs<int, 1>(idx + i + u * stride).v[0];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) s += appy_ldg1(x + c[u]);
+  }
+  for (; i < n; i += stride) s += appy_ldg1(x + appy_ld_cs<int, 1>(idx + i).v[0]);
+  out[(i64)blockIdx.x * blockDim.x + threadIdx.x] = s;
+}
+
 // ------------------------------------------------------------------ row-length histogram
 template <class IdxT>
 __global__ void k_row_hist(const IdxT* indptr, i64 nrows, u64* counts, u64* max_len) {
@@ -423,6 +471,26 @@ int appy_spmm_csr_f32(const float* ddata, const int32_t* dindptr, const int32_t*
   if (T <= 4) return launch_spmm<1, 4, 4, 4, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
   if (T <= 8) return launch_spmm<1, 8, 2, 3, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
   return launch_spmm<1, 16, 2, 2, 0, i64>(body, dindptr, row_lo, row_hi, ncols, s);
+}
+
+int appy_probe_row_gather_f32(const float* dB, int64_t ldb, const int32_t* drows, int64_t n, int row_floats,
+                              float* dout, void* stream) {
+  if (!dB || !drows || !dout || n < 0) return appy_fail_arg("appy_probe_row_gather_f32: bad arguments");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned grid = (unsigned)(sm_count() * 2);
+  switch (row_floats) {
+    case 128: k_probe_rows<4, 8><<<grid, 512, 0, s>>>(dB, ldb, drows, n, dout); break;
+    case 64: k_probe_rows<2, 8><<<grid, 512, 0, s>>>(dB, ldb, drows, n, dout); break;
+    case 32: k_probe_rows<1, 8><<<grid, 512, 0, s>>>(dB, ldb, drows, n, dout); break;
+    default: return appy_fail_arg("appy_probe_row_gather_f32: row_floats must be 128, 64 or 32");
+  }
+  return finish_launch("row-gather probe launch");
+}
+
+int appy_probe_gather_f32(const float* dx, const int32_t* didx, int64_t n, float* dout, void* stream) {
+  if (!dx || !didx || !dout || n < 0) return appy_fail_arg("appy_probe_gather_f32: bad arguments");
+  k_probe_gather<<<(unsigned)(sm_count() * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(dx, didx, n, dout);
+  return finish_launch("gather probe launch");
 }
 
 int appy_row_histogram(const void* d_indptr, int idx_bytes, int64_t nrows, int64_t* counts32,

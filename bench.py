@@ -37,9 +37,16 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 N_HEADLINE = 1 << 26
-# dram__bytes_read.sum + dram__bytes_write.sum per launch at n = 2**26, from one ncu capture each
-# (profiles/masked_sum_ncu.md, profiles/sum_ncu.md)
-NCU_TRAFFIC = {"masked sum": 343_734_016, "sum": 272_242_688}
+
+
+def ncu_traffic() -> dict:
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of every benchmark kernel, from
+    one ncu capture each of the full-size workload; the file names the capture each figure comes from."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as fh:
+            return json.load(fh)["kernels"]
+    except Exception:
+        return {}
 
 
 def measured_peak():
@@ -369,9 +376,14 @@ def kernel_table(torch, L, peak, rank, quick=False, with_triton=True, world=1):
     With several ranks every rank runs its own full-size shard (weak scaling): the time is the
     maximum over ranks and GB/s is the sum over ranks; `frac` stays per GPU."""
     from appy_b200 import workloads as W
+    from appy_b200.backends.cuda_sm100 import runtime as _rt
     rows = {}
     dev = "cuda"
     TK = _triton_arm() if with_triton else None
+    rt_lib, rt_check = _rt.lib(), _rt.check
+
+    def stream_of(t):
+        return t.cuda.current_stream().cuda_stream
 
     def tri(name, byts, fn, rot, iters):
         if TK is None:
@@ -440,6 +452,19 @@ def kernel_table(torch, L, peak, rank, quick=False, with_triton=True, world=1):
             {"l2": "2 rotating copies"})
         tri(f"C3 spmv {kind} M=2^20 nnz={Am.nnz}", byts,
             lambda i: TK.spmv(sets[i][0], sets[i][1], sets[i][2], sets[i][3], sets[i][4], M), 2, 6)
+        # the floor of this access pattern: the matrix's own column indices read once and x gathered through
+        # them, nothing else (no values, no rows, no output)
+        probe_out = torch.empty(512 * 8 * 148, device=dev)
+        floor = time_kernel(torch, lambda i: rt_check(rt_lib.appy_probe_gather_f32(
+            sets[i][3].data_ptr(), sets[i][2].data_ptr(), Am.nnz, probe_out.data_ptr(), stream_of(torch))), 2, 40)
+        if world > 1:
+            tf = torch.tensor([floor], dtype=torch.float64, device="cuda")
+            import torch.distributed as dist
+            dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+            floor = float(tf.item())
+        rows[f"C3 spmv {kind} M=2^20 nnz={Am.nnz}"].update({
+            "gather_floor_us": round(floor, 2), "floor_is": "x[indices[k]] summed over all non-zeros, no values/rows/output",
+            "kernel_over_floor": round(rows[f"C3 spmv {kind} M=2^20 nnz={Am.nnz}"]["us"] / floor, 3)})
         Asp = _scipy_csr(Am)
         if Asp is not None:
             host(f"C3 spmv {kind} M=2^20 nnz={Am.nnz}", lambda: Asp @ xv)
@@ -453,6 +478,18 @@ def kernel_table(torch, L, peak, rank, quick=False, with_triton=True, world=1):
     us = time_kernel(torch, lambda i: L.spmm(d[0], d[1], d[2], d[3], Cm, M), 1, 10)
     add(f"C5 spmm M=2^18 nnz={Am.nnz} B=2^18x128", b1, us,
         {"gather_bytes": int(b2), "gather_gbs": round(b2 / us / 1e3, 1), "l2": "403 MB working set"})
+    probe_out = torch.empty(512 * 8 * 148, device=dev)
+    ceil_us = time_kernel(torch, lambda i: rt_check(rt_lib.appy_probe_row_gather_f32(
+        d[3].data_ptr(), B.shape[1], d[2].data_ptr(), Am.nnz, 128, probe_out.data_ptr(), stream_of(torch))), 1, 10)
+    if world > 1:
+        tf = torch.tensor([ceil_us], dtype=torch.float64, device="cuda")
+        import torch.distributed as dist
+        dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+        ceil_us = float(tf.item())
+    rows[f"C5 spmm M=2^18 nnz={Am.nnz} B=2^18x128"].update({
+        "gather_ceiling_us": round(ceil_us, 2), "kernel_over_ceiling": round(us / ceil_us, 3),
+        "ceiling_is": "the B rows named by the matrix's column indices gathered and summed, 8 rows in flight per "
+                      "warp; no coefficients, row ends or output"})
     tri(f"C5 spmm M=2^18 nnz={Am.nnz} B=2^18x128", b1, lambda i: TK.spmm(d[0], d[1], d[2], d[3], Cm, M), 1, 2)
     Asp = _scipy_csr(Am)
     if Asp is not None:
@@ -630,10 +667,19 @@ def run_only(args):
     k, sc = args.only, max(1, args.scale)
     dev = "cuda"
     if k == "vec_add":
+        # four rotating buffer sets, as in the per-kernel table: 201 MB per set is close to the L2 size, and a
+        # single set would leave part of the previous launch's output in L2
         n = (1 << 24) // sc
         a, b = W.vec_add(n)
-        d = (torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev), torch.empty(n, device=dev))
-        fn, byts = (lambda: L.vec_add(*d)), W.bytes_vec_add(n)
+        sets = [(torch.from_numpy(a).to(dev), torch.from_numpy(b).to(dev), torch.empty(n, device=dev)) for _ in range(4)]
+        turn = [0]
+
+        def fn():
+            turn[0] = (turn[0] + 1) % 4
+            L.vec_add(*sets[turn[0]])
+        byts = W.bytes_vec_add(n)
+        for _ in range(4):
+            fn()
     elif k in ("sum", "masked_sum"):
         n = (1 << 26) // sc
         a, m = W.masked_sum(n)
@@ -674,6 +720,55 @@ def run_only(args):
                       "gbs": round(byts / us / 1e3, 1)}), flush=True)
 
 
+def run_ceilings(args):
+    """Gather ceilings of the two sparse kernels, measured with the library's probe kernels
+    (appy_probe_row_gather_f32 / appy_probe_gather_f32): 2^23 random rows of a 2^18 x 128 float32 matrix,
+    taken whole (512 B), in halves (256 B) and in quarters (128 B), from all of it (134 MB), half of its
+    rows (67 MB) and a quarter (34 MB); and x[indices[k]] over the column indices of both C3 matrices.
+    L2 is flushed before every timed launch.  Prints one JSON object."""
+    import torch
+    from appy_b200 import workloads as W
+    from appy_b200.backends.cuda_sm100 import runtime as rt
+    torch.cuda.set_device(0)
+    rt.init(0)
+    L = rt.lib()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def cold(fn, iters=6):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return float(np.median(ts))
+
+    M, n = 1 << 18, 1 << 23
+    B = torch.rand((M, 128), device="cuda")
+    out = torch.empty(512 * 8 * 148, device="cuda")
+    res = {"row_gather": [], "spmv_gather": []}
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for frac, label in ((1, "134 MB"), (2, "67 MB"), (4, "34 MB")):
+        rows = torch.randint(0, M // frac, (n,), device="cuda", dtype=torch.int32, generator=g)
+        for floats in (128, 64, 32):
+            us = cold(lambda: rt.check(L.appy_probe_row_gather_f32(B.data_ptr(), 128, rows.data_ptr(), n, floats,
+                                                                     out.data_ptr(), None)))
+            res["row_gather"].append({"operand": label, "bytes_per_row": 4 * floats, "rows": n, "us": round(us, 1),
+                                      "gbs": round(n * 4 * floats / us / 1e3)})
+    for kind in ("poisson", "zipf"):
+        Am, xv = W.spmv(kind=kind)
+        idx, x = torch.from_numpy(Am.indices).cuda(), torch.from_numpy(xv).cuda()
+        us = cold(lambda: rt.check(L.appy_probe_gather_f32(x.data_ptr(), idx.data_ptr(), Am.nnz, out.data_ptr(), None)))
+        res["spmv_gather"].append({"matrix": kind, "nnz": Am.nnz, "us": round(us, 1)})
+    print(json.dumps(res), flush=True)
+
+
 # --------------------------------------------------------------------------- main arm
 def main():
     ap = argparse.ArgumentParser()
@@ -687,6 +782,8 @@ def main():
     ap.add_argument("--only", default=None,
                     help="run a single configuration's kernel --steps times and exit (for profilers): "
                          "vec_add, sum, masked_sum, gemv, spmv_poisson, spmv_zipf, spmm")
+    ap.add_argument("--ceilings", action="store_true",
+                    help="measure the gather ceilings of the sparse kernels with the library's probe kernels and exit")
     ap.add_argument("--scale", type=int, default=1, help="with --only: divide the problem size by this factor")
     ap.add_argument("--combine", default="p2p", choices=["nccl", "p2p", "p2p-immediate"],
                     help="N > 1: how the two result scalars are combined across GPUs: peer mailboxes inside "
@@ -698,6 +795,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.ceilings:
+        run_ceilings(args)
         return
     if args.only:
         run_only(args)
@@ -994,8 +1094,19 @@ def main():
         if strong is not None:
             line["strong"] = {"what": "the configured problems split over the GPUs with @jit(distribute=True); "
                                       "time = maximum over ranks; strong_speedup = one_gpu_us / us", "kernels": strong}
+        traffic = ncu_traffic()
         if n == N_HEADLINE:
-            line["roofline"]["traffic"] = NCU_TRAFFIC.get(dom_name.split(" (")[0])
+            t = traffic.get("masked_sum" if dom_name.startswith("masked") else "sum")
+            line["roofline"]["traffic"] = t["dram_bytes"] if t else None
+            line["roofline"]["traffic_source"] = t["source"] if t else None
+            keys = {"C1": "vec_add", "C2a": "sum", "C2b": "masked_sum", "C4": "gemv", "C3 spmv poisson": "spmv_poisson",
+                    "C3 spmv zipf": "spmv_zipf", "C5": "spmm"}
+            for row, vals in table.items():
+                for prefix, key in keys.items():
+                    if row.startswith(prefix) and key in traffic:
+                        vals["traffic"] = traffic[key]["dram_bytes"]
+                        vals["traffic_over_algorithmic"] = round(traffic[key]["dram_bytes"] / vals["bytes"], 3)
+                        vals["traffic_source"] = traffic[key]["source"]
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

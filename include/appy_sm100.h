@@ -203,6 +203,18 @@ int appy_spmm_csr_f32(const float* ddata, const int32_t* dindptr, const int32_t*
                       const float* dB, int64_t ldb, float* dC, int64_t ldc, int64_t row_lo,
                       int64_t row_hi, int ncols, void* stream);
 
+/* ---- gather ceilings (measurement aids; no counterpart in the reference) ----
+ * What the memory system delivers for the gathers of the two sparse kernels alone, so that their times can
+ * be set against a measured floor instead of an assumed one.
+ * appy_probe_row_gather_f32: every warp sums rows drows[k] (k < n, rounded down to whole blocks of 32 per
+ * warp) of the row-major matrix dB, `row_floats` (128, 64 or 32) leading floats of each, eight rows in
+ * flight per warp — the gathers of appy_spmm_csr_f32 without coefficients, row ends or output.
+ * appy_probe_gather_f32: sums dx[didx[k]] — the gathers of appy_spmv_csr_f32 without values and rows.
+ * dout receives one float per thread of the probe's grid (at most 512 * 8 * the number of SMs). */
+int appy_probe_row_gather_f32(const float* dB, int64_t ldb, const int32_t* drows, int64_t n, int row_floats,
+                              float* dout, void* stream);
+int appy_probe_gather_f32(const float* dx, const int32_t* didx, int64_t n, float* dout, void* stream);
+
 /* ---- allocation-free variant ---------------------------------------------
  * No counterpart in the reference (it has no native code and allocates through torch).
  *
