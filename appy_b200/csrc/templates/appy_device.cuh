@@ -132,16 +132,6 @@ template <class T> APPY_DEV T appy_shfl(T v, int src, int width) {
   }
 }
 
-template <class T> APPY_DEV T appy_shfl_up(T v, int delta) {
-  if (sizeof(T) == 8) {
-    union { T t; u64 u; } x; x.t = v;
-    x.u = __shfl_up_sync(APPY_FULL_MASK, x.u, delta, 32);
-    return x.t;
-  } else {
-    return __shfl_up_sync(APPY_FULL_MASK, v, delta, 32);
-  }
-}
-
 // all-reduce over a group of G consecutive lanes (G a power of two, 1..32);
 // every lane of the group receives the result.  All 32 lanes of the warp must
 // reach the call (groups never diverge from one another in the templates).
