@@ -382,7 +382,7 @@ class CompiledLoop:
                 vals.append(C.c_uint64(multi_gpu.combiner().next_seq()))
             elif p.kind == "pend":
                 from . import multi_gpu
-                vals.append(multi_gpu.combiner().pending_struct())
+                vals.append(multi_gpu.Pending2())      # filled at launch time, when the grid is known
         return rt.ArgPack(vals)
 
     _P2P_OPS = {"+": 0, "*": 1, "max": 2, "min": 3}
@@ -792,16 +792,18 @@ class CompiledLoop:
         if cells:
             self._pre_combine(cells)
         if grid:
+            mine = None
             if seq_slot is not None:
                 from . import multi_gpu
                 comb = multi_gpu.combiner()
                 pack.values[seq_slot].value = comb.next_seq()
-                if deferred is not None:
-                    comb._fill_pending(pack.values[deferred[0]])      # what this launch collects ...
-                    comb.posted(pack.values[seq_slot].value, deferred[1])     # ... and what the next one will
+                if deferred is not None:      # which launches this one serves, and where its own partials go
+                    mine = comb.begin_split(pack.values[deferred[0]], deferred[2], grid)
             if scratch is not None:     # the stream's scratch buffer may have been replaced by a larger one
                 pack.values[scratch[0]].value = rt.scratch(stream, scratch[1])
             rt.launch(handle, grid, block, pack, smem, stream)
+            if mine is not None:
+                comb.end_split(pack.values[seq_slot].value, grid, mine, deferred[1])
             if post is not None:
                 rt.launch(post[0], post[1], post[2], pack, 0, stream)
         if cells:
@@ -871,20 +873,23 @@ class CompiledLoop:
             pack = self._pack(variant, args, arrays, lo, hi, stream, need)
             h = variant.handle(tun)
             grid, block, smem = variant.plan.launch_config(tun, hi - lo, self.sm_count)
+            kinds_ = [p.kind for p in variant.plan.params]
+            deferred = None
+            if "pend" in kinds_:            # split-phase exchange: the next two launches fold, post and collect this one
+                if any_host and any(a.host and a.name in self.stored for a in arrays):
+                    raise NotImplementedError("defer=True needs the shared(...) cells in device memory "
+                                              "(a host cell is read back before the exchange has completed)")
+                deferred = (kinds_.index("pend"), tuple(self._deferred_cells(args, arrays)), rt.workspace(stream))
+                comb = multi_gpu.combiner()
+                mine = comb.begin_split(pack.values[deferred[0]], deferred[2], grid)
             rt.launch(h, grid, block, pack, smem, stream)
+            if deferred is not None:
+                comb.end_split(pack.values[kinds_.index("seq")].value, grid, mine, deferred[1])
             post = variant.plan.post_config(tun, hi - lo, self.sm_count)
             if post is not None:        # second kernel of a two-kernel plan: same arguments, same stream
                 post = (variant.post_handle(tun), post[0], post[1])
                 rt.launch(post[0], post[1], post[2], pack, 0, stream)
-            kinds_ = [p.kind for p in variant.plan.params]
             scratch = (kinds_.index("scratch"), max(need, 1 << 20)) if "scratch" in kinds_ else None
-            deferred = None
-            if "pend" in kinds_:            # split-phase exchange: this launch posted, the next one collects it
-                if any_host and any(a.host and a.name in self.stored for a in arrays):
-                    raise NotImplementedError("defer=True needs the shared(...) cells in device memory "
-                                              "(a host cell is read back before the exchange has completed)")
-                deferred = (kinds_.index("pend"), tuple(self._deferred_cells(args, arrays)))
-                multi_gpu.combiner().posted(pack.values[kinds_.index("seq")].value, deferred[1])
             # Launch record.  With host arrays it is kept when they are contiguous, none of them had to
             # be copied to become so, the stored ones overlap nothing, and the loop does not distribute
             # or combine (those paths look at the arrays again).

@@ -320,7 +320,7 @@ class Lowering:
         if p.kind == "mb":
             return "const appy_mailbox* __mb"
         if p.kind == "pend":
-            return "appy_pending __pend"
+            return "appy_pending2 __pend"
         return f"{p.ty.strong().c} {p.name}"
 
     def _members(self, params) -> list[str]:
@@ -338,6 +338,11 @@ class Lowering:
             elif p.kind == "seq":
                 lines.append(f"  __body.{p.name} = {p.name};")
         lines += ["  " + l for l in extra_init]
+        if any(p.kind == "pend" for p in params):
+            # split-phase exchange: one warp serves the two launches before this one beside the kernel's own
+            # work.  The last CTA does it: in a grid-stride loop it never has more tiles than the others, and
+            # one fewer whenever the tiles do not divide evenly, which absorbs the warp's late start.
+            lines.append("  if (blockIdx.x == gridDim.x - 1 && threadIdx.x < 32) appy_split_service(__mb, __pend);")
         lines += [f"  {call}", "}"]
         return lines
 
@@ -406,6 +411,12 @@ class Lowering:
         for op, ty, acc, node in items:
             off, arr = em.offset(node)
             addrs.append(f"({arr.name} + ({off}))")
+        if self.options.get("combine") == "p2p" and self.options.get("defer"):
+            # split phase: a CTA only stores its partials; warp 0 of CTA 0 of the next two such kernels folds,
+            # posts and collects them (appy_split_service, called at the top of the kernel)
+            for r, (op, ty, acc, _n) in enumerate(items):
+                out.append(f"appy_split_publish<{ty.c}>(__pend.partials, {r}, {acc});")
+            return out
         if not ordered:
             out.append("if (threadIdx.x == 0) {")
             for (op, ty, acc, _n), addr in zip(items, addrs):
@@ -416,12 +427,6 @@ class Lowering:
             for r, (op, ty, acc, _n) in enumerate(items):
                 out.append(f"appy_ws_publish<{ty.c}>(__w, {r}, {acc});")
             out.append("if (appy_ws_arrive(__w, __smem)) {")
-            defer = self.options.get("combine") == "p2p" and self.options.get("defer")
-            if defer:
-                # split phase: the reads that the collect of the previous launch needs go out first, so that
-                # their latency hides behind the fold of this kernel's own partials
-                out.append("  appy_mb_view __mv; appy_collect_regs __cr;")
-                out.append("  if (threadIdx.x < 32) { __mv = appy_mb_open(__mb); appy_p2p_collect_begin(__mv, __pend, __cr); }")
             if self.options.get("combine") == "p2p":
                 # this GPU's totals, then the exchange with the other ranks inside the same kernel
                 for r, (op, ty, acc, _n) in enumerate(items):
@@ -430,14 +435,6 @@ class Lowering:
                 out.append("  if (threadIdx.x < 32) {")
                 bits = ", ".join(f"appy_to_bits<{ty.c}>(__t{r})" for r, (op, ty, acc, _n) in enumerate(items))
                 out.append(f"    u64 __x[{len(items)}] = {{{bits}}};")
-                if self.options.get("defer"):
-                    # split phase: post this launch's totals, collect those of the launches before it; the
-                    # cells of this loop are updated by whoever collects this launch
-                    out.append(f"    appy_p2p_post<{len(items)}>(__mv, __seq, __x);")
-                    out.append("    appy_p2p_collect_end(__mv, __pend, __cr);")
-                    out.append("  }")
-                    out.append("}")
-                    return out
                 out.append(f"    const bool __ok = appy_p2p_exchange<{len(items)}>(__mb, __seq, __x);")
                 for r, ((op, ty, acc, _n), addr) in enumerate(zip(items, addrs)):
                     out.append(f"    __t{r} = appy_p2p_fold<{OPS[op]}, {ty.c}>(__mb, __x[{r}]);")

@@ -64,9 +64,22 @@ def all_reduce(values, op: str = "+"):
 
 
 class Pending(_C.Structure):
-    """One split-phase launch whose totals are still to be collected (struct appy_pending of t_flat.cuh)."""
-    _fields_ = [("seq", _C.c_uint64), ("nv", _C.c_int32), ("pad", _C.c_int32), ("cell", _C.c_void_p * 4),
-                ("op", _C.c_int32 * 4), ("ty", _C.c_int32 * 4)]
+    """One split-phase launch that is still to be folded or collected (struct appy_pending of t_flat.cuh)."""
+    _fields_ = [("seq", _C.c_uint64), ("nv", _C.c_int32), ("grid", _C.c_int32), ("slot", _C.c_int32),
+                ("pad", _C.c_int32), ("partials", _C.c_void_p), ("cell", _C.c_void_p * 4), ("op", _C.c_int32 * 4),
+                ("ty", _C.c_int32 * 4)]
+
+
+class Pending2(_C.Structure):
+    """What a split-phase kernel (or the flush kernel) is given: the launch to fold and post, the launch to
+    collect, and where this launch's own partials go (struct appy_pending2)."""
+    _fields_ = [("fold", Pending), ("coll", Pending), ("partials", _C.c_void_p)]
+
+
+WS_SPLIT_OFFSET = 256 + 8 * 4 * 65536      # the split-phase partials inside the reduction workspace ...
+WS_SPLIT_PARITY_BYTES = 8 * 4 * 4096       # ... per launch parity: 4 variables x 4096 CTAs
+SPLIT_MAX_GRID = 4096
+MB_RING = 8
 
 
 class P2PCombiner:
@@ -102,7 +115,10 @@ class P2PCombiner:
         rt.check(rt.lib().appy_p2p_open(self._ctx, blob, spin_limit, C.byref(desc)))
         self.descriptor = desc.value
         self._seq = 0
-        self.pending = []           # split-phase launches not collected yet: (seq, [(cell address, op, dtype)])
+        self.pending = []           # split-phase launches whose cells are not final yet (to_collect, to_fold)
+        self.to_fold = None
+        self.to_collect = None
+        self.split_count = 0
         if world_size > 1 and not loopback_world:
             import torch.distributed as dist
             dist.barrier()          # every rank has mapped every mailbox before the first launch
@@ -131,36 +147,51 @@ class P2PCombiner:
                                            C.c_void_p(values.data_ptr()), values.numel(), C.c_void_p(stream)))
 
     # ---- split-phase exchange (`@jit(combine="p2p", defer=True)`)
-    def pending_struct(self):
-        """The launch still to be collected, marshalled as the kernels and appy_p2p_flush take it."""
-        return self._fill_pending(Pending())
+    # A split-phase launch goes through two stages after it has been queued: `to_fold` (its partials wait
+    # in the workspace for the next launch's first warp) and `to_collect` (its totals are posted; the launch
+    # after that applies the world's totals to its cells).  Each is (seq, slot, grid, partials, cells).
+    def begin_split(self, pend: "Pending2", workspace: int, grid: int) -> int:
+        """Fill `pend` for a split-phase kernel about to be queued with `grid` CTAs on the stream that owns
+        `workspace`; returns the address where that kernel's CTAs store their partials."""
+        if grid > SPLIT_MAX_GRID:
+            raise RuntimeError(f"defer=True: the kernel's grid ({grid} CTAs) exceeds {SPLIT_MAX_GRID}")
+        self._fill(pend.fold, self.to_fold)
+        self._fill(pend.coll, self.to_collect)
+        mine = workspace + WS_SPLIT_OFFSET + (self.split_count & 1) * WS_SPLIT_PARITY_BYTES
+        pend.partials = mine
+        return mine
 
-    def _fill_pending(self, e):
-        if self.pending:
-            seq, cells = self.pending[0]
-            e.seq, e.nv = seq, len(cells)
-            for v, (ptr, op, ty) in enumerate(cells):
-                e.cell[v], e.op[v], e.ty[v] = ptr, op, ty
-        else:
+    def end_split(self, seq: int, grid: int, partials: int, cells) -> None:
+        """The kernel prepared by begin_split has been queued: its predecessors move one stage on."""
+        self.to_collect = self.to_fold
+        self.to_fold = (seq, self.split_count % MB_RING, grid, partials, list(cells))
+        self.split_count += 1
+        self.pending = [x for x in (self.to_collect, self.to_fold) if x]
+
+    @staticmethod
+    def _fill(e: "Pending", rec) -> None:
+        if rec is None:
             e.seq, e.nv = 0, 0
-        return e
-
-    def posted(self, seq: int, cells) -> None:
-        """A kernel that collects `self.pending` and posts launch `seq` has been queued."""
-        self.pending = [(seq, list(cells))]
+            return
+        seq, slot, grid, partials, cells = rec
+        e.seq, e.nv, e.grid, e.slot, e.partials = seq, len(cells), grid, slot, partials
+        for v, (ptr, op, ty) in enumerate(cells):
+            e.cell[v], e.op[v], e.ty[v] = ptr, op, ty
 
     def flush(self, stream: int | None = None) -> None:
-        """Collect the totals of split-phase launches that no later kernel has collected; afterwards the
-        shared(...) cells of every loop launched so far hold their final values (once the stream has run).
-        Collective: every rank calls it at the same point of its launch sequence."""
-        import ctypes as C
-        if not self.pending:
-            return
+        """Complete the split-phase launches that no later kernel serves: a one-warp kernel folds and posts
+        the last launch and collects the one before it, a second one collects the last launch.  Afterwards
+        (once the stream has run) the shared(...) cells of every loop launched so far hold their final
+        values.  Collective: every rank calls it at the same point of its launch sequence."""
         if stream is None:
             import torch
             stream = torch.cuda.current_stream().cuda_stream
-        p = self.pending_struct()
-        rt.check(rt.lib().appy_p2p_flush(self._ctx, C.byref(p), C.c_void_p(stream)))
+        while self.to_fold or self.to_collect:
+            p = Pending2()
+            self._fill(p.fold, self.to_fold)
+            self._fill(p.coll, self.to_collect)
+            rt.check(rt.lib().appy_p2p_flush(self._ctx, _C.byref(p), _C.c_void_p(stream)))
+            self.to_collect, self.to_fold = self.to_fold, None
         self.pending = []
 
     def timed_out(self) -> bool:

@@ -49,7 +49,11 @@ int fail(int code, const char* fmt, ...) {
                   __FILE__, __LINE__);                                                    \
   } while (0)
 
-const size_t kWorkspaceBytes = 256 + 8 * 4 * 65536;  // ticket + 4 variables x 65536 CTAs
+// ticket + 4 variables x 65536 CTAs of the ordered commit, then the partials of split-phase launches:
+// two parities x 4 variables x 4096 CTAs
+const size_t kWorkspaceSplitOffset = 256 + 8 * 4 * 65536;
+const size_t kWorkspaceSplitBytes = 2 * 8 * 4 * 4096;
+const size_t kWorkspaceBytes = kWorkspaceSplitOffset + kWorkspaceSplitBytes;
 
 struct DeviceState {
   bool ready = false;
@@ -960,12 +964,10 @@ int appy_p2p_combine(void* ctx, uint64_t seq, int op, int dtype, void* dvalues, 
 }  // extern "C"
 
 namespace {
-// One warp: collect the totals of an earlier launch that only posted them (split-phase exchange).
-__global__ void __launch_bounds__(32) k_p2p_flush(const appy_mailbox* mb, appy_pending pend) {
-  const appy_mb_view mv = appy_mb_open(mb);
-  appy_collect_regs regs;
-  appy_p2p_collect_begin(mv, pend, regs);
-  appy_p2p_collect_end(mv, pend, regs);
+// One warp: what the start of a split-phase kernel does for the launches before it (fold and post one,
+// collect the other), for launches that no later kernel serves.
+__global__ void __launch_bounds__(32) k_p2p_flush(const appy_mailbox* mb, appy_pending2 pend) {
+  appy_split_service(mb, pend);
 }
 }  // namespace
 
@@ -975,10 +977,14 @@ int appy_p2p_flush(void* ctx, const void* pending, void* stream) {
   if (!ctx || !pending) return fail(APPY_ERR_ARG, "appy_p2p_flush: NULL argument");
   P2PContext* c = static_cast<P2PContext*>(ctx);
   if (!c->opened) return fail(APPY_ERR_ARG, "appy_p2p_flush: appy_p2p_open has not been called");
-  appy_pending pend;
+  appy_pending2 pend;
   memcpy(&pend, pending, sizeof pend);
-  if (pend.seq != 0 && (pend.nv < 1 || pend.nv > 4))
-    return fail(APPY_ERR_ARG, "appy_p2p_flush: a pending launch must carry 1..4 variables");
+  const appy_pending* both[2] = {&pend.fold, &pend.coll};
+  for (const appy_pending* e : both)
+    if (e->seq != 0 && (e->nv < 1 || e->nv > 4 || e->slot < 0 || e->slot >= APPY_MB_RING))
+      return fail(APPY_ERR_ARG, "appy_p2p_flush: a pending launch must carry 1..4 variables and a ring slot");
+  if (pend.fold.seq != 0 && (pend.fold.grid < 1 || pend.fold.grid > 4096 || !pend.fold.partials))
+    return fail(APPY_ERR_ARG, "appy_p2p_flush: the launch to fold needs its partials and 1..4096 CTAs");
   k_p2p_flush<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const appy_mailbox*>(c->d_desc), pend);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(APPY_ERR_CUDA, "appy_p2p_flush launch failed: %s", cudaGetErrorString(e));

@@ -227,37 +227,50 @@ template <class Op, class T> APPY_DEV T appy_p2p_fold(const appy_mailbox* mb, u6
 // ---------------------------------------------------------------------------
 // Split-phase form of the exchange (`@jit(combine="p2p", defer=True)`).
 //
-// The exchange above makes every reduction kernel wait, in its tail, for the slowest rank and for one
-// NVLink round trip.  Here a kernel only POSTS its totals (stores into every rank's mailbox, its own
-// included) and leaves the shared(...) cells alone; the totals are COLLECTED one launch later, in the tail
-// of the next such kernel (or by the stand-alone flush kernel): by then the words have long arrived, so
-// the poll finds them at once, and the latency and the ranks' end-of-kernel skew hide behind that kernel's
-// own work.  The cells hold their final value once the collecting kernel has finished.
+// The exchange above makes every reduction kernel end with a chain of waits: the ordered commit (a fence, a
+// ticket, the last CTA's fold of all partials), then the slowest rank and one NVLink round trip.  Here the
+// kernel's tail is only what a single-GPU reduction has: every CTA stores its partial and is done.  The rest
+// moves to the START of the next two kernels, where one warp (warp 0 of the last CTA) does it beside the
+// kernel's own work:
+//   launch k      every CTA stores its partial (slot of parity k in the workspace);
+//   launch k + 1  that warp FOLDS the partials of launch k — complete, because launch k has ended — and POSTS
+//                 the GPU's totals: stores into every rank's mailbox, its own included;
+//   launch k + 2  that warp COLLECTS launch k: the ranks' words have long arrived, it folds them in rank
+//                 order and applies the result to the shared(...) cells.
+// A stand-alone one-warp kernel (flush) runs the same two steps for the launches that no later kernel
+// serves.  The cells of a loop hold their final value once the second launch after it, or the flush, has
+// run, and must be left alone until then.
 //
-// Posted words live in a ring of APPY_MB_RING slots per mailbox, indexed by the launch number, at byte
-// offset 4096 (after the two slots of the immediate exchange).  A rank collects launch s before it posts
-// launch s + 2 at the latest, and collecting s needs every rank's words of s, so no rank runs more than two
-// launches ahead of the slowest one and a slot is never overwritten before every rank has read it.
-// A collect is described by values alone (cell addresses, operator and type codes), because the kernel
-// that collects was generated for another loop than the one that posted.  Between a loop's launch and the
-// launch (or flush) that collects it, its cells must be left alone: they are read when the collect begins
-// and written when it ends.
+// Posted words live in a ring of APPY_MB_RING slots per mailbox, indexed by the count of split-phase
+// launches, at byte offset 4096 (after the two slots of the immediate exchange).  A rank posts launch k + 8
+// only after it collected k + 6, which needs every rank's words of k + 6, posted after those ranks read k:
+// a slot is never overwritten unread.  A launch is described by values alone (cell addresses, operator and
+// type codes, the address and number of its partials), because the kernel that serves it was generated for
+// another loop.
 // ---------------------------------------------------------------------------
 #define APPY_MB_RING 8
 enum { APPY_PEND_ADD = 0, APPY_PEND_MUL = 1, APPY_PEND_MAX = 2, APPY_PEND_MIN = 3 };
 enum { APPY_PEND_F32 = 0, APPY_PEND_F64 = 1, APPY_PEND_I32 = 2, APPY_PEND_I64 = 3 };
 
-struct appy_pending {      // one earlier launch whose totals are still to be collected; seq == 0: none
-  u64 seq;
-  int nv;                  // variables of that launch (1..4)
+struct appy_pending {      // one earlier split-phase launch; seq == 0: none
+  u64 seq;                 // its launch number (the tag of its words)
+  int nv;                  // its shared(...) variables (1..4)
+  int grid;                // its CTAs = partials per variable
+  int slot;                // its ring slot
   int pad;
+  void* partials;          // its partials: variable r in the 8-byte cells [r*grid, (r+1)*grid)
   void* cell[4];           // the shared(...) cells, in this GPU's memory
   int op[4];               // APPY_PEND_ADD ..
   int ty[4];               // APPY_PEND_F32 ..
 };
+struct appy_pending2 {
+  appy_pending fold;       // the launch before this one: fold its partials and post the totals
+  appy_pending coll;       // the launch before that: collect the ranks' totals into its cells
+  void* partials;          // where THIS launch's CTAs store their partials
+};
 
-APPY_DEV u64* appy_mb_ring_words(u64* mailbox, u64 seq, int world, int src) {
-  return mailbox + 512 + ((seq % APPY_MB_RING) * (u64)world + src) * 8;
+APPY_DEV u64* appy_mb_ring_words(u64* mailbox, int slot, int world, int src) {
+  return mailbox + 512 + ((u64)slot * (u64)world + src) * 8;
 }
 
 template <class T> APPY_DEV T appy_fold_any(int op, T a, T b) {
@@ -271,6 +284,18 @@ APPY_DEV u64 appy_fold_bits(int op, int ty, u64 a, u64 b) {
   if (ty == APPY_PEND_F64) return appy_to_bits<double>(appy_fold_any<double>(op, appy_from_bits<double>(a), appy_from_bits<double>(b)));
   if (ty == APPY_PEND_I32) return appy_to_bits<int>(appy_fold_any<int>(op, appy_from_bits<int>(a), appy_from_bits<int>(b)));
   return appy_to_bits<i64>(appy_fold_any<i64>(op, appy_from_bits<i64>(a), appy_from_bits<i64>(b)));
+}
+template <class T> APPY_DEV u64 appy_identity_of(int op) {
+  if (op == APPY_PEND_ADD) return appy_to_bits<T>(appy_add::id<T>());
+  if (op == APPY_PEND_MUL) return appy_to_bits<T>(appy_mul::id<T>());
+  if (op == APPY_PEND_MAX) return appy_to_bits<T>(appy_max::id<T>());
+  return appy_to_bits<T>(appy_min::id<T>());
+}
+APPY_DEV u64 appy_identity_bits(int op, int ty) {
+  if (ty == APPY_PEND_F32) return appy_identity_of<float>(op);
+  if (ty == APPY_PEND_F64) return appy_identity_of<double>(op);
+  if (ty == APPY_PEND_I32) return appy_identity_of<int>(op);
+  return appy_identity_of<i64>(op);
 }
 
 // The descriptor's fields read once, all loads independent of one another (it lives in device memory, and
@@ -293,79 +318,101 @@ APPY_DEV appy_mb_view appy_mb_open(const appy_mailbox* mb) {
   return v;
 }
 
-// Called by the 32 threads of warp 0: lane r stores this rank's totals of launch `seq` into rank r's ring.
-template <int NV> APPY_DEV void appy_p2p_post(const appy_mb_view& mv, u64 seq, const u64 (&x)[NV]) {
-  const int lane = threadIdx.x & 31;
-  if (lane < mv.world) {
-    const u64 tag = (u64)((unsigned)seq | 0x80000000u) << 32;
-    u64* dst = appy_mb_ring_words(mv.to, seq, mv.world, mv.rank);
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      appy_st_relaxed_sys(dst + 2 * v, tag | (x[v] & 0xffffffffull));
-      appy_st_relaxed_sys(dst + 2 * v + 1, tag | (x[v] >> 32));
-    }
+// What a CTA of a split-phase kernel does in its tail: thread 0 stores the CTA's partial of variable `var`.
+template <class T> APPY_DEV void appy_split_publish(void* partials, int var, T v) {
+  if (threadIdx.x == 0) {
+    T* cell = reinterpret_cast<T*>(reinterpret_cast<double*>(partials) + (size_t)var * gridDim.x + blockIdx.x);
+    __stcg(cell, v);
   }
 }
 
-// Collecting launch p.seq, in two halves so that the memory latencies of the first hide behind whatever the
-// caller does in between (the kernels fold their own partials there).  Called by the 32 threads of warp 0.
-// begin: lane r reads rank r's words of that launch from this rank's own mailbox, lane 0 reads the cells.
 struct appy_collect_regs { u64 lo[4], hi[4], cell[4]; };
-APPY_DEV void appy_p2p_collect_begin(const appy_mb_view& mv, const appy_pending& p, appy_collect_regs& r) {
-  if (p.seq == 0) return;
+
+// Called by the 32 threads of one warp (warp 0 of the last CTA at the start of a split-phase kernel, or the flush
+// kernel): folds and posts p.fold, collects p.coll.  The reads that the collect needs go out first, so that
+// their latency hides behind the fold.  A wait that runs out sets the error word and turns floating-point
+// results into NaN, as in the immediate exchange.
+APPY_DEV void appy_split_service(const appy_mailbox* mb, const appy_pending2& p) {
+  if (p.fold.seq == 0 && p.coll.seq == 0) return;
   const int lane = threadIdx.x & 31;
-  const u64* src = appy_mb_ring_words(mv.own, p.seq, mv.world, lane < mv.world ? lane : 0);
+  const appy_mb_view mv = appy_mb_open(mb);
+  appy_collect_regs r;
+  const appy_pending& c = p.coll;
+  const u64* src = appy_mb_ring_words(mv.own, c.slot, mv.world, lane < mv.world ? lane : 0);
+  if (c.seq != 0) {
 #pragma unroll
-  for (int v = 0; v < 4; ++v) {
-    if (v < p.nv) {
-      r.lo[v] = appy_ld_relaxed_sys(src + 2 * v);
-      r.hi[v] = appy_ld_relaxed_sys(src + 2 * v + 1);
-      if (lane == 0) {
-        if (p.ty[v] == APPY_PEND_F32 || p.ty[v] == APPY_PEND_I32) r.cell[v] = (u64)*reinterpret_cast<const unsigned*>(p.cell[v]);
-        else r.cell[v] = *reinterpret_cast<const u64*>(p.cell[v]);
+    for (int v = 0; v < 4; ++v) {
+      if (v < c.nv) {
+        r.lo[v] = appy_ld_relaxed_sys(src + 2 * v);
+        r.hi[v] = appy_ld_relaxed_sys(src + 2 * v + 1);
+        if (lane == 0) {
+          if (c.ty[v] == APPY_PEND_F32 || c.ty[v] == APPY_PEND_I32) r.cell[v] = (u64)*reinterpret_cast<const unsigned*>(c.cell[v]);
+          else r.cell[v] = *reinterpret_cast<const u64*>(c.cell[v]);
+        }
       }
     }
   }
-}
-// end: waits (bounded) for words that had not arrived yet, folds the ranks' totals in rank order and applies
-// the result to the cells.  A wait that runs out sets the error word and turns floating-point results into
-// NaN, as in the immediate exchange.
-APPY_DEV void appy_p2p_collect_end(const appy_mb_view& mv, const appy_pending& p, appy_collect_regs& r) {
-  if (p.seq == 0) return;
-  const int world = mv.world, lane = threadIdx.x & 31;
-  const u64 tag = (u64)((unsigned)p.seq | 0x80000000u) << 32;
-  const u64* src = appy_mb_ring_words(mv.own, p.seq, world, lane < world ? lane : 0);
-  unsigned spins = 0;
-  bool ok = true;
+  // ---- fold the partials of the previous launch (fixed order: lane l takes cells l, l+32, ..; then the
+  // lanes are folded by a butterfly), and post the totals
+  const appy_pending& f = p.fold;
+  if (f.seq != 0) {
+    const u64 tag = (u64)((unsigned)f.seq | 0x80000000u) << 32;
+    u64* dst = appy_mb_ring_words(mv.to, f.slot, mv.world, mv.rank);
 #pragma unroll
-  for (int v = 0; v < 4; ++v) {
-    if (v < p.nv) {
-      u64 lo = r.lo[v], hi = r.hi[v];
-      if (lane < world) {
-        while (((lo ^ tag) >> 32) != 0 || ((hi ^ tag) >> 32) != 0) {
-          if (!ok || ++spins > mv.limit) {
-            ok = false;
-            break;
-          }
-          __nanosleep(spins < 256 ? 20 : 1000);
-          lo = appy_ld_relaxed_sys(src + 2 * v);
-          hi = appy_ld_relaxed_sys(src + 2 * v + 1);
+    for (int v = 0; v < 4; ++v) {
+      if (v < f.nv) {
+        const int op = f.op[v], ty = f.ty[v];
+        const bool narrow = ty == APPY_PEND_F32 || ty == APPY_PEND_I32;
+        const u64* cells = reinterpret_cast<const u64*>(f.partials) + (size_t)v * f.grid;
+        u64 acc = appy_identity_bits(op, ty);
+        for (int b = lane; b < f.grid; b += 32) {
+          const u64 raw = __ldcg(cells + b);
+          acc = appy_fold_bits(op, ty, acc, narrow ? (raw & 0xffffffffull) : raw);
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) acc = appy_fold_bits(op, ty, acc, __shfl_xor_sync(0xffffffffu, acc, m));
+        if (lane < mv.world) {
+          appy_st_relaxed_sys(dst + 2 * v, tag | (acc & 0xffffffffull));
+          appy_st_relaxed_sys(dst + 2 * v + 1, tag | (acc >> 32));
         }
       }
-      const bool all_ok = __all_sync(0xffffffffu, ok) != 0;
-      const u64 mine = (hi << 32) | (lo & 0xffffffffull);
-      u64 total = __shfl_sync(0xffffffffu, mine, 0);
-      for (int q = 1; q < world; ++q) total = appy_fold_bits(p.op[v], p.ty[v], total, __shfl_sync(0xffffffffu, mine, q));
-      if (lane == 0) {
-        const int ty = p.ty[v];
-        if (!all_ok) {
-          atomicExch(mv.err, 1u);
-          if (ty == APPY_PEND_F32) total = appy_to_bits<float>(appy_p2p_poison<float>(0.f));
-          if (ty == APPY_PEND_F64) total = appy_to_bits<double>(appy_p2p_poison<double>(0.0));
+    }
+  }
+  // ---- collect: words that had not arrived yet are waited for (bounded)
+  if (c.seq != 0) {
+    const u64 tag = (u64)((unsigned)c.seq | 0x80000000u) << 32;
+    unsigned spins = 0;
+    bool ok = true;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      if (v < c.nv) {
+        u64 lo = r.lo[v], hi = r.hi[v];
+        if (lane < mv.world) {
+          while (((lo ^ tag) >> 32) != 0 || ((hi ^ tag) >> 32) != 0) {
+            if (!ok || ++spins > mv.limit) {
+              ok = false;
+              break;
+            }
+            __nanosleep(spins < 256 ? 20 : 1000);
+            lo = appy_ld_relaxed_sys(src + 2 * v);
+            hi = appy_ld_relaxed_sys(src + 2 * v + 1);
+          }
         }
-        const u64 res = appy_fold_bits(p.op[v], ty, r.cell[v], total);
-        if (ty == APPY_PEND_F32 || ty == APPY_PEND_I32) *reinterpret_cast<unsigned*>(p.cell[v]) = (unsigned)res;
-        else *reinterpret_cast<u64*>(p.cell[v]) = res;
+        const bool all_ok = __all_sync(0xffffffffu, ok) != 0;
+        const u64 mine = (hi << 32) | (lo & 0xffffffffull);
+        u64 total = __shfl_sync(0xffffffffu, mine, 0);
+        for (int q = 1; q < mv.world; ++q) total = appy_fold_bits(c.op[v], c.ty[v], total, __shfl_sync(0xffffffffu, mine, q));
+        if (lane == 0) {
+          const int ty = c.ty[v];
+          if (!all_ok) {
+            atomicExch(mv.err, 1u);
+            if (ty == APPY_PEND_F32) total = appy_to_bits<float>(appy_p2p_poison<float>(0.f));
+            if (ty == APPY_PEND_F64) total = appy_to_bits<double>(appy_p2p_poison<double>(0.0));
+          }
+          const u64 res = appy_fold_bits(c.op[v], ty, r.cell[v], total);
+          if (ty == APPY_PEND_F32 || ty == APPY_PEND_I32) *reinterpret_cast<unsigned*>(c.cell[v]) = (unsigned)res;
+          else *reinterpret_cast<u64*>(c.cell[v]) = res;
+        }
       }
     }
   }

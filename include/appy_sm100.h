@@ -164,12 +164,18 @@ int appy_p2p_destroy(void* ctx);
 enum { APPY_OP_ADD = 0, APPY_OP_MUL = 1, APPY_OP_MAX = 2, APPY_OP_MIN = 3 };
 enum { APPY_F32 = 0, APPY_F64 = 1, APPY_I32 = 2, APPY_I64 = 3 };
 int appy_p2p_combine(void* ctx, uint64_t seq, int op, int dtype, void* dvalues, int count, void* stream);
-/* Split-phase form of the exchange: kernels generated with `combine="p2p", defer=True` only post their
- * totals and collect those of the launch before them, so that no kernel waits for the slowest rank or
- * for an NVLink round trip.  appy_p2p_flush runs the collect for launches that no later kernel has
- * collected yet; `pending` points to one record {uint64 seq (0 = none); int32 nv; int32 pad;
- * void* cell[4]; int32 op[4] (APPY_OP_*); int32 dtype[4] (APPY_F32..)} as the kernels take it.
- * Collective like the kernels themselves: every rank flushes at the same point of its launch sequence.
+/* Split-phase form of the exchange: kernels generated with `combine="p2p", defer=True` end like a
+ * single-GPU reduction (every CTA stores its partial); one warp at the start of the next such kernel folds
+ * those partials and posts the GPU's totals, and one launch later collects the ranks' totals into the
+ * shared(...) cells, so that no kernel ends waiting for the slowest rank or for an NVLink round trip.
+ * appy_p2p_flush runs those two steps for launches that no later kernel serves (call it twice to complete
+ * the last launch: once to fold and post it, once to collect it).  `pending` points to
+ *   struct { record fold, coll; void* unused; }   with
+ *   record = { uint64 seq (0 = none); int32 nv, grid, slot, pad; void* partials; void* cell[4];
+ *              int32 op[4] (APPY_OP_*); int32 dtype[4] (APPY_F32..) }
+ * as the kernels take it; a launch's partials live in the stream's workspace (appy_workspace) from byte
+ * 256 + 8*4*65536 on, 8*4*4096 bytes per launch parity.  Collective like the kernels themselves: every
+ * rank flushes at the same point of its launch sequence.
  * (The reference has no multi-GPU path; north_star asks for the combine of shared(...) scalars.) */
 int appy_p2p_flush(void* ctx, const void* pending, void* stream);
 

@@ -197,9 +197,11 @@ def test_split_phase_exchange_compiles():
     scope = dict(a=A1, s=np.array([0.0]), m=np.array([0.0], f32), n=1000)
     plan, code = build(src, scope, combine="p2p", defer=True)
     assert [p.kind for p in plan.params][-3:] == ["mb", "seq", "pend"]
-    assert "appy_p2p_post<2>(__mv, __seq, __x);" in code and "appy_p2p_collect_end(__mv, __pend, __cr);" in code
-    assert code.index("appy_p2p_collect_begin") < code.index("appy_ws_collect<")       # reads go out before the local fold
-    assert "appy_p2p_exchange" not in code.split("struct kernel_loop_1_body")[1]
+    # the tail of a CTA is two stores; the exchange is served by one warp at the top of the kernel
+    assert "appy_split_publish<double>(__pend.partials, 0," in code and "appy_split_publish<float>(__pend.partials, 1," in code
+    body = code.split("struct kernel_loop_1_body")[1]
+    assert "appy_ws_arrive" not in body and "appy_p2p_exchange" not in body
+    assert body.index("blockIdx.x == gridDim.x - 1 && threadIdx.x < 32) appy_split_service(__mb, __pend);") < body.index("appy_flat<")
     plan, code = build(src, scope, combine="p2p")
     assert "appy_p2p_exchange<2>" in code and "pend" not in [p.kind for p in plan.params]
 

@@ -103,8 +103,8 @@ def count_into(a, out_n):
 
 
 def test_split_phase_exchange_on_one_rank(rt):
-    """defer=True: a kernel posts its totals and collects those of the launch before it; the cells are final
-    once the next such kernel, or flush(), has run."""
+    """defer=True: a kernel only stores its CTAs' partials; the first warp of the next such kernel folds and
+    posts them, the one after that collects the ranks' totals into the cells (or flush() does both)."""
     mg.set_combiner(None)
     c = mg.enable_p2p()
     try:
@@ -113,23 +113,28 @@ def test_split_phase_exchange_on_one_rank(rt):
         s = torch.full((1,), 2.0, dtype=torch.float64, device="cuda")
         m = torch.full((1,), -1.0, dtype=torch.float32, device="cuda")
         n = torch.zeros(1, dtype=torch.int64, device="cuda")
-        sum_and_max_into(da, s, m)
+        total, big, cnt = float(np.sum(a, dtype=np.float64)), float(a.max()), int((a > 0.5).sum())
+        sum_and_max_into(da, s, m)              # launch 1: partials stored
+        count_into(da, n)                       # launch 2: folds and posts launch 1
         torch.cuda.synchronize()
-        assert s.item() == 2.0 and m.item() == -1.0 and len(c.pending) == 1       # posted, not collected yet
-        count_into(da, n)                       # collects the launch before it, posts its own
+        assert s.item() == 2.0 and m.item() == -1.0 and n.item() == 0 and len(c.pending) == 2
+        count_into(da, n)                       # launch 3: collects launch 1, folds and posts launch 2
         torch.cuda.synchronize()
-        assert np.isclose(s.item(), 2.0 + float(np.sum(a, dtype=np.float64)), rtol=1e-5) and m.item() == float(a.max())
-        assert n.item() == 0 and len(c.pending) == 1
+        assert np.isclose(s.item(), 2.0 + total, rtol=1e-5) and m.item() == big and n.item() == 0
         c.flush()
         torch.cuda.synchronize()
-        assert n.item() == int((a > 0.5).sum()) and c.pending == []
+        assert n.item() == 2 * cnt and c.pending == []
         for _ in range(12):                     # more launches than the ring has slots
             sum_and_max_into(da, s, m)
             count_into(da, n)
         c.flush()
         torch.cuda.synchronize()
-        assert np.isclose(s.item(), 2.0 + 13 * float(np.sum(a, dtype=np.float64)), rtol=1e-5)
-        assert n.item() == 13 * int((a > 0.5).sum()) and not c.timed_out()
+        assert np.isclose(s.item(), 2.0 + 13 * total, rtol=1e-5) and m.item() == big
+        assert n.item() == 14 * cnt and not c.timed_out()
+        sum_and_max_into(da, s, m)              # a single launch, completed by the flush alone
+        c.flush()
+        torch.cuda.synchronize()
+        assert np.isclose(s.item(), 2.0 + 14 * total, rtol=1e-5)
         with pytest.raises(NotImplementedError, match="device memory"):
             sum_and_max_into(a, np.zeros(1), np.zeros(1, np.float32))      # host cells cannot be deferred
     finally:
@@ -144,10 +149,10 @@ def test_split_phase_collect_times_out_with_a_status(rt):
         da = torch.from_numpy(W.vec_sum(1 << 16, seed=5)).cuda()
         s = torch.zeros(1, dtype=torch.float64, device="cuda")
         m = torch.zeros(1, dtype=torch.float32, device="cuda")
-        sum_and_max_into(da, s, m)              # posts only: nothing to wait for
+        sum_and_max_into(da, s, m)              # stores its partials: nothing to wait for
         torch.cuda.synchronize()
         assert not c.timed_out()
-        c.flush()                               # rank 1 never posts: the bounded wait runs out
+        c.flush()                               # folds, posts, then collects: rank 1 never posts, the bounded wait runs out
         torch.cuda.synchronize()
         assert np.isnan(s.item()) and np.isnan(m.item()) and c.timed_out()
         assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0            # the context is still usable
