@@ -681,7 +681,10 @@ class CompiledLoop:
             cache = self.__dict__.setdefault("_row_split", {})
             if key not in cache:
                 host = ip.obj if ip.host else ip.obj.detach().cpu().numpy()
-                b = rt.partition_rows(np.ascontiguousarray(host[lo:hi + 1]), world_size)
+                # a row costs the row-reduction kernel about as much as eight of its non-zeros (pointer loads,
+                # the group's reduction, the store) and the row-times-dense kernel about one (the C row's store)
+                row_cost = int(self.options.get("_row_cost", 8 if plan.kind == "csr" else 1))
+                b = rt.partition_rows(np.ascontiguousarray(host[lo:hi + 1]), world_size, row_cost)
                 if len(cache) > 64:
                     cache.clear()
                 cache[key] = [lo + x for x in b]
@@ -1074,7 +1077,7 @@ def _register_finalizer(obj, hptr: int) -> None:
 
 _OPTION_KEYS = ("ordered_reduction", "combine", "defer", "distribute", "fp_contract", "autotune", "pin_host", "_generic_only", "_vectorize",
                 "_stream_hint", "_hoist_safe", "_shape_spec", "_neighbours", "_bulk_rows", "_group_vectorize",
-                "_spmm_stream", "_stream_rows")
+                "_spmm_stream", "_stream_rows", "_row_cost")
 
 
 _site_options: dict = {}       # site number -> option key; the loops of one rewritten function always pass the same options

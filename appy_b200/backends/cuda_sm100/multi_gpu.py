@@ -34,9 +34,10 @@ def split_range(lo: int, hi: int, world_size: int, rank: int, align: int = 32):
     return b[rank], b[rank + 1]
 
 
-def split_rows(indptr, world_size: int, rank: int):
-    """This rank's contiguous row range of a CSR matrix, balanced by non-zero count."""
-    b = rt.partition_rows(np.asarray(indptr), world_size)
+def split_rows(indptr, world_size: int, rank: int, row_cost: int = 0):
+    """This rank's contiguous row range of a CSR matrix, balanced by non-zero count plus `row_cost` per row
+    (`@jit(distribute=True)` uses 8 for row reductions such as SpMV and 1 for row-times-dense loops)."""
+    b = rt.partition_rows(np.asarray(indptr), world_size, row_cost)
     return b[rank], b[rank + 1]
 
 

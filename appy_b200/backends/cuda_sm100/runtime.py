@@ -56,6 +56,8 @@ SIGNATURES = {
                                        C.POINTER(C.c_int64)]),
     "appy_partition_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int,
                                       C.POINTER(C.c_int64)]),
+    "appy_partition_rows_weighted": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int64,
+                                               C.POINTER(C.c_int64)]),
     "appy_row_histogram": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.POINTER(C.c_int64),
                                      C.POINTER(C.c_int64), C.c_void_p]),
     "appy_p2p_create": (C.c_int, [C.c_int, C.c_int, c_void_pp, C.c_void_p]),
@@ -296,14 +298,16 @@ def partition_range(lo: int, hi: int, parts: int, align: int = 1) -> list[int]:
     return list(out)
 
 
-def partition_rows(indptr, parts: int) -> list[int]:
-    """nnz-balanced contiguous row split; `indptr` is a host numpy int32/int64 array."""
+def partition_rows(indptr, parts: int, row_cost: int = 0) -> list[int]:
+    """Contiguous row split balanced by non-zeros plus `row_cost` per row; `indptr` is a host numpy
+    int32/int64 array."""
     import numpy as np
     ip = np.ascontiguousarray(indptr)
     if ip.dtype not in (np.int32, np.int64):
         ip = ip.astype(np.int64)
     out = (C.c_int64 * (parts + 1))()
-    check(lib().appy_partition_rows(C.c_void_p(ip.ctypes.data), ip.dtype.itemsize, len(ip) - 1, parts, out))
+    check(lib().appy_partition_rows_weighted(C.c_void_p(ip.ctypes.data), ip.dtype.itemsize, len(ip) - 1, parts,
+                                             row_cost, out))
     return list(out)
 
 

@@ -813,30 +813,38 @@ int appy_partition_range(int64_t lo, int64_t hi, int parts, int64_t align, int64
   return APPY_OK;
 }
 
-int appy_partition_rows(const void* indptr, int idx_bytes, int64_t nrows, int parts,
-                        int64_t* bounds) {
-  if (!indptr || parts <= 0 || !bounds || nrows < 0 || (idx_bytes != 4 && idx_bytes != 8))
+int appy_partition_rows_weighted(const void* indptr, int idx_bytes, int64_t nrows, int parts, int64_t row_cost,
+                                 int64_t* bounds) {
+  if (!indptr || parts <= 0 || !bounds || nrows < 0 || row_cost < 0 || (idx_bytes != 4 && idx_bytes != 8))
     return fail(APPY_ERR_ARG, "bad partition arguments");
   auto at = [&](int64_t i) -> int64_t {
     return idx_bytes == 4 ? (int64_t) static_cast<const int32_t*>(indptr)[i]
                           : static_cast<const int64_t*>(indptr)[i];
   };
-  const int64_t first = at(0), nnz = at(nrows) - first;
+  // cost of rows [0, i): their non-zeros plus row_cost per row; non-decreasing in i
+  const int64_t first = at(0);
+  auto cost = [&](int64_t i) -> int64_t { return at(i) - first + row_cost * i; };
+  const int64_t total = cost(nrows);
   bounds[0] = 0;
   for (int p = 1; p < parts; ++p) {
-    const int64_t target = first + (int64_t)((__int128)nnz * p / parts);
-    // first row r with indptr[r] >= target
+    const int64_t target = (int64_t)((__int128)total * p / parts);
+    // first row r with cost(r) >= target
     int64_t a = bounds[p - 1], b = nrows;
     while (a < b) {
       const int64_t m = a + (b - a) / 2;
-      if (at(m) < target) a = m + 1; else b = m;
+      if (cost(m) < target) a = m + 1; else b = m;
     }
     // choose the nearer of the two neighbouring row boundaries
-    if (a > bounds[p - 1] && a <= nrows && (at(a) - target) > (target - at(a - 1))) --a;
+    if (a > bounds[p - 1] && a <= nrows && (cost(a) - target) > (target - cost(a - 1))) --a;
     bounds[p] = std::min(std::max(a, bounds[p - 1]), nrows);
   }
   bounds[parts] = nrows;
   return APPY_OK;
+}
+
+int appy_partition_rows(const void* indptr, int idx_bytes, int64_t nrows, int parts,
+                        int64_t* bounds) {
+  return appy_partition_rows_weighted(indptr, idx_bytes, nrows, parts, 0, bounds);
 }
 
 // ---------------------------------------------------------------- peer mailboxes (multi-GPU scalar combine)

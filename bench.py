@@ -231,6 +231,12 @@ def d_sum_into_p2p(a, out):
     for i in range(a.shape[0]):
         out[0] += a[i]
 
+@appy.jit(distribute=True, combine="p2p", defer=True)
+def d_sum_into_split(a, out):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        out[0] += a[i]
+
 @appy.jit(distribute=True)
 def d_sum_into(a, out):
     #pragma parallel for simd
@@ -330,17 +336,21 @@ def spmm(A_data, A_indptr, A_indices, B, y, M):
     return mod
 
 
-def time_kernel(torch, fn, rot: int, iters: int, warm: int = 3):
+def time_kernel(torch, fn, rot: int, iters: int, warm: int = 3, after=None):
     """Average device time (us) of one call of fn(i), with CUDA events on the current stream.
     Every one of the `rot` rotating input sets is used at least once before the timed calls, so that
     no first call of a set (launch record, row-length profile, row partition) falls inside them."""
     for i in range(max(warm, rot)):
         fn(i % rot)
+    if after is not None:
+        after()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(iters):
         fn(i % rot)
+    if after is not None:       # work that completes the timed calls (the flush of a split-phase exchange)
+        after()
     e1.record()
     e1.synchronize()
     return e0.elapsed_time(e1) * 1e3 / iters
@@ -514,9 +524,9 @@ def strong_table(torch, L, peak, rank, world, quick=False, use_p2p=True):
     def copies(per_gpu_bytes):
         return int(max(2, min(24, -(-2.2 * L2 // max(per_gpu_bytes, 1)))))
 
-    def both(name, byts, one_fn, dist_fn, rot, iters, note):
+    def both(name, byts, one_fn, dist_fn, rot, iters, note, after=None):
         t1 = time_kernel(torch, one_fn, rot, max(4, iters // 2))
-        tn = time_kernel(torch, dist_fn, rot, iters)
+        tn = time_kernel(torch, dist_fn, rot, iters, after=after)
         t = torch.tensor([t1, tn], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         t1, tn = float(t[0]), float(t[1])
@@ -541,12 +551,19 @@ def strong_table(torch, L, peak, rank, world, quick=False, use_p2p=True):
     rot = copies(W.bytes_sum(n) / world)
     das = [torch.from_numpy(av).to(dev) for _ in range(rot)]
     cell = torch.zeros(1, dtype=torch.float64, device=dev)
-    d_sum = L.d_sum_into_p2p if use_p2p else L.d_sum_into
+    d_sum = L.d_sum_into_split if use_p2p else L.d_sum_into
+    flush = None
+    if use_p2p:
+        from appy_b200.backends.cuda_sm100 import multi_gpu as _mg
+        flush = _mg.combiner().flush
     both("C2a sum f32 n=2^26", W.bytes_sum(n), lambda i: L.sum_into(das[i], cell), lambda i: d_sum(das[i], cell),
          rot, 8 * rot, "contiguous index ranges; the scalar is combined " +
-         ("in the kernel's tail over peer mailboxes" if use_p2p else "by an NCCL all-reduce"))
+         ("over peer mailboxes, split phase (posted and collected by the following launches, the last ones by a "
+          "flush inside the timed region)" if use_p2p else "by an NCCL all-reduce"), after=flush)
     cell.zero_()
     d_sum(das[0], cell)
+    if flush is not None:
+        flush()
     assert np.isclose(float(cell.item()), float(np.sum(av, dtype=np.float64)), rtol=1e-5)
     del das
     # C4

@@ -135,6 +135,12 @@ int appy_partition_range(int64_t lo, int64_t hi, int parts, int64_t align, int64
  * entries (idx_bytes = 4 or 8). */
 int appy_partition_rows(const void* indptr, int idx_bytes, int64_t nrows, int parts,
                         int64_t* bounds);
+/* The same with a fixed cost per row beside its non-zeros: the ranges are balanced by
+ * (non-zeros + row_cost * rows).  A row costs a kernel its pointer loads, its reduction and its store
+ * whatever its length, so a range of many short rows takes longer than its non-zeros say; row_cost = 0
+ * is appy_partition_rows.  (The reference is single-GPU; north_star asks for nnz-balanced row splits.) */
+int appy_partition_rows_weighted(const void* indptr, int idx_bytes, int64_t nrows, int parts, int64_t row_cost,
+                                 int64_t* bounds);
 /* Row-length histogram of a device-resident indptr: counts[b] = rows whose length
  * lies in [2^(b-1), 2^b) (b = 0: empty rows), 32 bins; also the longest row. */
 int appy_row_histogram(const void* d_indptr, int idx_bytes, int64_t nrows, int64_t* counts32,

@@ -50,3 +50,12 @@ def test_partition_rows_balances_nonzeros():
         assert max(per) - min(per) <= 2 * 500
     b64 = runtime.partition_rows(indptr.astype(np.int64), 4)
     assert b64 == runtime.partition_rows(indptr, 4)
+    # with a cost per row the ranges balance non-zeros + cost * rows: a range of short rows gets fewer rows
+    lens = np.concatenate([np.full(9000, 2), np.full(1000, 200)])
+    ip = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    for cost in (0, 8, 100):
+        b = runtime.partition_rows(ip, 4, cost)
+        assert b[0] == 0 and b[-1] == 10000 and all(x <= y for x, y in zip(b, b[1:]))
+        load = [int(ip[b[k + 1]] - ip[b[k]]) + cost * (b[k + 1] - b[k]) for k in range(4)]
+        assert max(load) - min(load) <= 200 + cost
+    assert runtime.partition_rows(ip, 4, 100)[1] < runtime.partition_rows(ip, 4, 0)[1]

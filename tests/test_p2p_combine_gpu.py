@@ -289,7 +289,7 @@ def _rank_main(rank, world, port, out_dir):
         yv = np.full(A.shape[0], np.nan, np.float32)
         cg.transfer_stats.update(h2d=0, d2h=0)
         d_spmv(A.data, A.indptr, A.indices, xv, yv, A.shape[0])
-        r0, r1 = mg.split_rows(A.indptr, world, rank)        # rows balanced by non-zeros
+        r0, r1 = mg.split_rows(A.indptr, world, rank, 8)     # rows balanced by non-zeros + 8 per row
         nnz_r = int(A.indptr[r1] - A.indptr[r0])             # data and indices in part, indptr and x whole
         assert cg.transfer_stats["h2d"] == 8 * nnz_r + A.indptr.nbytes + xv.nbytes + 4 * (r1 - r0)
         assert cg.transfer_stats["d2h"] == 4 * (r1 - r0)
@@ -307,7 +307,7 @@ def _rank_main(rank, world, port, out_dir):
         ys = np.full((As.shape[0], 128), np.nan, np.float32)
         cg.transfer_stats.update(h2d=0, d2h=0)
         d_spmm(As.data, As.indptr, As.indices, Bs, ys, As.shape[0])
-        r0, r1 = mg.split_rows(As.indptr, world, rank)
+        r0, r1 = mg.split_rows(As.indptr, world, rank, 1)
         nnz_r = int(As.indptr[r1] - As.indptr[r0])
         assert cg.transfer_stats["h2d"] == 8 * nnz_r + As.indptr.nbytes + Bs.nbytes + 4 * 128 * (r1 - r0)
         assert cg.transfer_stats["d2h"] == 4 * 128 * (r1 - r0)
