@@ -143,10 +143,14 @@ def _torch_stream(torch, device: int) -> int:
         return torch.cuda.current_stream().cuda_stream
 
 
+_cell_turn = [0]        # which 512-byte window of the page of host cells the next call uses
+_cell_pages: dict = {}  # device -> (host address, device address, bytes) of its page of host cells
+
+
 class _Array:
     """One array argument resolved for a launch."""
     __slots__ = ("name", "obj", "host", "dptr", "nbytes", "shape", "strides", "itemsize", "tmp", "hptr",
-                 "pinnable")
+                 "pinnable", "cell")
 
 
 class _DevView:
@@ -219,6 +223,51 @@ class CompiledLoop:
                                       if sg[0] == "S" and nm not in in_ranges)
         self.device = None
         self.sm_count = 148
+        self.cell_names = self._find_cell_names()
+
+    def _find_cell_names(self) -> frozenset:
+        """Arrays that the loop touches only as targets of its own reductions (`s[0] += ...`, what a
+        shared(...) scalar becomes).  When such an array arrives as a small host array it needs no device
+        mirror: the kernel is given a cell in mapped host memory (_host_cells)."""
+        from ...frontend.loop_normalize import reductions_of
+        targets = {}
+        for text in reductions_of(self.ir.loop):
+            node = ast.parse(text, mode="eval").body
+            if isinstance(node, ast.Subscript) and isinstance(node.value, ast.Name) \
+                    and isinstance(node.slice, ast.Constant):
+                targets.setdefault(node.value.id, set()).add(text)
+            elif isinstance(node, ast.Subscript) and isinstance(node.value, ast.Name):
+                targets.setdefault(node.value.id, set()).add(None)        # not a constant index: no cell
+        names = set()
+        for name, texts in targets.items():
+            if None in texts:
+                continue
+            ok = True
+            for st in ast.walk(self.ir.loop):
+                if isinstance(st, (ast.Assign, ast.AugAssign)):
+                    if not any(isinstance(x, ast.Name) and x.id == name for x in ast.walk(st)):
+                        continue
+                    tgt = st.targets[0] if isinstance(st, ast.Assign) else st.target
+                    if ast.unparse(tgt) not in texts:
+                        ok = False
+                elif isinstance(st, (ast.If, ast.While, ast.For)):
+                    head = st.test if not isinstance(st, ast.For) else st.iter
+                    if any(isinstance(x, ast.Name) and x.id == name for x in ast.walk(head)):
+                        ok = False
+            if ok:
+                names.add(name)
+        return frozenset(names)
+
+    def _host_cells(self, arrays) -> tuple:
+        """Names of the host arrays of this call that become cells in mapped host memory: reduction-only
+        targets (cell_names) of at most 64 bytes, at most eight per call; never in a distributed or
+        cross-GPU combining loop (their cells are exchanged through device memory)."""
+        if not self.cell_names or not self.options.get("_host_cells", True) or self.options.get("distribute") \
+                or self.options.get("combine"):
+            return ()
+        out = [a.name for a in arrays if a.host and a.name in self.cell_names and 0 < a.nbytes <= 64
+               and a.tmp is None]
+        return tuple(out[:8])
 
     # ------------------------------------------------------------------ specialisation
     def _resolve_arrays(self, args):
@@ -228,7 +277,7 @@ class CompiledLoop:
             if sig[0] != "A":
                 continue
             a = _Array()
-            a.name, a.obj, a.tmp, a.hptr = name, v, None, 0
+            a.name, a.obj, a.tmp, a.hptr, a.cell = name, v, None, 0, 0
             a.pinnable = sig[1] == "np"      # NumPy owners can be tracked by a finaliser; tensor views cannot
             if sig[1] == "cuda":
                 a.host = False
@@ -253,14 +302,32 @@ class CompiledLoop:
             arrays.append(a)
         return arrays
 
-    def _acquire_device(self, arrays, stream, slices=None):
+    def _acquire_device(self, arrays, stream, slices=None, hostcells=()):
         """Device mirrors of the host arrays, filled from the host.  `slices` (distributed loops):
-        {array name: (first byte, one past last byte)} for arrays of which this rank touches only a part."""
+        {array name: (first byte, one past last byte)} for arrays of which this rank touches only a part.
+        `hostcells`: names of arrays that get a cell in the device's page of mapped host memory instead
+        (the value is copied in by the CPU; the kernel reads and writes it over PCIe)."""
+        window = None
         for a in arrays:
+            a.cell = 0
             if not a.host:
                 continue
             if a.nbytes == 0:
                 a.dptr = 0
+                continue
+            if a.name in hostcells:
+                if window is None:      # this call's 512 bytes of the page: eight calls may be in flight
+                    page = _cell_pages.get(self.device)
+                    if page is None:
+                        page = _cell_pages[self.device] = rt.host_cells()
+                    base_h, base_d = page[0], page[1]
+                    _cell_turn[0] = turn = (_cell_turn[0] + 1) % 8
+                    window = [base_h + 512 * turn, base_d + 512 * turn]
+                C.memmove(window[0], a.hptr, a.nbytes)
+                a.cell, a.dptr = window[0], window[1]
+                window[0] += 64
+                window[1] += 64
+                transfer_stats["h2d"] += a.nbytes
                 continue
             a.dptr, created = rt.mirror(a.hptr, a.nbytes)
             state = _resident.get(a.hptr) if (_resident and not slices and a.tmp is None) else None
@@ -276,7 +343,7 @@ class CompiledLoop:
             _upload(a.dptr + b0, a.hptr + b0, b1 - b0, a.hptr, a.nbytes, a.obj,
                     a.tmp is None and a.pinnable and self.options.get("pin_host", True), stream)
 
-    def _spec_key(self, arrays):
+    def _spec_key(self, arrays, hostcells=()):
         key = []
         for a in arrays:
             nd = len(a.shape)
@@ -301,7 +368,7 @@ class CompiledLoop:
         shape_spec = ()
         if self.options.get("_shape_spec", True):
             shape_spec = tuple((a.name, a.shape[1]) for a in arrays if len(a.shape) == 2 and a.name in self.stored)
-        return (tuple(key), noalias, shape_spec)
+        return (tuple(key), noalias, shape_spec, tuple(hostcells))
 
     def _variant(self, arrays, key) -> Variant:
         v = self.variants.get(key)
@@ -326,6 +393,10 @@ class CompiledLoop:
         opts = dict(self.options)
         opts["_noalias"] = key[1]
         opts["_shape"] = {(n, 1): s for n, s in key[2]}
+        if len(key) > 3 and key[3]:
+            # cells in mapped host memory: one read and one write per cell at the very end of the kernel
+            # (atomics on host memory would cross PCIe one by one)
+            opts["ordered_reduction"] = True
         import copy as _copy
         ir = _copy.deepcopy(self.ir)
         plan = Lowering(ir, self.kernel_name, infos, opts).lower()
@@ -537,7 +608,11 @@ class CompiledLoop:
             return dict(start, **store[tkey])
         # keep the stored arrays intact: run candidates, then restore
         saved = []
+        saved_cells = []        # cells in mapped host memory are saved and restored by the CPU
         for a in arrays:
+            if a.host and getattr(a, "cell", 0):
+                saved_cells.append((a, C.string_at(a.cell, a.nbytes)))
+                continue
             if a.name in self.stored:
                 ext = (sum((n - 1) * abs(s) for n, s in zip(a.shape, a.strides)) + 1) * a.itemsize if all(a.shape) else 0
                 if ext:
@@ -571,6 +646,8 @@ class CompiledLoop:
         rt.sync(stream)
         for _a, tmp, _e in saved:
             rt.free(tmp)
+        for a, raw in saved_cells:
+            C.memmove(a.cell, raw, a.nbytes)
         store[tkey] = best
         _tune_save()
         if os.environ.get("APPY_TUNE_LOG") == "1":
@@ -753,7 +830,7 @@ class CompiledLoop:
         for argi, name, _slot in slots:
             v = args[argi]
             a = _Array()
-            a.name, a.tmp = name, None
+            a.name, a.tmp, a.cell = name, None, 0
             a.pinnable = type(v) is np.ndarray or isinstance(v, np.ndarray)
             h = v if a.pinnable else v.numpy()
             a.obj, a.host, a.hptr, a.nbytes, a.dptr = h, True, h.ctypes.data, h.nbytes, 0
@@ -776,7 +853,7 @@ class CompiledLoop:
 
     def _replay(self, memo, args) -> bool:
         (handle, grid, block, smem, pack, seq_slot, memo_stream, cells, host_slots, scalar_slots, post, scratch,
-         deferred) = memo
+         deferred, hostcells) = memo
         torch = sys.modules.get("torch")
         if torch is not None and (self.has_device_args or not host_slots):
             stream = _torch_stream(torch, self.device)      # orders with the producers of the device tensors
@@ -786,7 +863,7 @@ class CompiledLoop:
         if not disjoint or not (memo_stream is None or memo_stream == stream):     # a workspace belongs to one stream
             return False
         if host_slots:        # mirrors of the host arrays: look up, upload, patch into the arguments
-            self._acquire_device(harr, stream)
+            self._acquire_device(harr, stream, None, hostcells)
             for a, (_argi, _name, slot) in zip(harr, host_slots):
                 pack.values[slot].value = a.dptr
         for argi, slot in scalar_slots:
@@ -813,10 +890,14 @@ class CompiledLoop:
             self._post_combine(cells)
         if host_slots:
             for a in harr:
-                if a.name in self.stored and a.nbytes:
+                if a.name in self.stored and a.nbytes and not a.cell:
                     rt.d2h(a.hptr, a.dptr, a.nbytes, stream)
                     transfer_stats["d2h"] += a.nbytes
             rt.sync(stream)
+            for a in harr:
+                if a.cell:
+                    C.memmove(a.hptr, a.cell, a.nbytes)
+                    transfer_stats["d2h"] += a.nbytes
         return True
 
     def __call__(self, *args):
@@ -842,9 +923,10 @@ class CompiledLoop:
             stream = rt.stream(0)
         from . import multi_gpu
         sharded = bool(self.options.get("distribute")) and any_host and multi_gpu.world()[1] > 1
+        hostcells = self._host_cells(arrays) if any_host else ()
         if not sharded:
-            self._acquire_device(arrays, stream)
-        key = self._spec_key(arrays)       # mirrors are 16-byte aligned whether or not they exist yet
+            self._acquire_device(arrays, stream, None, hostcells)
+        key = self._spec_key(arrays, hostcells)     # mirrors are 16-byte aligned whether or not they exist yet
         variant = self._variant(arrays, key)
         self.last_variant = variant
         scope = self._scope(args, arrays)
@@ -916,19 +998,23 @@ class CompiledLoop:
                                      if self.arg_names[i] in pslot)
                 self.memo[mkey] = (h, grid, block, smem, pack, seq_slot,
                                    stream if (variant.plan.uses_ws or any_host or scratch) else None, cells,
-                                   tuple(host_slots), scalar_slots, post, scratch, deferred)
+                                   tuple(host_slots), scalar_slots, post, scratch, deferred, hostcells)
         elif not any_host and mkey is not None:
-            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells, (), (), None, None, None)
+            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells, (), (), None, None, None, ())
         if cells:
             self._post_combine(cells)
         if any_host:
             for a in arrays:
-                if a.host and a.name in self.stored and a.nbytes:
+                if a.host and a.name in self.stored and a.nbytes and not a.cell:
                     b0, b1 = slices.get(a.name, (0, a.nbytes)) if slices else (0, a.nbytes)
                     if b1 > b0:
                         rt.d2h(a.hptr + b0, a.dptr + b0, b1 - b0, stream)
                         transfer_stats["d2h"] += b1 - b0
             rt.sync(stream)
+            for a in arrays:            # cells in mapped host memory: the kernel has written them
+                if a.host and a.cell:
+                    C.memmove(a.hptr, a.cell, a.nbytes)
+                    transfer_stats["d2h"] += a.nbytes
             for a in arrays:
                 if a.host and a.tmp is not None:
                     if a.name in self.stored:
@@ -953,7 +1039,7 @@ class CompiledLoop:
     # convenience for tests and dumps
     def source_for(self, *args) -> str:
         arrays = self._resolve_arrays(args)    # host arrays: dptr 0, mirrors are always aligned
-        return self._variant(arrays, self._spec_key(arrays)).plan.source
+        return self._variant(arrays, self._spec_key(arrays, self._host_cells(arrays))).plan.source
 
 
 def _upload(dst: int, src: int, nbytes: int, base: int, base_bytes: int, owner, may_pin: bool, stream: int) -> None:
@@ -1077,7 +1163,7 @@ def _register_finalizer(obj, hptr: int) -> None:
 
 _OPTION_KEYS = ("ordered_reduction", "combine", "defer", "distribute", "fp_contract", "autotune", "pin_host", "_generic_only", "_vectorize",
                 "_stream_hint", "_hoist_safe", "_shape_spec", "_neighbours", "_bulk_rows", "_group_vectorize",
-                "_spmm_stream", "_stream_rows", "_row_cost")
+                "_spmm_stream", "_stream_rows", "_row_cost", "_host_cells")
 
 
 _site_options: dict = {}       # site number -> option key; the loops of one rewritten function always pass the same options

@@ -37,6 +37,7 @@ SIGNATURES = {
     "appy_evict": (C.c_int, [C.c_void_p]),
     "appy_h2d_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "appy_d2h_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "appy_host_cells": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]),
     "appy_h2d_staged": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "appy_d2d_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "appy_compile": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, c_void_pp]),
@@ -191,6 +192,13 @@ def h2d_staged(dptr: int, hptr: int, nbytes: int, stream_: int = 0) -> None:
 
 def d2h(hptr: int, dptr: int, nbytes: int, stream_: int = 0) -> None:
     check(lib().appy_d2h_async(C.c_void_p(hptr), C.c_void_p(dptr), nbytes, C.c_void_p(stream_)))
+
+
+def host_cells() -> tuple[int, int, int]:
+    """(host address, device address, bytes) of the current device's page of mapped pinned memory."""
+    h, d, n = C.c_void_p(), C.c_void_p(), C.c_size_t()
+    check(lib().appy_host_cells(C.byref(h), C.byref(d), C.byref(n)))
+    return h.value, d.value, n.value
 
 
 def workspace(stream_: int = 0) -> int:

@@ -79,6 +79,10 @@ struct Staging {
 };
 Staging g_stage[16];
 
+const size_t kHostCellBytes = 4096;           // mapped pinned page for shared scalars (appy_host_cells)
+void* g_host_cells[16] = {nullptr};
+void* g_host_cells_dev[16] = {nullptr};
+
 int staging_for(int dev, Staging** out) {
   Staging& st = g_stage[dev];
   if (!st.buf[0]) {
@@ -361,6 +365,10 @@ int appy_shutdown(void) {
       if (g_stage[dev].buf[i]) { cudaFreeHost(g_stage[dev].buf[i]); g_stage[dev].buf[i] = nullptr; }
       if (g_stage[dev].done[i]) { cudaEventDestroy(g_stage[dev].done[i]); g_stage[dev].done[i] = nullptr; }
     }
+    if (g_host_cells[dev]) {
+      cudaFreeHost(g_host_cells[dev]);
+      g_host_cells[dev] = g_host_cells_dev[dev] = nullptr;
+    }
     for (auto& kv : d.live_blocks) cudaFree(kv.first);
     d.live_blocks.clear();
     d.free_blocks.clear();
@@ -591,6 +599,34 @@ int appy_h2d_staged(void* dptr, const void* hptr, size_t bytes, void* stream) {
     off += n;
     which ^= 1;
   }
+  return APPY_OK;
+}
+
+// Cells for shared scalars: one page of mapped, pinned host memory per device.  A reduction kernel that is
+// given the device address of a cell reads the initial value and writes the result over PCIe itself, so
+// the host needs neither an upload nor a download, only the wait for the stream (measured on a 4096-element
+// sum: 17.6 us per call against 31.5 us with a mirror, an 8-byte upload and an 8-byte download).
+int appy_host_cells(void** hptr, void** dptr, size_t* bytes) {
+  if (!hptr || !dptr) return fail(APPY_ERR_ARG, "appy_host_cells: NULL argument");
+  int dev;
+  if (int rc = cur_device(&dev)) return rc;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_host_cells[dev]) {
+    void* h = nullptr;
+    CK(cudaHostAlloc(&h, kHostCellBytes, cudaHostAllocMapped | cudaHostAllocPortable));
+    void* d = nullptr;
+    cudaError_t e = cudaHostGetDevicePointer(&d, h, 0);
+    if (e != cudaSuccess) {
+      cudaFreeHost(h);
+      return appy_fail_cuda(e, "cudaHostGetDevicePointer(host cells)");
+    }
+    memset(h, 0, kHostCellBytes);
+    g_host_cells[dev] = h;
+    g_host_cells_dev[dev] = d;
+  }
+  *hptr = g_host_cells[dev];
+  *dptr = g_host_cells_dev[dev];
+  if (bytes) *bytes = kHostCellBytes;
   return APPY_OK;
 }
 

@@ -79,6 +79,14 @@ int appy_d2h_async(void* hptr, const void* dptr, size_t bytes, void* stream);
  * chunk overlaps the DMA of the previous one.  Returns when the last chunk has been queued. */
 int appy_h2d_staged(void* dptr, const void* hptr, size_t bytes, void* stream);
 int appy_d2d_async(void* dst, const void* src, size_t bytes, void* stream);
+/* One page (4096 bytes) of mapped, pinned host memory of the current device, for the cells of shared
+ * scalars: *hptr is the host address, *dptr the address kernels use for the same bytes.  A kernel that
+ * updates a cell with ONE read and ONE write at its very end (the ordered commit of the reduction
+ * templates; atomics on host memory cross PCIe one by one) needs no upload and no download, only
+ * appy_sync.  Replaces, for a shared scalar, the pair `__tg_s = __tc_s.to('cuda')` / `__tc_s.copy_(__tg_s)`
+ * of the reference's generated host code (appy/backends/triton/passes/host_passes/gen_data_movement.py:14-96).
+ * The page lives until appy_shutdown; the caller hands out its bytes. */
+int appy_host_cells(void** hptr, void** dptr, size_t* bytes);
 
 /* ---- compile / launch -------------------------------------------------- */
 

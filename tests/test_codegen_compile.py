@@ -185,7 +185,7 @@ def test_shared_reduction_with_inner_simd_loops_uses_the_group_lowering():
     src = ("#pragma parallel for shared(s, m)\nfor i in range(M):\n    t = 0.0\n    #pragma simd\n"
            "    for j in range(N):\n        t += A[i, j]\n        m[0] = max(m[0], A[i, j])\n    s[0] += t * w[i]")
     scope = dict(A=A, w=np.ones(64, f32), s=np.array([0.0]), m=np.array([0.0], f32), M=64, N=64)
-    plan, code = build(src, scope)
+    plan, code = build(src, scope, _host_cells=False)     # cells mirrored on the device: atomic commit
     assert plan.kind == "group" and "appy_atomic(appy_add()" in code and "appy_atomic(appy_max()" in code
     assert "if (__g.lane == 0) __acc0" in code            # one lane of the group accumulates
     plan, code = build(src, scope, ordered_reduction=True)
@@ -285,3 +285,32 @@ def test_scalar_carried_through_a_simd_loop_without_a_reduction_is_refused():
           "        t = A[i, j]\n        t = t * 2.0\n        B[i, j] = t")     # written first in every iteration
     plan, _code = build(ok, dict(A=A, B=A.copy(), M=8, N=8))
     assert plan.kind == "group"
+
+
+def test_shared_scalar_in_a_host_array_gets_a_cell_in_mapped_host_memory():
+    """A reduction-only 1-element NumPy array (what shared(s) becomes) needs no device mirror: the variant uses
+    the ordered commit (one read and one write of the cell at the end of the kernel), so the cell can live in
+    mapped host memory.  A loop that also reads the array elsewhere, or the option switched off, keeps the
+    atomic commit on a mirrored cell."""
+    src = "#pragma parallel for simd shared(s)\nfor i in range(n):\n    s[0] += a[i]"
+    scope = dict(a=np.ones(100, f32), n=100, s=np.zeros(1))
+
+    def loop(text, sc, **opts):
+        vm = dispatcher.build_val_map(text, sc, {"np": np, "math": math})
+        e = cg.CompiledLoop(text, "kernel_loop_1", list(vm), tuple(cg._kind_of(v) for v in vm.values()), opts)
+        args = [v for v in vm.values() if not isinstance(v, types.ModuleType)]
+        return e, e._resolve_arrays(args), e.source_for(*args)
+
+    e, arrays, code = loop(src, scope)
+    assert e.cell_names == {"s"} and e._host_cells(arrays) == ("s",)
+    assert "appy_ws_arrive" in code and "appy_atomic" not in code
+    rt.compile_check(code, "kernel_loop_1", [f"-D{k}={v}" for k, v in list(e.variants.values())[0].tun.items()])
+    e, arrays, code = loop(src, scope, _host_cells=False)
+    assert e._host_cells(arrays) == () and "appy_atomic" in code
+    e, arrays, code = loop(src, scope, distribute=True)
+    assert e._host_cells(arrays) == ()
+    e, arrays, code = loop(src + "\n    b[i] = s[0]", dict(scope, b=np.ones(100, f32)))
+    assert e.cell_names == frozenset() and e._host_cells(arrays) == ()
+    big = dict(scope, s=np.zeros(100))          # 800 bytes: an array, not a cell
+    e, arrays, code = loop(src, big)
+    assert e._host_cells(arrays) == ()

@@ -1027,3 +1027,68 @@ def test_resident_host_arrays_are_uploaded_once_and_again_after_touch():
     cg.transfer_stats.update(h2d=0, d2h=0)
     k_axpy_host(1.0, x, y)
     assert cg.transfer_stats["h2d"] == 2 * 4 * n
+
+
+@appy.jit
+def k_cells_three(a, n):
+    s = 0.0
+    hi = -1.0e30
+    cnt = 0
+    #pragma parallel for simd shared(s, hi, cnt)
+    for i in range(n):
+        s += a[i]
+        hi = max(hi, a[i])
+        cnt += 1
+    return s, hi, cnt
+
+
+@appy.jit
+def k_cell_and_stored_array(a, b, n):
+    s = 1.5
+    #pragma parallel for simd shared(s)
+    for i in range(n):
+        b[i] = a[i] * 2.0
+        s += a[i]
+    return s
+
+
+@appy.jit(_host_cells=False)
+def k_cells_mirrored(a, n):
+    s = 0.0
+    #pragma parallel for simd shared(s)
+    for i in range(n):
+        s += a[i]
+    return s
+
+
+def test_shared_scalars_live_in_mapped_host_memory():
+    """shared(...) scalars reach the kernel as cells in the device's page of mapped host memory: no mirror, no
+    copy call; the kernel reads the initial value and writes the result itself (ordered commit).  Same values
+    as with mirrored cells; several cells per loop, float and integer, next to an ordinary stored NumPy array,
+    from the launch record as well as on first sight."""
+    import torch
+    from appy_b200.backends.cuda_sm100 import codegen as cg
+    rng = np.random.default_rng(5)
+    for n in (1, 1000, 100_000, 3_000_001):
+        a = rng.standard_normal(n).astype(np.float32)
+        da = torch.from_numpy(a).cuda()
+        for _rep in range(3):                       # first sight, then the launch record
+            s, hi, cnt = k_cells_three(da, n)
+            assert cnt == n and hi == a.max()
+            assert abs(s - float(a.sum(dtype=np.float64))) <= 1e-6 * float(np.abs(a).sum(dtype=np.float64)) + 1e-12
+        assert abs(k_cells_mirrored(da, n) - s) <= 1e-6 * float(np.abs(a).sum(dtype=np.float64)) + 1e-12
+    entry = [e for e in cg.code_cache.values() if e.kernel_name.startswith("k_cells_three_")][0]
+    assert entry.cell_names == {"s", "hi", "cnt"}
+    assert "appy_ws_arrive" in entry.last_variant.plan.source and "appy_atomic" not in entry.last_variant.plan.source
+    mirrored = [e for e in cg.code_cache.values() if e.kernel_name.startswith("k_cells_mirrored_")][0]
+    assert "appy_atomic" in mirrored.last_variant.plan.source
+    # NumPy inputs: the array is mirrored and comes back by a copy, the cell does not
+    a = rng.standard_normal(5000).astype(np.float32)
+    b = np.zeros(5000, np.float32)
+    cg.transfer_stats.update(h2d=0, d2h=0)
+    for _rep in range(2):
+        s = k_cell_and_stored_array(a, b, 5000)
+        assert np.array_equal(b, a * 2) and abs(s - 1.5 - float(a.sum(dtype=np.float64))) < 1e-3
+    assert cg.transfer_stats == {"h2d": 2 * (2 * 4 * 5000 + 8), "d2h": 2 * (4 * 5000 + 8)}
+    # an empty range leaves the cells as they were
+    assert k_cells_three(da, 0) == (0.0, -1.0e30, 0)
