@@ -224,6 +224,7 @@ class CompiledLoop:
         self.device = None
         self.sm_count = 148
         self.cell_names = self._find_cell_names()
+        self.overwritten, self._range_codes = self._find_overwritten()
 
     def _find_cell_names(self) -> frozenset:
         """Arrays that the loop touches only as targets of its own reductions (`s[0] += ...`, what a
@@ -257,6 +258,55 @@ class CompiledLoop:
             if ok:
                 names.add(name)
         return frozenset(names)
+
+    def _find_overwritten(self):
+        """(names, (lo code, hi code)): one-dimensional arrays that the loop never reads and whose only
+        store is `name[i] = ...` with the parallel index, unconditionally, in the loop's top-level body.
+        When the loop runs over the whole array, every element is written, so the host copy need not be
+        uploaded first (_skip_uploads)."""
+        loop = self.ir.loop
+        var = loop.target.id if isinstance(loop.target, ast.Name) else None
+        it = loop.iter
+        if var is None or not (isinstance(it, ast.Call) and 1 <= len(it.args) <= 3):
+            return frozenset(), None
+        if len(it.args) == 3 and not (isinstance(it.args[2], ast.Constant) and it.args[2].value == 1):
+            return frozenset(), None
+        import re
+        hoist = lambda node: re.sub(r"\b(\w+)\.shape\[(\d+)\]", r"\1_shape_\2", ast.unparse(node))
+        lo_src = "0" if len(it.args) == 1 else hoist(it.args[0])
+        hi_src = hoist(it.args[0] if len(it.args) == 1 else it.args[1])
+        try:
+            codes = (compile(lo_src, "<lo>", "eval"), compile(hi_src, "<hi>", "eval"))
+        except SyntaxError:
+            return frozenset(), None
+        if any(isinstance(x, (ast.Continue, ast.Break, ast.Return)) for x in ast.walk(loop)):
+            return frozenset(), None            # a top-level store may be jumped over
+        stores = {}
+        for st in loop.body:
+            if isinstance(st, ast.Assign) and len(st.targets) == 1 and isinstance(st.targets[0], ast.Subscript):
+                t = st.targets[0]
+                if isinstance(t.value, ast.Name) and isinstance(t.slice, ast.Name) and t.slice.id == var:
+                    stores.setdefault(t.value.id, []).append(t)
+        names = set()
+        for name, tgts in stores.items():
+            if name not in self.stored or name in self.cell_names:
+                continue
+            mentions = [x for x in ast.walk(loop) if isinstance(x, ast.Name) and x.id == name]
+            if len(mentions) == len(tgts):          # mentioned nowhere but as those targets
+                names.add(name)
+        return frozenset(names), codes
+
+    def _skip_uploads(self, args, arrays) -> tuple:
+        """Names of this call's host arrays that are written in full before anything could read them."""
+        if not self.overwritten or self.options.get("distribute") or not self.options.get("_skip_uploads", True):
+            return ()
+        try:
+            scope = self._scope(args, arrays)
+            lo, hi = int(eval(self._range_codes[0], {}, scope)), int(eval(self._range_codes[1], {}, scope))
+        except Exception:
+            return ()
+        return tuple(a.name for a in arrays if a.host and a.name in self.overwritten and a.tmp is None
+                     and len(a.shape) == 1 and lo == 0 and hi == a.shape[0])
 
     def _host_cells(self, arrays) -> tuple:
         """Names of the host arrays of this call that become cells in mapped host memory: reduction-only
@@ -302,7 +352,7 @@ class CompiledLoop:
             arrays.append(a)
         return arrays
 
-    def _acquire_device(self, arrays, stream, slices=None, hostcells=()):
+    def _acquire_device(self, arrays, stream, slices=None, hostcells=(), skip=()):
         """Device mirrors of the host arrays, filled from the host.  `slices` (distributed loops):
         {array name: (first byte, one past last byte)} for arrays of which this rank touches only a part.
         `hostcells`: names of arrays that get a cell in the device's page of mapped host memory instead
@@ -330,6 +380,8 @@ class CompiledLoop:
                 transfer_stats["h2d"] += a.nbytes
                 continue
             a.dptr, created = rt.mirror(a.hptr, a.nbytes)
+            if a.name in skip:          # every element is written by the loop before anything reads it
+                continue
             state = _resident.get(a.hptr) if (_resident and not slices and a.tmp is None) else None
             if state is not None and state[0] == a.nbytes:
                 if state[1] and not created:
@@ -853,7 +905,7 @@ class CompiledLoop:
 
     def _replay(self, memo, args) -> bool:
         (handle, grid, block, smem, pack, seq_slot, memo_stream, cells, host_slots, scalar_slots, post, scratch,
-         deferred, hostcells) = memo
+         deferred, hostcells, skip) = memo
         torch = sys.modules.get("torch")
         if torch is not None and (self.has_device_args or not host_slots):
             stream = _torch_stream(torch, self.device)      # orders with the producers of the device tensors
@@ -863,7 +915,7 @@ class CompiledLoop:
         if not disjoint or not (memo_stream is None or memo_stream == stream):     # a workspace belongs to one stream
             return False
         if host_slots:        # mirrors of the host arrays: look up, upload, patch into the arguments
-            self._acquire_device(harr, stream, None, hostcells)
+            self._acquire_device(harr, stream, None, hostcells, skip)
             for a, (_argi, _name, slot) in zip(harr, host_slots):
                 pack.values[slot].value = a.dptr
         for argi, slot in scalar_slots:
@@ -924,8 +976,9 @@ class CompiledLoop:
         from . import multi_gpu
         sharded = bool(self.options.get("distribute")) and any_host and multi_gpu.world()[1] > 1
         hostcells = self._host_cells(arrays) if any_host else ()
+        skip = self._skip_uploads(args, arrays) if any_host else ()
         if not sharded:
-            self._acquire_device(arrays, stream, None, hostcells)
+            self._acquire_device(arrays, stream, None, hostcells, skip)
         key = self._spec_key(arrays, hostcells)     # mirrors are 16-byte aligned whether or not they exist yet
         variant = self._variant(arrays, key)
         self.last_variant = variant
@@ -998,9 +1051,9 @@ class CompiledLoop:
                                      if self.arg_names[i] in pslot)
                 self.memo[mkey] = (h, grid, block, smem, pack, seq_slot,
                                    stream if (variant.plan.uses_ws or any_host or scratch) else None, cells,
-                                   tuple(host_slots), scalar_slots, post, scratch, deferred, hostcells)
+                                   tuple(host_slots), scalar_slots, post, scratch, deferred, hostcells, skip)
         elif not any_host and mkey is not None:
-            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells, (), (), None, None, None, ())
+            self.memo[mkey] = (0, 0, 0, 0, None, None, None, cells, (), (), None, None, None, (), ())
         if cells:
             self._post_combine(cells)
         if any_host:
@@ -1163,7 +1216,7 @@ def _register_finalizer(obj, hptr: int) -> None:
 
 _OPTION_KEYS = ("ordered_reduction", "combine", "defer", "distribute", "fp_contract", "autotune", "pin_host", "_generic_only", "_vectorize",
                 "_stream_hint", "_hoist_safe", "_shape_spec", "_neighbours", "_bulk_rows", "_group_vectorize",
-                "_spmm_stream", "_stream_rows", "_row_cost", "_host_cells")
+                "_spmm_stream", "_stream_rows", "_row_cost", "_host_cells", "_skip_uploads")
 
 
 _site_options: dict = {}       # site number -> option key; the loops of one rewritten function always pass the same options

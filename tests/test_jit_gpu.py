@@ -1089,6 +1089,53 @@ def test_shared_scalars_live_in_mapped_host_memory():
     for _rep in range(2):
         s = k_cell_and_stored_array(a, b, 5000)
         assert np.array_equal(b, a * 2) and abs(s - 1.5 - float(a.sum(dtype=np.float64))) < 1e-3
-    assert cg.transfer_stats == {"h2d": 2 * (2 * 4 * 5000 + 8), "d2h": 2 * (4 * 5000 + 8)}
+    assert cg.transfer_stats == {"h2d": 2 * (4 * 5000 + 8), "d2h": 2 * (4 * 5000 + 8)}     # b is only written
     # an empty range leaves the cells as they were
     assert k_cells_three(da, 0) == (0.0, -1.0e30, 0)
+
+
+@appy.jit
+def k_overwrite_all(a, b, c):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        c[i] = a[i] + b[i]
+
+
+@appy.jit
+def k_overwrite_part(a, c, n):
+    #pragma parallel for simd
+    for i in range(n):
+        c[i] = a[i] * 2.0
+
+
+@appy.jit
+def k_overwrite_some(a, c):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        if a[i] > 0.0:
+            c[i] = a[i]
+
+
+def test_an_array_that_is_overwritten_in_full_is_not_uploaded():
+    """A NumPy array that the loop never reads and stores in every element (`c[i] = ...` at the top level, over
+    the whole array) is not uploaded first; a partial range or a conditional store still uploads it, so the
+    elements the loop leaves alone come back unchanged."""
+    from appy_b200.backends.cuda_sm100 import codegen as cg
+    n = 10_000
+    rng = np.random.default_rng(11)
+    a, b = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    for _rep in range(2):                           # full path, then the launch record
+        c = np.full(n, 7.0, np.float32)
+        cg.transfer_stats.update(h2d=0, d2h=0)
+        k_overwrite_all(a, b, c)
+        assert np.array_equal(c, a + b)
+        assert cg.transfer_stats == {"h2d": 2 * 4 * n, "d2h": 4 * n}
+    for m in (n, n // 2, 0):
+        c = np.full(n, 7.0, np.float32)
+        cg.transfer_stats.update(h2d=0, d2h=0)
+        k_overwrite_part(a, c, m)
+        assert np.array_equal(c[:m], a[:m] * 2) and np.all(c[m:] == 7.0)
+        assert cg.transfer_stats["h2d"] == (4 * n if m == n else 2 * 4 * n)
+    c = np.full(n, 7.0, np.float32)
+    k_overwrite_some(a, c)
+    assert np.array_equal(c, np.where(a > 0, a, np.float32(7.0)))
