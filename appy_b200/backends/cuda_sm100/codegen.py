@@ -381,6 +381,7 @@ class CompiledLoop:
                 continue
             a.dptr, created = rt.mirror(a.hptr, a.nbytes)
             if a.name in skip:          # every element is written by the loop before anything reads it
+                _maybe_pin(a.hptr, a.nbytes, a.obj, a.pinnable and self.options.get("pin_host", True))
                 continue
             state = _resident.get(a.hptr) if (_resident and not slices and a.tmp is None) else None
             if state is not None and state[0] == a.nbytes:
@@ -1095,13 +1096,10 @@ class CompiledLoop:
         return self._variant(arrays, self._spec_key(arrays, self._host_cells(arrays))).plan.source
 
 
-def _upload(dst: int, src: int, nbytes: int, base: int, base_bytes: int, owner, may_pin: bool, stream: int) -> None:
-    """Host-to-device copy of [src, src + nbytes), a part of the host buffer [base, base + base_bytes)
-    owned by `owner`.  A buffer of at least 1 MiB that comes back a second time is pinned in place, after
-    which its copies are true DMA; until then large pageable buffers go through the pinned staging
-    buffers of the runtime."""
-    if nbytes <= 0:
-        return
+def _maybe_pin(base: int, base_bytes: int, owner, may_pin: bool) -> bool:
+    """Pin the host buffer [base, base + base_bytes) in place when it is at least 1 MiB and is seen for
+    the second time; True if it is pinned.  Serves downloads as well as uploads: a copy into pageable
+    memory is staged by the driver and blocks the caller."""
     pinned = base in _finalizers
     if base_bytes >= _PIN_MIN_BYTES and may_pin and not pinned:
         if len(_seen_host) > 4096:
@@ -1115,6 +1113,17 @@ def _upload(dst: int, src: int, nbytes: int, base: int, base_bytes: int, owner, 
                 pinned = base in _finalizers
             except rt.AppyRuntimeError:
                 pass
+    return pinned
+
+
+def _upload(dst: int, src: int, nbytes: int, base: int, base_bytes: int, owner, may_pin: bool, stream: int) -> None:
+    """Host-to-device copy of [src, src + nbytes), a part of the host buffer [base, base + base_bytes)
+    owned by `owner`.  A buffer of at least 1 MiB that comes back a second time is pinned in place, after
+    which its copies are true DMA; until then large pageable buffers go through the pinned staging
+    buffers of the runtime."""
+    if nbytes <= 0:
+        return
+    pinned = _maybe_pin(base, base_bytes, owner, may_pin)
     if pinned or base_bytes < _PIN_MIN_BYTES:
         rt.h2d(dst, src, nbytes, stream)          # true DMA, or too small to matter
     else:
