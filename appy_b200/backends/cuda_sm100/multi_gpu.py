@@ -207,6 +207,30 @@ class P2PCombiner:
             self._ctx = None
 
 
+def local_group(world_size: int, spin_limit: int = 0) -> list:
+    """`world_size` combiners, one per rank, for ranks that live in this process on the current device
+    (appy_p2p_open_local: mailboxes wired by address).  A rank's loops are called with its combiner
+    installed (set_combiner) and on a stream of its own (the partials of a split-phase launch wait in the
+    stream's workspace); kernels of different ranks on one GPU must not wait for one another, so only
+    `defer=True` loops fit, with every rank's launch k complete before any rank's launch k+1 starts."""
+    import ctypes as C
+    group = []
+    for r in range(world_size):
+        c = P2PCombiner.__new__(P2PCombiner)
+        c.rank, c.world = r, world_size
+        c._ctx = C.c_void_p()
+        handle = (C.c_char * 64)()
+        rt.check(rt.lib().appy_p2p_create(world_size, r, C.byref(c._ctx), handle))
+        c._seq, c.pending, c.to_fold, c.to_collect, c.split_count = 0, [], None, None, 0
+        group.append(c)
+    ctxs = (C.c_void_p * world_size)(*[c._ctx.value for c in group])
+    for c in group:
+        desc = C.c_void_p()
+        rt.check(rt.lib().appy_p2p_open_local(c._ctx, ctxs, spin_limit, C.byref(desc)))
+        c.descriptor = desc.value
+    return group
+
+
 _COMBINER = None
 
 

@@ -63,6 +63,7 @@ SIGNATURES = {
                                      C.POINTER(C.c_int64), C.c_void_p]),
     "appy_p2p_create": (C.c_int, [C.c_int, C.c_int, c_void_pp, C.c_void_p]),
     "appy_p2p_open": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint, c_void_pp]),
+    "appy_p2p_open_local": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_uint, c_void_pp]),
     "appy_p2p_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
     "appy_p2p_destroy": (C.c_int, [C.c_void_p]),
     "appy_p2p_combine": (C.c_int, [C.c_void_p, C.c_uint64, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),

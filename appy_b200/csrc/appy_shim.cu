@@ -897,6 +897,22 @@ struct P2PContext {
 
 typedef appy_mailbox MailboxDesc;   // the descriptor the kernels read (templates/t_flat.cuh)
 
+// the device-side descriptor of an opened context: every rank's mailbox, own mailbox, limits
+static int p2p_finish_open(P2PContext* c, unsigned spin_limit, void** device_descriptor) {
+  MailboxDesc d;
+  memset(&d, 0, sizeof d);
+  d.world = c->world;
+  d.rank = c->rank;
+  d.spin_limit = spin_limit ? spin_limit : (1u << 23);
+  d.err = c->d_err;
+  for (int r = 0; r < 16; ++r) d.peer[r] = static_cast<unsigned long long*>(c->peers[r < c->world ? r : c->rank]);
+  d.own = static_cast<unsigned long long*>(c->peers[c->rank]);
+  CK(cudaMemcpy(c->d_desc, &d, sizeof d, cudaMemcpyHostToDevice));
+  c->opened = true;
+  *device_descriptor = c->d_desc;
+  return APPY_OK;
+}
+
 int appy_p2p_create(int world, int rank, void** ctx, void* ipc_handle_out) {
   if (!ctx || !ipc_handle_out || world < 1 || world > 16 || rank < 0 || rank >= world)
     return fail(APPY_ERR_ARG, "appy_p2p_create: bad arguments");
@@ -938,18 +954,21 @@ int appy_p2p_open(void* ctx, const void* all_handles, unsigned spin_limit, void*
     if (e != cudaSuccess)
       return fail(APPY_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d) failed: %s", r, cudaGetErrorString(e));
   }
-  MailboxDesc d;
-  memset(&d, 0, sizeof d);
-  d.world = c->world;
-  d.rank = c->rank;
-  d.spin_limit = spin_limit ? spin_limit : (1u << 23);
-  d.err = c->d_err;
-  for (int r = 0; r < 16; ++r) d.peer[r] = static_cast<unsigned long long*>(c->peers[r < c->world ? r : c->rank]);
-  d.own = static_cast<unsigned long long*>(c->peers[c->rank]);
-  CK(cudaMemcpy(c->d_desc, &d, sizeof d, cudaMemcpyHostToDevice));
-  c->opened = true;
-  *device_descriptor = c->d_desc;
-  return APPY_OK;
+  return p2p_finish_open(c, spin_limit, device_descriptor);
+}
+
+int appy_p2p_open_local(void* ctx, void* const* contexts, unsigned spin_limit, void** device_descriptor) {
+  if (!ctx || !contexts || !device_descriptor) return fail(APPY_ERR_ARG, "appy_p2p_open_local: NULL argument");
+  P2PContext* c = static_cast<P2PContext*>(ctx);
+  for (int r = 0; r < c->world; ++r) {
+    const P2PContext* o = static_cast<const P2PContext*>(contexts[r]);
+    if (!o || o->world != c->world || o->rank != r)
+      return fail(APPY_ERR_ARG, "appy_p2p_open_local: contexts[%d] is not rank %d of a world of %d", r, r, c->world);
+    c->peers[r] = o->local;
+  }
+  if (contexts[c->rank] != ctx) return fail(APPY_ERR_ARG, "appy_p2p_open_local: contexts[rank] is another context");
+  c->loopback = true;              // nothing was opened through IPC, so nothing is closed
+  return p2p_finish_open(c, spin_limit, device_descriptor);
 }
 
 }  // extern "C"

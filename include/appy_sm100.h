@@ -168,6 +168,12 @@ int appy_row_histogram(const void* d_indptr, int idx_bytes, int64_t nrows, int64
 int appy_p2p_create(int world, int rank, void** ctx, void* ipc_handle_out /* 64 bytes */);
 int appy_p2p_open(void* ctx, const void* all_handles /* world x 64 bytes */, unsigned spin_limit,
                   void** device_descriptor);
+/* The same for ranks that live in ONE process (a host that drives several GPUs itself, or several ranks on
+ * one GPU whose kernels are queued one after another on one stream): contexts[r] is the context created for
+ * rank r in this process; the mailboxes are wired by address, no IPC handle is opened.  With ranks on
+ * different GPUs the caller enables peer access first.  Kernels of ranks that share a GPU must not wait for
+ * one another: only the split-phase exchange, whose collect finds the words already posted, fits that use. */
+int appy_p2p_open_local(void* ctx, void* const* contexts, unsigned spin_limit, void** device_descriptor);
 int appy_p2p_status(void* ctx, int* timed_out);
 int appy_p2p_destroy(void* ctx);
 /* Combine `count` (1..4) device scalars of one type across all ranks, in place: every rank ends with

@@ -142,6 +142,51 @@ def test_split_phase_exchange_on_one_rank(rt):
         mg.set_combiner(None)
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_split_phase_exchange_with_all_ranks_on_one_gpu(rt, world):
+    """The device side of the split-phase exchange for a world of 8 without 8 GPUs: the ranks live in this
+    process (mg.local_group: mailboxes wired by address), each with its own stream, data and cells.  Every
+    rank's launch k has completed before any rank's launch k+1 is queued, so no kernel ever waits for
+    another one: the words a launch collects were posted by launches that are over.  All ranks must end
+    with the same bits, equal to the sum over ranks and steps."""
+    mg.set_combiner(None)
+    group = mg.local_group(world)
+    streams = [torch.cuda.Stream() for _ in range(world)]
+    try:
+        n = (1 << 18) + 3
+        data = [torch.from_numpy(W.vec_sum(n, seed=20 + r)).cuda() for r in range(world)]
+        s = [torch.full((1,), 2.0, dtype=torch.float64, device="cuda") for _ in range(world)]
+        m = [torch.full((1,), -1.0, dtype=torch.float32, device="cuda") for _ in range(world)]
+        cnt = [torch.zeros(1, dtype=torch.int64, device="cuda") for _ in range(world)]
+        torch.cuda.synchronize()
+
+        def step(fn):
+            for r in range(world):
+                mg.set_combiner(group[r])
+                with torch.cuda.stream(streams[r]):
+                    fn(r)
+            torch.cuda.synchronize()
+
+        steps = 11                                    # more than the ring's 8 slots
+        for _k in range(steps):
+            step(lambda r: sum_and_max_into(data[r], s[r], m[r]))
+            step(lambda r: count_into(data[r], cnt[r]))
+        for _ in range(2):
+            step(lambda r: group[r].flush(streams[r].cuda_stream))
+        host = [d.cpu().numpy() for d in data]
+        total = sum(float(np.sum(h, dtype=np.float64)) for h in host)
+        for r in range(world):
+            assert not group[r].timed_out() and group[r].pending == []
+            assert np.isclose(s[r].item(), 2.0 + steps * total, rtol=1e-5)
+            assert m[r].item() == max(float(h.max()) for h in host)
+            assert cnt[r].item() == steps * sum(int((h > 0.5).sum()) for h in host)
+            assert s[r].item() == s[0].item()         # the same bits on every rank
+    finally:
+        mg.set_combiner(None)
+        for c in group:
+            c.close()
+
+
 def test_split_phase_collect_times_out_with_a_status(rt):
     c = mg.P2PCombiner(spin_limit=100_000, loopback_world=2)
     mg.set_combiner(c)
