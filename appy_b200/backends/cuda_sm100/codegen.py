@@ -315,9 +315,12 @@ class CompiledLoop:
         if not self.cell_names or not self.options.get("_host_cells", True) or self.options.get("distribute") \
                 or self.options.get("combine"):
             return ()
-        out = [a.name for a in arrays if a.host and a.name in self.cell_names and 0 < a.nbytes <= 64
-               and a.tmp is None]
-        return tuple(out[:8])
+        picked = [a for a in arrays if a.host and a.name in self.cell_names and 0 < a.nbytes <= 64
+                  and a.tmp is None]
+        spans = sorted((a.hptr, a.hptr + a.nbytes) for a in arrays if a.host and a.nbytes)
+        if any(spans[i][1] > spans[i + 1][0] for i in range(len(spans) - 1)):
+            return ()           # two names for one host array accumulate into one mirror; two cells would not
+        return tuple(a.name for a in picked[:8])
 
     # ------------------------------------------------------------------ specialisation
     def _resolve_arrays(self, args):

@@ -1061,6 +1061,14 @@ def k_cells_mirrored(a, n):
     return s
 
 
+@appy.jit
+def k_two_cells_into(a, o1, o2):
+    #pragma parallel for simd
+    for i in range(a.shape[0]):
+        o1[0] += a[i]
+        o2[0] += 2.0 * a[i]
+
+
 def test_shared_scalars_live_in_mapped_host_memory():
     """shared(...) scalars reach the kernel as cells in the device's page of mapped host memory: no mirror, no
     copy call; the kernel reads the initial value and writes the result itself (ordered commit).  Same values
@@ -1082,6 +1090,8 @@ def test_shared_scalars_live_in_mapped_host_memory():
     assert "appy_ws_arrive" in entry.last_variant.plan.source and "appy_atomic" not in entry.last_variant.plan.source
     mirrored = [e for e in cg.code_cache.values() if e.kernel_name.startswith("k_cells_mirrored_")][0]
     assert "appy_atomic" in mirrored.last_variant.plan.source
+    a_last = da.cpu().numpy()
+    a_dev_sum = a_last.sum(dtype=np.float64)
     # NumPy inputs: the array is mirrored and comes back by a copy, the cell does not
     a = rng.standard_normal(5000).astype(np.float32)
     b = np.zeros(5000, np.float32)
@@ -1092,6 +1102,10 @@ def test_shared_scalars_live_in_mapped_host_memory():
     assert cg.transfer_stats == {"h2d": 2 * (4 * 5000 + 8), "d2h": 2 * (4 * 5000 + 8)}     # b is only written
     # an empty range leaves the cells as they were
     assert k_cells_three(da, 0) == (0.0, -1.0e30, 0)
+    # one host array under two names: both reductions land in the same cell, as with a mirror
+    o = np.zeros(1)
+    k_two_cells_into(da, o, o)
+    assert abs(o[0] - 3.0 * float(a_dev_sum)) <= 1e-6 * float(np.abs(a_last).sum(dtype=np.float64))
 
 
 @appy.jit
